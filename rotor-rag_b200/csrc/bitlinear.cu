@@ -1,0 +1,382 @@
+// Ternary BitLinear integer core: acc[c][o] = sum_k xq[c][k] * w[o][k].
+//
+// HBM-bound: the kernel streams each 512-byte weight tile exactly once with one
+// 128-bit load per lane, stages the int8 activation columns in shared memory with a
+// bulk (TMA) copy, and decodes in registers with one AND per operand word:
+// (word & (0x03030303 << 2j)) is the int8x4 vector 4^j * (w+1).  Partial sums are
+// kept per bit-pair j and rescaled exactly (arithmetic shift) at the end; the "+1"
+// of the code is removed by subtracting sum_k xq[c][k] (xsum).
+//
+// Two instruction mixes share the layout:
+//   DP4A : dp4a.u32.s32 lanes, up to 4 columns per pass (decode work is per weight,
+//          multiply work per weight per column);
+//   MMA  : mma.sync m16n8k32 u8 x s8 -> s32; the tile IS the A fragment, 8 columns
+//          per pass at the cost of one, which also carries the residual terms of the
+//          multi-term activation quantiser.
+#include "common.cuh"
+
+namespace rb {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Stage `ncols` activation columns, `bytes` each, into shared memory with bulk async
+// copies signalled on an mbarrier, then wait with a bounded spin.  Returns false when
+// the wait gave up (the caller records it; results are then undefined but every access
+// stays in bounds).
+__device__ __forceinline__ void stage_begin(uint64_t* bar, int8_t* xs, int xs_stride, const int8_t* src,
+                                            size_t src_stride, int ncols, uint32_t bytes) {
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                     "r"(bytes * (uint32_t)ncols)
+                     : "memory");
+        for (int c = 0; c < ncols; ++c)
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                    smem_u32(xs + (size_t)c * xs_stride)),
+                "l"(src + (size_t)c * src_stride), "r"(bytes), "r"(smem_u32(bar))
+                : "memory");
+    }
+}
+
+// Call after a __syncthreads() that follows stage_begin.
+__device__ __forceinline__ bool stage_wait(uint64_t* bar) {
+    uint32_t ok = 0;
+    for (int spin = 0; spin < (1 << 20) && !ok; ++spin)
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(smem_u32(bar))
+            : "memory");
+    return ok != 0;
+}
+
+constexpr int XS_PAD = 16;  // bytes between staged columns: keeps 128-bit fragment loads conflict-free
+
+struct AccParams {
+    const uint4* tiles;
+    const int8_t* xq;      // [ncols][kpad]
+    const int32_t* xsum;   // [ncols]
+    int32_t* acc;          // [ncols][out]
+    unsigned* status;      // device word, set to ROTOR_B200_ERR_TIMEOUT on a staging timeout
+    int out;
+    int nkt;               // k-tiles per row of tiles
+    int kt_per_split;
+    int ncols;
+    int atomic;            // gridDim.y > 1: accumulate with integer atomics into zeroed acc
+};
+
+template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
+__global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(AccParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int rt = blockIdx.x;
+    const int kt0 = blockIdx.y * p.kt_per_split;
+    const int kt1 = min(p.nkt, kt0 + p.kt_per_split);
+    const int ks = (kt1 - kt0) * TILE_K;
+    const int xs_stride = p.kt_per_split * TILE_K + XS_PAD;
+
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
+    int* red = reinterpret_cast<int*>(smem_raw + 16);            // [WARPS][128]
+    int8_t* xs = reinterpret_cast<int8_t*>(smem_raw + 16 + WARPS * 128 * 4);
+
+    stage_begin(bar, xs, xs_stride, p.xq + (size_t)kt0 * TILE_K, (size_t)p.nkt * TILE_K, p.ncols, (uint32_t)ks);
+
+    const uint4* trow = p.tiles + ((size_t)rt * p.nkt) * 32 + lane;
+
+    int accm[4][4];          // MMA: [bit pair j][fragment register]
+    int accd[2][4][NCOL];    // DP4A: [row half][bit pair j][column]
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) accm[j][r] = 0;
+#pragma unroll
+        for (int c = 0; c < NCOL; ++c) accd[0][j][c] = accd[1][j][c] = 0;
+    }
+
+    // First batch of weight tiles is requested before the activations are waited for.
+    uint4 wv[UMAX];
+    int base = kt0 + warp;
+#pragma unroll
+    for (int u = 0; u < UMAX; ++u)
+        if (base + u * WARPS < kt1) wv[u] = ld_stream_v4(trow + (size_t)(base + u * WARPS) * 32);
+    __syncthreads();  // mbarrier initialised, bulk copies issued
+    if (!stage_wait(bar) && threadIdx.x == 0) atomicMax(p.status, (unsigned)ROTOR_B200_ERR_TIMEOUT);
+
+    while (base < kt1) {
+#pragma unroll
+        for (int u = 0; u < UMAX; ++u) {
+            const int kt = base + u * WARPS;
+            if (kt < kt1) {
+                const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+                const int koff = (kt - kt0) * TILE_K + 32 * t;
+                if constexpr (USE_MMA) {
+                    uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
+                    if (g < p.ncols) {
+                        const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)g * xs_stride + koff);
+                        xa = xp[0];
+                        xb = xp[1];
+                    }
+                    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t m = 0x03030303u << (2 * j);
+                        mma_u8s8(accm[j], pw[0] & m, pw[1] & m, pw[2] & m, pw[3] & m, xw[2 * j], xw[2 * j + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < NCOL; ++c) {
+                        const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)c * xs_stride + koff);
+                        const uint4 xa = xp[0], xb = xp[1];
+                        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t m = 0x03030303u << (2 * j);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                accd[i & 1][j][c] = dp4a_us(pw[i] & m, xw[2 * j + (i >> 1)], accd[i & 1][j][c]);
+                        }
+                    }
+                }
+            }
+        }
+        base += UMAX * WARPS;
+#pragma unroll
+        for (int u = 0; u < UMAX; ++u)
+            if (base + u * WARPS < kt1) wv[u] = ld_stream_v4(trow + (size_t)(base + u * WARPS) * 32);
+    }
+
+    // exact rescale of the per-bit-pair partial sums, then reduce across the CTA
+    int* myred = red + warp * 128;
+    if constexpr (USE_MMA) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int v = accm[0][r] + (accm[1][r] >> 2) + (accm[2][r] >> 4) + (accm[3][r] >> 6);
+            const int row_l = g + 8 * (r >> 1), col = 2 * t + (r & 1);
+            myred[row_l * 8 + col] = v;
+        }
+    } else {
+#pragma unroll
+        for (int rh = 0; rh < 2; ++rh)
+#pragma unroll
+            for (int c = 0; c < NCOL; ++c) {
+                int v = accd[rh][0][c] + (accd[rh][1][c] >> 2) + (accd[rh][2][c] >> 4) + (accd[rh][3][c] >> 6);
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                if (t == 0) myred[(g + 8 * rh) * 8 + c] = v;
+            }
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        const int row_l = threadIdx.x >> 3, col = threadIdx.x & 7;
+        const int row = rt * TILE_ROWS + row_l;
+        if (col < p.ncols && row < p.out) {
+            int s = 0;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) s += red[w * 128 + threadIdx.x];
+            if (blockIdx.y == 0) s -= p.xsum[col];
+            int32_t* dst = p.acc + (size_t)col * p.out + row;
+            if (p.atomic)
+                atomicAdd(dst, s);
+            else
+                *dst = s;
+        }
+    }
+}
+
+__global__ void dequant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ sx, int m, int terms,
+                               int out, float wscale, const float* __restrict__ wscale_vec,
+                               float* __restrict__ y) {
+    const size_t total = (size_t)m * out;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / out), o = (int)(i % out);
+        float v = 0.f;
+        for (int tt = 0; tt < terms; ++tt)
+            v = __fadd_rn(v, __fmul_rn((float)acc[((size_t)r * terms + tt) * out + o], sx[r * terms + tt]));
+        y[i] = __fmul_rn(v, wscale_vec ? wscale_vec[o] : wscale);
+    }
+}
+
+// Device status word shared by every launch of the library in this process.
+static unsigned* g_status = nullptr;
+static int ensure_status() {
+    if (g_status) return ROTOR_B200_OK;
+    RB_CUDA(cudaMalloc(&g_status, sizeof(unsigned)));
+    RB_CUDA(cudaMemset(g_status, 0, sizeof(unsigned)));
+    return ROTOR_B200_OK;
+}
+
+template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
+static int launch_acc(const AccParams& p, int nrt, int ksplit, cudaStream_t st) {
+    auto kern = bitlinear_acc_kernel<WARPS, UMAX, USE_MMA, NCOL>;
+    const size_t smem = 16 + WARPS * 128 * 4 + (size_t)p.ncols * (p.kt_per_split * TILE_K + XS_PAD);
+    if (smem > 48 * 1024) {
+        static size_t configured = 0;
+        if (smem > configured) {
+            RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            configured = 200 * 1024;
+        }
+    }
+    kern<<<dim3(nrt, ksplit), WARPS * 32, smem, st>>>(p);
+    return launch_status();
+}
+
+// Split the K range over gridDim.y so that the grid covers the GPU a few times and
+// the staged activations stay below ~64 KB per CTA.
+static int choose_ksplit(int nrt, int nkt, int ncols, int warps) {
+    int ks = 1;
+    while (ks < nkt) {
+        const int per = (nkt + ks - 1) / ks;
+        const bool enough_ctas = (long)nrt * ks >= 2 * 148;
+        const bool smem_ok = (size_t)ncols * (per * TILE_K + XS_PAD) <= 64 * 1024;
+        const bool too_thin = per / 2 < warps;  // keep at least one tile per warp after doubling
+        if (smem_ok && (enough_ctas || too_thin)) break;
+        ks *= 2;
+    }
+    return ks > nkt ? nkt : ks;
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" {
+
+int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum,
+                             size_t ncols, int32_t* acc, int variant, void* stream) {
+    RB_REQUIRE(tiles && xq && xsum && acc && out > 0 && in > 0 && ncols > 0);
+    RB_REQUIRE(out < (1u << 30) && in < (1u << 30));
+    RB_REQUIRE(((uintptr_t)tiles & 15) == 0 && ((uintptr_t)xq & 15) == 0);
+    if (variant == ROTOR_B200_VARIANT_AUTO) variant = ROTOR_B200_VARIANT_MMA;
+    RB_REQUIRE(variant == ROTOR_B200_VARIANT_DP4A || variant == ROTOR_B200_VARIANT_MMA);
+    int rc = ensure_status();
+    if (rc) return rc;
+    cudaStream_t st = as_stream(stream);
+    const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
+    const size_t kpad = kpad_of(in);
+    const size_t chunk = variant == ROTOR_B200_VARIANT_MMA ? 8 : 4;
+    constexpr int WARPS = 4, UMAX = 8;
+    for (size_t c0 = 0; c0 < ncols; c0 += chunk) {
+        const int nc = (int)((ncols - c0) < chunk ? (ncols - c0) : chunk);
+        const int ksplit = choose_ksplit(nrt, nkt, nc, WARPS);
+        AccParams p;
+        p.tiles = (const uint4*)tiles;
+        p.xq = xq + c0 * kpad;
+        p.xsum = xsum + c0;
+        p.acc = acc + c0 * out;
+        p.status = g_status;
+        p.out = (int)out;
+        p.nkt = nkt;
+        p.kt_per_split = (nkt + ksplit - 1) / ksplit;
+        p.ncols = nc;
+        p.atomic = ksplit > 1;
+        const int ksplit_eff = (nkt + p.kt_per_split - 1) / p.kt_per_split;
+        if (p.atomic) RB_CUDA(cudaMemsetAsync(p.acc, 0, (size_t)nc * out * sizeof(int32_t), st));
+        if (variant == ROTOR_B200_VARIANT_MMA)
+            rc = launch_acc<WARPS, UMAX, true, 8>(p, nrt, ksplit_eff, st);
+        else if (nc == 1)
+            rc = launch_acc<WARPS, UMAX, false, 1>(p, nrt, ksplit_eff, st);
+        else if (nc == 2)
+            rc = launch_acc<WARPS, UMAX, false, 2>(p, nrt, ksplit_eff, st);
+        else if (nc == 3)
+            rc = launch_acc<WARPS, UMAX, false, 3>(p, nrt, ksplit_eff, st);
+        else
+            rc = launch_acc<WARPS, UMAX, false, 4>(p, nrt, ksplit_eff, st);
+        if (rc) return rc;
+    }
+    return ROTOR_B200_OK;
+}
+
+int rotor_b200_bitlinear_dequant(const int32_t* acc, const float* sx, size_t m, int terms, size_t out,
+                                 float wscale, const float* wscale_vec, float* y, void* stream) {
+    RB_REQUIRE(acc && sx && y && m > 0 && out > 0 && terms >= 1 && terms <= 4);
+    const size_t total = m * out;
+    unsigned grid = (unsigned)((total + 255) / 256);
+    if (grid > 148 * 16) grid = 148 * 16;
+    dequant_kernel<<<grid, 256, 0, as_stream(stream)>>>(acc, sx, (int)m, terms, (int)out, wscale, wscale_vec, y);
+    return launch_status();
+}
+
+static inline size_t al256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+size_t rotor_b200_bitlinear_workspace_bytes(size_t out, size_t in, size_t m, int terms) {
+    const size_t nc = m * (size_t)terms;
+    return al256(nc * kpad_of(in)) + al256(nc * 4) + al256(nc * 4) + al256(nc * out * 4);
+}
+
+int rotor_b200_bitlinear_forward(const void* tiles, size_t out, size_t in, const float* x, size_t m, int terms,
+                                 float wscale, const float* wscale_vec, float* y, void* workspace,
+                                 size_t workspace_bytes, int variant, void* stream) {
+    RB_REQUIRE(tiles && x && y && workspace && m > 0 && terms >= 1 && terms <= 4);
+    RB_REQUIRE(((uintptr_t)workspace & 255) == 0);
+    if (workspace_bytes < rotor_b200_bitlinear_workspace_bytes(out, in, m, terms)) return ROTOR_B200_ERR_WORKSPACE;
+    const size_t nc = m * (size_t)terms;
+    unsigned char* w = (unsigned char*)workspace;
+    int8_t* xq = (int8_t*)w;
+    w += al256(nc * kpad_of(in));
+    float* sx = (float*)w;
+    w += al256(nc * 4);
+    int32_t* xsum = (int32_t*)w;
+    w += al256(nc * 4);
+    int32_t* acc = (int32_t*)w;
+    int rc = rotor_b200_quantize_rows(x, m, in, terms, xq, sx, xsum, stream);
+    if (rc) return rc;
+    rc = rotor_b200_bitlinear_acc(tiles, out, in, xq, xsum, nc, acc, variant, stream);
+    if (rc) return rc;
+    return rotor_b200_bitlinear_dequant(acc, sx, m, terms, out, wscale, wscale_vec, y, stream);
+}
+
+int rotor_b200_ternary_matmul_host(const void* tiles, const float* scales_host, const float* x_host, size_t in,
+                                   size_t out, int terms, float* y_host) {
+    RB_REQUIRE(tiles && scales_host && x_host && y_host && in > 0 && out > 0 && terms >= 1 && terms <= 4);
+    // grow-only staging area owned by the library: this seam is synchronous and single-threaded
+    static unsigned char* stage = nullptr;
+    static size_t stage_bytes = 0;
+    const size_t ws = rotor_b200_bitlinear_workspace_bytes(out, in, 1, terms);
+    const size_t need = al256(in * 4) + 2 * al256(out * 4) + ws;
+    if (need > stage_bytes) {
+        if (stage) RB_CUDA(cudaFree(stage));
+        stage = nullptr;
+        stage_bytes = 0;
+        RB_CUDA(cudaMalloc(&stage, need));
+        stage_bytes = need;
+    }
+    float* dx = (float*)stage;
+    float* dsc = (float*)(stage + al256(in * 4));
+    float* dy = (float*)(stage + al256(in * 4) + al256(out * 4));
+    void* dws = stage + al256(in * 4) + 2 * al256(out * 4);
+    RB_CUDA(cudaMemcpy(dx, x_host, in * 4, cudaMemcpyHostToDevice));
+    RB_CUDA(cudaMemcpy(dsc, scales_host, out * 4, cudaMemcpyHostToDevice));
+    int rc = rotor_b200_bitlinear_forward(tiles, out, in, dx, 1, terms, 1.0f, dsc, dy, dws, ws,
+                                          ROTOR_B200_VARIANT_AUTO, nullptr);
+    if (rc) return rc;
+    RB_CUDA(cudaMemcpy(y_host, dy, out * 4, cudaMemcpyDeviceToHost));
+    return ROTOR_B200_OK;
+}
+
+/* Reads and clears the device status word that bounded waits write to. */
+int rotor_b200_device_status(void) {
+    if (!g_status) return ROTOR_B200_OK;
+    unsigned v = 0;
+    RB_CUDA(cudaMemcpy(&v, g_status, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v) RB_CUDA(cudaMemset(g_status, 0, sizeof(v)));
+    return (int)v;
+}
+
+}  // extern "C"

@@ -1,0 +1,98 @@
+// Shared declarations for the sm_100a kernels behind librotor_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/rotor_b200.h"
+
+namespace rb {
+
+// Weight tile: 16 output rows x 128 input columns, 512 bytes, one uint4 per lane.
+constexpr int TILE_ROWS = 16;
+constexpr int TILE_K = 128;
+constexpr int TILE_BYTES = 512;
+
+__host__ __device__ inline size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+__host__ __device__ inline size_t kpad_of(size_t in) { return round_up(in, TILE_K); }
+__host__ __device__ inline size_t opad_of(size_t out) { return round_up(out, TILE_ROWS); }
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Launch-status helper: maps the last CUDA error to the library's status codes.
+inline int launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ROTOR_B200_OK : ROTOR_B200_ERR_CUDA;
+}
+
+#define RB_REQUIRE(cond)                     \
+    do {                                     \
+        if (!(cond)) return ROTOR_B200_ERR_ARG; \
+    } while (0)
+
+#define RB_CUDA(call)                                        \
+    do {                                                     \
+        if ((call) != cudaSuccess) return ROTOR_B200_ERR_CUDA; \
+    } while (0)
+
+// ---------------------------------------------------------------- device helpers
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Block-wide reductions over up to 1024 threads.  `scratch` holds 33 floats.
+// Every thread receives the result.  Two barriers per call.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[w] = v;
+    __syncthreads();
+    float r = (lane < nw) ? scratch[lane] : 0.f;
+    return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[w] = v;
+    __syncthreads();
+    float r = (lane < nw) ? scratch[lane] : -3.4e38f;
+    return warp_max(r);
+}
+__device__ __forceinline__ int block_sum_i(int v, int* scratch) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum_i(v);
+    __syncthreads();
+    if (lane == 0) scratch[w] = v;
+    __syncthreads();
+    int r = (lane < nw) ? scratch[lane] : 0;
+    return warp_sum_i(r);
+}
+
+// Streaming 128-bit load that bypasses L1 (weights are read exactly once).
+__device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace rb

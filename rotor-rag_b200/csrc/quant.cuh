@@ -1,0 +1,51 @@
+// Per-row absmax int8 quantiser shared by the stand-alone quantise kernel and the
+// fused vector stages.  Arithmetic is float32 with one IEEE rounding per operation
+// (no fused multiply-add, true division) so the result is bit-identical to NumPy's
+// max|x|/127, rint(x/s), clip, residual = x - q*s evaluated in float32.
+#pragma once
+#include "common.cuh"
+
+namespace rb {
+
+// row      : shared memory, k floats; overwritten by the residual when terms > 1
+// xq       : global int8, term t written at xq + t*kpad, zero padded to kpad
+// sx, xsum : global, one entry per term
+// scratch  : shared memory, 33 floats
+// All threads of the block must call; blockDim.x is a multiple of 32.
+__device__ __forceinline__ void quantize_row_from_smem(float* row, int k, int kpad, int terms,
+                                                       int8_t* __restrict__ xq, float* __restrict__ sx,
+                                                       int32_t* __restrict__ xsum, float* scratch) {
+    for (int t = 0; t < terms; ++t) {
+        float mx = 0.f;
+        for (int i = threadIdx.x; i < k; i += blockDim.x) mx = fmaxf(mx, fabsf(row[i]));
+        mx = block_max(mx, scratch);
+        const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
+        int lsum = 0;
+        for (int i4 = threadIdx.x * 4; i4 < kpad; i4 += blockDim.x * 4) {
+            char4 q4;
+            int8_t* qp = reinterpret_cast<int8_t*>(&q4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = i4 + e;
+                int q = 0;
+                if (i < k) {
+                    const float v = row[i];
+                    float r = rintf(__fdiv_rn(v, s));
+                    r = fminf(fmaxf(r, -128.f), 127.f);
+                    q = (int)r;
+                    if (t + 1 < terms) row[i] = __fsub_rn(v, __fmul_rn(r, s));
+                }
+                qp[e] = (int8_t)q;
+                lsum += q;
+            }
+            *reinterpret_cast<char4*>(xq + (size_t)t * kpad + i4) = q4;
+        }
+        lsum = block_sum_i(lsum, reinterpret_cast<int*>(scratch));
+        if (threadIdx.x == 0) {
+            sx[t] = s;
+            xsum[t] = lsum;
+        }
+    }
+}
+
+}  // namespace rb

@@ -1,0 +1,103 @@
+"""ctypes binding of librotor_b200.so (declared in include/rotor_b200.h).
+
+The library is the only compute path.  If it is missing or a call fails this
+module raises; nothing falls back to NumPy.  torch tensors serve as device
+buffers: every wrapper takes tensors (or raw pointers) and passes
+``tensor.data_ptr()`` through the C ABI together with the current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librotor_b200.so")
+
+OK = 0
+VARIANT_AUTO, VARIANT_DP4A, VARIANT_MMA = 0, 1, 2
+
+
+class RotorB200Error(RuntimeError):
+    pass
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise RotorB200Error(
+            f"{LIB_PATH} not found: build it with `make -C rotor-rag_b200/csrc` "
+            "(or __graft_entry__.build()); there is no CPU fallback")
+    return C.CDLL(LIB_PATH)
+
+
+lib = _load()
+
+_p, _sz, _i, _f = C.c_void_p, C.c_size_t, C.c_int, C.c_float
+
+_SIGNATURES = {
+    "rotor_b200_version": (_i, []),
+    "rotor_b200_status_string": (C.c_char_p, [_i]),
+    "rotor_b200_device_status": (_i, []),
+    "rotor_b200_encode": (_i, [_p, _sz, _p, _p, _p]),
+    "rotor_b200_decode": (_i, [_p, _p, _sz, _p, _p]),
+    "rotor_b200_pack": (_i, [_p, _p, _sz, _p, _p]),
+    "rotor_b200_unpack": (_i, [_p, _sz, _p, _p, _p]),
+    "rotor_b200_packed_to_planes": (_i, [_p, _sz, _sz, _p, _p, _p]),
+    "rotor_b200_planes_to_int8": (_i, [_p, _p, _sz, _sz, _p, _p]),
+    "bitnet_to_rotor": (None, [_p, _sz, _sz, _p, _p]),
+    "rotor_unpack_weights": (None, [_p, _p, _sz, _sz, _p]),
+    "rotor_b200_tiles_bytes": (_sz, [_sz, _sz]),
+    "rotor_b200_in_padded": (_sz, [_sz]),
+    "rotor_b200_out_padded": (_sz, [_sz]),
+    "rotor_b200_packed_to_tiles": (_i, [_p, _sz, _sz, _p, _p]),
+    "rotor_b200_int8_to_tiles": (_i, [_p, _sz, _sz, _p, _p]),
+    "rotor_b200_tiles_to_int8": (_i, [_p, _sz, _sz, _p, _p]),
+    "rotor_b200_quantize_rows": (_i, [_p, _sz, _sz, _i, _p, _p, _p, _p]),
+    "rotor_b200_bitlinear_acc": (_i, [_p, _sz, _sz, _p, _p, _sz, _p, _i, _p]),
+    "rotor_b200_bitlinear_dequant": (_i, [_p, _p, _sz, _i, _sz, _f, _p, _p, _p]),
+    "rotor_b200_bitlinear_workspace_bytes": (_sz, [_sz, _sz, _sz, _i]),
+    "rotor_b200_bitlinear_forward": (_i, [_p, _sz, _sz, _p, _sz, _i, _f, _p, _p, _p, _sz, _i, _p]),
+    "rotor_b200_ternary_matmul_host": (_i, [_p, _p, _p, _sz, _sz, _i, _p]),
+}
+
+
+def _declare(signatures):
+    for name, (res, args) in signatures.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library out of step
+        fn.restype = res
+        fn.argtypes = args
+
+
+_declare(_SIGNATURES)
+
+
+def check(status: int, what: str = "librotor_b200 call"):
+    if status != OK:
+        raise RotorB200Error(f"{what}: {lib.rotor_b200_status_string(status).decode()} (status {status})")
+
+
+def device_status():
+    """Raise if a bounded device-side wait gave up since the last check."""
+    check(lib.rotor_b200_device_status(), "device status")
+
+
+def ptr(t):
+    """Device (or host) address of a torch tensor / numpy array / int / None."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    if hasattr(t, "data_ptr"):
+        return t.data_ptr()
+    return t.ctypes.data
+
+
+def stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_cuda():
+    import torch
+    if not torch.cuda.is_available():
+        raise RotorB200Error("no CUDA device: the rotor_b200 path runs on a B200 only (no CPU fallback)")
+    return torch
