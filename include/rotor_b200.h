@@ -139,6 +139,109 @@ int rotor_b200_ternary_matmul_host(const void* tiles, const float* scales_host,
                                    const float* x_host, size_t in, size_t out, int terms,
                                    float* y_host);
 
+/* ---------------------------------------------------------------- transformer glue (a6)
+ * RMSNorm.forward, src/rotor/transformer.py:24-36: y = x / sqrt(mean(x^2) + eps) * weight,
+ * x and y float32 [rows][n]. */
+int rotor_b200_rmsnorm(const float* x, size_t rows, size_t n, const float* weight, float eps,
+                       float* y, void* stream);
+
+/* ---------------------------------------------------------------- whole model (a7-a12)
+ * Semantics switches.  The defaults in the comments are what the reference code does when
+ * run; the alternatives are the published BitNet-b1.58 description. */
+enum {
+    ROTOR_B200_FFN_SILU_CLIP20 = 0, /* gate * silu(clip(up,-20,20)), src/rotor/transformer.py:328-351 */
+    ROTOR_B200_FFN_RELU2 = 1        /* relu(gate)^2 * up */
+};
+enum {
+    ROTOR_B200_LOGITS_NONE = 0,
+    ROTOR_B200_LOGITS_LAST = 1,     /* last position of each sequence: float32 [batch][vocab] */
+    ROTOR_B200_LOGITS_ALL = 2       /* every position, as the reference computes (bitnet_model.py:235) */
+};
+
+typedef struct rotor_b200_model_config {
+    int32_t vocab_size, d_model, n_layers, n_heads, n_kv_heads, d_ff; /* src/rotor/bitnet_model.py:56-61 */
+    int32_t act_terms;    /* int8 activation terms per BitLinear input: 1 = per-token absmax int8,
+                             3 = float32-faithful (matches the reference's float path) */
+    int32_t ffn_act;      /* ROTOR_B200_FFN_* */
+    int32_t causal;       /* 0 = no mask (the reference never passes one, bitnet_model.py:226) */
+    float rope_theta;     /* 0 = no positional encoding (reference); > 0 = rotary, half-split pairs */
+    float eps;            /* RMSNorm epsilon (reference 1e-6, transformer.py:20) */
+    int32_t max_batch;    /* sequences the KV cache holds */
+    int32_t max_seq;      /* positions per sequence the KV cache holds */
+    int32_t max_rows;     /* most token rows (batch*seq) in one forward call */
+    int32_t gemv_variant; /* ROTOR_B200_VARIANT_* */
+} rotor_b200_model_config;
+
+/* Device pointers of one transformer block.  qkv_tiles holds the tiles of q, k and v one
+ * after the other (their row counts are multiples of 16, so this is the tile layout of the
+ * stacked matrix); gate_up_tiles likewise.  Scales are the per-tensor weight scales
+ * (src/rotor/transformer.py:87).  Caches are float32 [max_batch][n_kv_heads][max_seq][head_dim]. */
+typedef struct rotor_b200_layer_weights {
+    const void* qkv_tiles;
+    const void* o_tiles;
+    const void* gate_up_tiles;
+    const void* down_tiles;
+    float q_scale, k_scale, v_scale, o_scale, gate_scale, up_scale, down_scale;
+    const float* input_norm;
+    const float* post_attn_norm;
+    const float* attn_sub_norm;
+    const float* ffn_sub_norm;
+    float* k_cache;
+    float* v_cache;
+} rotor_b200_layer_weights;
+
+/* BitNetModel (src/rotor/bitnet_model.py:41-90).  `layers` is a HOST array of n_layers
+ * entries (copied); embed_bf16 is the device bf16 table [vocab][d_model] used for both the
+ * embedding gather and the tied LM head; final_norm device float32 [d_model].  workspace is
+ * device memory of rotor_b200_model_workspace_bytes(cfg) bytes, 256-byte aligned, owned by
+ * the caller for the lifetime of the handle. */
+size_t rotor_b200_model_workspace_bytes(const rotor_b200_model_config* cfg);
+int rotor_b200_model_create(const rotor_b200_model_config* cfg, const rotor_b200_layer_weights* layers,
+                            const void* embed_bf16, const float* final_norm, void* workspace,
+                            size_t workspace_bytes, void** handle);
+void rotor_b200_model_destroy(void* handle);
+
+/* BitNetModel.forward (src/rotor/bitnet_model.py:190-244) over ids int64 [batch][seq] with
+ * past_len positions already cached; the new K/V are appended to the caches.  logits
+ * (float32, shape by logits_mode) and next_ids (int64 [batch], greedy pick of the last
+ * position, generation.py:42) are optional outputs. */
+int rotor_b200_model_forward(void* handle, const int64_t* ids, int batch, int seq, int past_len,
+                             int logits_mode, float* logits, int64_t* next_ids, void* stream);
+
+/* Device-resident greedy generation, the cached loop of TextGenerator.generate
+ * (src/rotor/generation.py:220-279): begin() seeds the loop with the token picked after the
+ * prompt; steps() runs n one-token forwards, each feeding its greedy pick to the next and
+ * logging it on the device (use_graph != 0 replays one captured CUDA graph per step);
+ * read_tokens() copies logged tokens [count][batch] to HOST memory and synchronises. */
+int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int batch, int past_len, void* stream);
+int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void* stream);
+int rotor_b200_model_read_tokens(void* handle, int first_step, int count, int64_t* tokens_host, void* stream);
+int rotor_b200_model_position(void* handle);
+
+/* Blocks [layer_begin, layer_end) of the model on caller-provided hidden rows (float32
+ * [batch*seq][d_model]).  apply_final_norm != 0 applies the model's final norm, as
+ * BitNetModel.forward(return_logits=False) does (src/rotor/bitnet_model.py:231-243);
+ * 0 returns the raw residual stream (TransformerBlock.forward, src/rotor/transformer.py:383-413). */
+int rotor_b200_model_forward_hidden(void* handle, const float* hidden_in, int batch, int seq, int past_len,
+                                    int layer_begin, int layer_end, int apply_final_norm,
+                                    float* hidden_out, void* stream);
+
+/* ---------------------------------------------------------------- stand-alone block halves
+ * GatedFFN.forward (src/rotor/transformer.py:320-341): x float32 [rows][d_model] ->
+ * y float32 [rows][d_model]; pre_norm != NULL applies RMSNorm(pre_norm) to x first.
+ * MultiHeadAttention.forward (src/rotor/transformer.py:206-292): x float32
+ * [batch*seq][d_model] -> y, output projection and sub-norm included; appends K/V to the
+ * layer's caches at past_len.  Both read dimensions and switches from cfg and pointers from
+ * layer (only the members of their half need to be set) and need
+ * rotor_b200_block_workspace_bytes(...) bytes of 256-byte aligned device workspace. */
+size_t rotor_b200_block_workspace_bytes(int d_model, int n_heads, int n_kv_heads, int d_ff, int terms, int rows);
+int rotor_b200_ffn_forward(const rotor_b200_model_config* cfg, const rotor_b200_layer_weights* layer,
+                           const float* pre_norm, const float* x, int rows, float* y,
+                           void* workspace, size_t workspace_bytes, void* stream);
+int rotor_b200_attention_forward(const rotor_b200_model_config* cfg, const rotor_b200_layer_weights* layer,
+                                 const float* x, int batch, int seq, int past_len, float* y,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

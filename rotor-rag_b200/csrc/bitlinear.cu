@@ -13,7 +13,7 @@
 //   MMA  : mma.sync m16n8k32 u8 x s8 -> s32; the tile IS the A fragment, 8 columns
 //          per pass at the cost of one, which also carries the residual terms of the
 //          multi-term activation quantiser.
-#include "common.cuh"
+#include "model.cuh"
 
 namespace rb {
 
@@ -80,6 +80,7 @@ struct AccParams {
     int kt_per_split;
     int ncols;
     int atomic;            // gridDim.y > 1: accumulate with integer atomics into zeroed acc
+    size_t plane_stride;   // != 0: K split s stores its partial sums to acc + s*plane_stride instead
 };
 
 template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(AccParams p) 
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) s += red[w * 128 + threadIdx.x];
             if (blockIdx.y == 0) s -= p.xsum[col];
-            int32_t* dst = p.acc + (size_t)col * p.out + row;
+            int32_t* dst = p.acc + (size_t)blockIdx.y * p.plane_stride + (size_t)col * p.out + row;
             if (p.atomic)
                 atomicAdd(dst, s);
             else
@@ -252,6 +253,78 @@ static int choose_ksplit(int nrt, int nkt, int ncols, int warps) {
     return ks > nkt ? nkt : ks;
 }
 
+static int dispatch_acc(const AccParams& p, int nrt, int ksplit, int variant, cudaStream_t st) {
+    constexpr int WARPS = 4, UMAX = 8;
+    if (variant == ROTOR_B200_VARIANT_MMA) return launch_acc<WARPS, UMAX, true, 1>(p, nrt, ksplit, st);
+    switch (p.ncols) {
+        case 1: return launch_acc<WARPS, UMAX, false, 1>(p, nrt, ksplit, st);
+        case 2: return launch_acc<WARPS, UMAX, false, 2>(p, nrt, ksplit, st);
+        case 3: return launch_acc<WARPS, UMAX, false, 3>(p, nrt, ksplit, st);
+        case 4: return launch_acc<WARPS, UMAX, false, 4>(p, nrt, ksplit, st);
+    }
+    return ROTOR_B200_ERR_ARG;
+}
+
+template <bool USE_MMA, int NCOL>
+static int configure_one() {
+    RB_CUDA(cudaFuncSetAttribute(bitlinear_acc_kernel<4, 8, USE_MMA, NCOL>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    return ROTOR_B200_OK;
+}
+
+// Done once, outside any stream capture: status word and the shared-memory opt-ins.
+int configure_gemv_kernels() {
+    int rc = ensure_status();
+    if (rc) return rc;
+    if ((rc = configure_one<true, 1>())) return rc;
+    if ((rc = configure_one<false, 1>())) return rc;
+    if ((rc = configure_one<false, 2>())) return rc;
+    if ((rc = configure_one<false, 3>())) return rc;
+    return configure_one<false, 4>();
+}
+
+static int pick_variant(int variant, int ncols) {
+    if (variant != ROTOR_B200_VARIANT_AUTO) return variant;
+    return ncols <= 2 ? ROTOR_B200_VARIANT_DP4A : ROTOR_B200_VARIANT_MMA;
+}
+
+GemvPlan plan_gemv(size_t out, size_t in, int ncols) {
+    const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
+    const int per_pass = ncols < 8 ? ncols : 8;
+    int ks = choose_ksplit(nrt, nkt, per_pass, 4);
+    GemvPlan g;
+    g.kt_per_split = (nkt + ks - 1) / ks;
+    g.ksplit = (nkt + g.kt_per_split - 1) / g.kt_per_split;
+    return g;
+}
+
+int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
+                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st) {
+    int rc = ensure_status();
+    if (rc) return rc;
+    const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
+    const size_t kpad = kpad_of(in);
+    variant = pick_variant(variant, ncols);
+    const int chunk = variant == ROTOR_B200_VARIANT_MMA ? 8 : 4;
+    for (int c0 = 0; c0 < ncols; c0 += chunk) {
+        AccParams p;
+        p.tiles = (const uint4*)tiles;
+        p.xq = xq + (size_t)c0 * kpad;
+        p.xsum = xsum + c0;
+        p.acc = acc + (size_t)c0 * out;
+        p.status = g_status;
+        p.out = (int)out;
+        p.nkt = nkt;
+        p.kt_per_split = plan.kt_per_split;
+        p.ncols = (ncols - c0) < chunk ? (ncols - c0) : chunk;
+        p.atomic = 0;
+        p.plane_stride = plane_stride;
+        rc = dispatch_acc(p, nrt, plan.ksplit, variant, st);
+        if (rc) return rc;
+    }
+    return ROTOR_B200_OK;
+}
+
 }  // namespace rb
 
 using namespace rb;
@@ -263,18 +336,17 @@ int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int
     RB_REQUIRE(tiles && xq && xsum && acc && out > 0 && in > 0 && ncols > 0);
     RB_REQUIRE(out < (1u << 30) && in < (1u << 30));
     RB_REQUIRE(((uintptr_t)tiles & 15) == 0 && ((uintptr_t)xq & 15) == 0);
-    if (variant == ROTOR_B200_VARIANT_AUTO) variant = ROTOR_B200_VARIANT_MMA;
-    RB_REQUIRE(variant == ROTOR_B200_VARIANT_DP4A || variant == ROTOR_B200_VARIANT_MMA);
+    RB_REQUIRE(variant >= ROTOR_B200_VARIANT_AUTO && variant <= ROTOR_B200_VARIANT_MMA);
     int rc = ensure_status();
     if (rc) return rc;
     cudaStream_t st = as_stream(stream);
     const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
     const size_t kpad = kpad_of(in);
+    variant = pick_variant(variant, (int)(ncols < 8 ? ncols : 8));
     const size_t chunk = variant == ROTOR_B200_VARIANT_MMA ? 8 : 4;
-    constexpr int WARPS = 4, UMAX = 8;
     for (size_t c0 = 0; c0 < ncols; c0 += chunk) {
         const int nc = (int)((ncols - c0) < chunk ? (ncols - c0) : chunk);
-        const int ksplit = choose_ksplit(nrt, nkt, nc, WARPS);
+        const int ksplit = choose_ksplit(nrt, nkt, nc, 4);
         AccParams p;
         p.tiles = (const uint4*)tiles;
         p.xq = xq + c0 * kpad;
@@ -285,19 +357,11 @@ int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int
         p.nkt = nkt;
         p.kt_per_split = (nkt + ksplit - 1) / ksplit;
         p.ncols = nc;
-        p.atomic = ksplit > 1;
         const int ksplit_eff = (nkt + p.kt_per_split - 1) / p.kt_per_split;
+        p.atomic = ksplit_eff > 1;
+        p.plane_stride = 0;
         if (p.atomic) RB_CUDA(cudaMemsetAsync(p.acc, 0, (size_t)nc * out * sizeof(int32_t), st));
-        if (variant == ROTOR_B200_VARIANT_MMA)
-            rc = launch_acc<WARPS, UMAX, true, 8>(p, nrt, ksplit_eff, st);
-        else if (nc == 1)
-            rc = launch_acc<WARPS, UMAX, false, 1>(p, nrt, ksplit_eff, st);
-        else if (nc == 2)
-            rc = launch_acc<WARPS, UMAX, false, 2>(p, nrt, ksplit_eff, st);
-        else if (nc == 3)
-            rc = launch_acc<WARPS, UMAX, false, 3>(p, nrt, ksplit_eff, st);
-        else
-            rc = launch_acc<WARPS, UMAX, false, 4>(p, nrt, ksplit_eff, st);
+        rc = dispatch_acc(p, nrt, ksplit_eff, variant, st);
         if (rc) return rc;
     }
     return ROTOR_B200_OK;

@@ -1,0 +1,200 @@
+// Tied LM head: logits[m][v] = sum_k x[m][k] * embed[v][k] with a bf16 table
+// (np.dot(hidden, embed_tokens.T), src/rotor/bitnet_model.py:231-235), fused with the
+// greedy pick (int(np.argmax(logits)), lowest index on ties, src/rotor/generation.py:42).
+//
+// HBM-bound on the table (vocab * d * 2 bytes per pass).  Each warp owns rows of the
+// table four at a time; a lane reads 8 bf16 (one 128-bit load) per row per 256 columns
+// and keeps the activation slice it needs in shared memory.  Up to LM_ROWS token rows
+// share one pass over the table.
+#include "model.cuh"
+
+namespace rb {
+
+constexpr int LM_ROWS = 4;       // token rows per pass over the table
+constexpr int LM_VROWS = 4;      // table rows in flight per warp
+constexpr int LM_WARPS = 8;
+constexpr int LM_PARTS = 148 * 4;  // CTAs = argmax partials per token row
+
+int lmhead_parts() { return LM_PARTS; }
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <int NROWS>
+__global__ void __launch_bounds__(LM_WARPS * 32) lmhead_kernel(LmHeadParams p, int row0) {
+    extern __shared__ __align__(16) float xs[];  // [NROWS][d]
+    const int d = p.d;
+    for (int i = threadIdx.x; i < NROWS * d; i += blockDim.x) xs[i] = p.x[(size_t)row0 * d + i];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gw = blockIdx.x * LM_WARPS + warp, nw = gridDim.x * LM_WARPS;
+    const int nchunk = d / 256;  // d is a multiple of 256 (checked on the host)
+
+    float best[NROWS];
+    int besti[NROWS];
+#pragma unroll
+    for (int r = 0; r < NROWS; ++r) {
+        best[r] = -INFINITY;
+        besti[r] = 0x7fffffff;
+    }
+    for (int v0 = gw * LM_VROWS; v0 < p.vocab; v0 += nw * LM_VROWS) {
+        float acc[LM_VROWS][NROWS];
+#pragma unroll
+        for (int j = 0; j < LM_VROWS; ++j)
+#pragma unroll
+            for (int r = 0; r < NROWS; ++r) acc[j][r] = 0.f;
+        for (int c = 0; c < nchunk; ++c) {
+            const int k = c * 256 + lane * 8;
+            uint4 wv[LM_VROWS];
+#pragma unroll
+            for (int j = 0; j < LM_VROWS; ++j) {
+                const int v = min(v0 + j, p.vocab - 1);
+                wv[j] = ld_stream_v4(reinterpret_cast<const uint4*>(p.embed + (size_t)v * d + k));
+            }
+            float xf[NROWS][8];
+#pragma unroll
+            for (int r = 0; r < NROWS; ++r) {
+                const float4 a = *reinterpret_cast<const float4*>(xs + r * d + k);
+                const float4 b = *reinterpret_cast<const float4*>(xs + r * d + k + 4);
+                xf[r][0] = a.x; xf[r][1] = a.y; xf[r][2] = a.z; xf[r][3] = a.w;
+                xf[r][4] = b.x; xf[r][5] = b.y; xf[r][6] = b.z; xf[r][7] = b.w;
+            }
+#pragma unroll
+            for (int j = 0; j < LM_VROWS; ++j) {
+                float wf[8];
+                bf16x8_to_float(wv[j], wf);
+#pragma unroll
+                for (int r = 0; r < NROWS; ++r)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[j][r] += wf[e] * xf[r][e];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < LM_VROWS; ++j)
+#pragma unroll
+            for (int r = 0; r < NROWS; ++r) {
+                const float s = warp_sum(acc[j][r]);
+                const int v = v0 + j;
+                if (v < p.vocab) {
+                    if (p.logits && lane == 0) p.logits[(size_t)(row0 + r) * p.vocab + v] = s;
+                    if (s > best[r] || (s == best[r] && v < besti[r])) {
+                        best[r] = s;
+                        besti[r] = v;
+                    }
+                }
+            }
+    }
+    // CTA-level pick, lowest index on ties
+    __shared__ float sb[LM_WARPS][NROWS];
+    __shared__ int si[LM_WARPS][NROWS];
+    if (lane == 0)
+#pragma unroll
+        for (int r = 0; r < NROWS; ++r) {
+            sb[warp][r] = best[r];
+            si[warp][r] = besti[r];
+        }
+    __syncthreads();
+    if (threadIdx.x < NROWS) {
+        const int r = threadIdx.x;
+        float bv = sb[0][r];
+        int bi = si[0][r];
+        for (int w = 1; w < LM_WARPS; ++w)
+            if (sb[w][r] > bv || (sb[w][r] == bv && si[w][r] < bi)) {
+                bv = sb[w][r];
+                bi = si[w][r];
+            }
+        p.part_val[(size_t)(row0 + r) * p.nparts + blockIdx.x] = bv;
+        p.part_idx[(size_t)(row0 + r) * p.nparts + blockIdx.x] = bi;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int nparts,
+                                    long long* __restrict__ out) {
+    const int m = blockIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < nparts; i += blockDim.x) {
+        const float v = part_val[(size_t)m * nparts + i];
+        const int id = part_idx[(size_t)m * nparts + i];
+        if (v > bv || (v == bv && id < bi)) {
+            bv = v;
+            bi = id;
+        }
+    }
+    __shared__ float sv[32];
+    __shared__ int sidx[32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = bv;
+        sidx[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (sv[w] > bv || (sv[w] == bv && sidx[w] < bi)) {
+                bv = sv[w];
+                bi = sidx[w];
+            }
+        out[m] = bi;
+    }
+}
+
+template <int NROWS>
+static int launch_lm(const LmHeadParams& p, int row0, cudaStream_t st) {
+    const size_t smem = (size_t)NROWS * p.d * sizeof(float);
+    if (smem > 48 * 1024) {
+        static bool configured = false;
+        if (!configured) {
+            RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<NROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         200 * 1024));
+            configured = true;
+        }
+        if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
+    }
+    lmhead_kernel<NROWS><<<LM_PARTS, LM_WARPS * 32, smem, st>>>(p, row0);
+    return launch_status();
+}
+
+int configure_lmhead() {
+    RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    return ROTOR_B200_OK;
+}
+
+int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st) {
+    if (p.d % 256 != 0) return ROTOR_B200_ERR_SHAPE;
+    int rc = ROTOR_B200_OK;
+    for (int r0 = 0; r0 < rows && !rc; r0 += LM_ROWS) {
+        const int n = rows - r0 < LM_ROWS ? rows - r0 : LM_ROWS;
+        switch (n) {
+            case 1: rc = launch_lm<1>(p, r0, st); break;
+            case 2: rc = launch_lm<2>(p, r0, st); break;
+            case 3: rc = launch_lm<3>(p, r0, st); break;
+            default: rc = launch_lm<4>(p, r0, st); break;
+        }
+    }
+    if (rc) return rc;
+    if (p.argmax_out) {
+        argmax_final_kernel<<<rows, 256, 0, st>>>(p.part_val, p.part_idx, p.nparts, p.argmax_out);
+        rc = launch_status();
+    }
+    return rc;
+}
+
+}  // namespace rb

@@ -1,0 +1,636 @@
+// Model driver: sequences the decode-path kernels for BitNetModel.forward
+// (src/rotor/bitnet_model.py:190-244) and the cached generation loop of
+// TextGenerator (src/rotor/generation.py:179-279) on one GPU.  All buffers are
+// caller-owned device memory; the handle only records pointers and plans.
+//
+// Per block (src/rotor/transformer.py:383-413) the launch sequence is
+//   q/k/v product (stacked)  -> qkv_finish (dequant, rotary, cache append) -> attention
+//   -> quantise -> o product -> [sub-norm, residual, pre-norm, quantise]
+//   -> gate/up product (stacked) -> [gating, sub-norm, quantise] -> down product
+//   -> [residual, next pre-norm, quantise]
+// and a generation step ends with the tied LM head fused with the greedy pick.  A
+// generation step reads the position and the input token from device memory, so one
+// captured CUDA graph replays for every step.
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "model.cuh"
+
+namespace rb {
+
+static inline size_t al256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Scratch buffers and dimensions one block needs; carved from caller-owned device memory.
+struct Ctx {
+    int d, ff, n_heads, n_kv_heads, head_dim, dq, dkv;
+    int terms, ffn_act, causal, variant, max_seq;
+    float rope_theta, eps;
+    size_t kmax;  // widest padded BitLinear input
+    float* h;     // residual stream [rows][d]
+    float* hn;    // final-normed rows
+    float* qbuf;
+    float* attn;
+    int8_t* xq;
+    float* sx[2];
+    int32_t* xsum[2];
+    int32_t* accA;  // q/k/v and gate/up accumulators
+    int32_t* accB;  // o and down accumulators
+    int* d_pos;
+};
+
+struct Model {
+    rotor_b200_model_config cfg;
+    rotor_b200_layer_weights* layers;
+    const __nv_bfloat16* embed;
+    const float* final_norm;
+    Ctx c;
+    float* part_val;
+    int* part_idx;
+    long long* cur_ids;
+    long long* tok_log;
+    int* d_step;
+    int max_log;
+    // host mirror of the generation state
+    int pos, step, batch;
+    cudaGraphExec_t graph;
+    int graph_batch;
+};
+
+struct Carve {
+    unsigned char* base;
+    size_t off;
+    template <typename T>
+    T* take(size_t count) {
+        T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+        off += al256(count * sizeof(T));
+        return p;
+    }
+};
+
+static int max_planes(size_t out, size_t in) { return plan_gemv(out, in, 8).ksplit; }
+
+static int derive_ctx(Ctx& c, int d_model, int n_heads, int n_kv_heads, int d_ff, int terms) {
+    if (d_model <= 0 || n_heads <= 0 || n_kv_heads <= 0 || d_ff <= 0) return ROTOR_B200_ERR_ARG;
+    if (terms < 1 || terms > 4) return ROTOR_B200_ERR_ARG;
+    if (d_model % n_heads || n_heads % n_kv_heads) return ROTOR_B200_ERR_SHAPE;
+    c.d = d_model;
+    c.ff = d_ff;
+    c.n_heads = n_heads;
+    c.n_kv_heads = n_kv_heads;
+    c.terms = terms;
+    c.head_dim = d_model / n_heads;  // head_dim = d_model // n_heads, src/rotor/transformer.py:192
+    if (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128) return ROTOR_B200_ERR_SHAPE;
+    c.dq = n_heads * c.head_dim;
+    c.dkv = n_kv_heads * c.head_dim;
+    if (c.dq % 16 || c.dkv % 16 || d_ff % 16) return ROTOR_B200_ERR_SHAPE;  // stacked products need whole row tiles
+    c.kmax = kpad_of(d_model);
+    if (kpad_of(c.dq) > c.kmax) c.kmax = kpad_of(c.dq);
+    if (kpad_of(d_ff) > c.kmax) c.kmax = kpad_of(d_ff);
+    return ROTOR_B200_OK;
+}
+
+static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
+    const size_t cols = rows * c.terms;
+    const size_t d = c.d, ff = c.ff;
+    const size_t qkv_out = c.dq + 2 * (size_t)c.dkv;
+    c.h = cv.take<float>(rows * d);
+    c.hn = cv.take<float>(rows * d);
+    c.qbuf = cv.take<float>(rows * c.dq);
+    c.attn = cv.take<float>(rows * c.dq);
+    c.xq = cv.take<int8_t>(cols * c.kmax);
+    for (int i = 0; i < 2; ++i) {
+        c.sx[i] = cv.take<float>(cols);
+        c.xsum[i] = cv.take<int32_t>(cols);
+    }
+    const size_t pa1 = (size_t)max_planes(qkv_out, d) * cols * qkv_out;
+    const size_t pa2 = (size_t)max_planes(2 * ff, d) * cols * 2 * ff;
+    const size_t pb1 = (size_t)max_planes(d, c.dq) * cols * d;
+    const size_t pb2 = (size_t)max_planes(d, ff) * cols * d;
+    c.accA = cv.take<int32_t>(pa1 > pa2 ? pa1 : pa2);
+    c.accB = cv.take<int32_t>(pb1 > pb2 ? pb1 : pb2);
+    c.d_pos = cv.take<int>(1);
+}
+
+static void carve(Model& m, unsigned char* base, size_t* total) {
+    const rotor_b200_model_config& c = m.cfg;
+    const size_t rows = (size_t)c.max_rows;
+    Carve cv{base, 0};
+    carve_ctx(m.c, cv, rows);
+    m.part_val = cv.take<float>(rows * lmhead_parts());
+    m.part_idx = cv.take<int>(rows * lmhead_parts());
+    m.cur_ids = cv.take<long long>(c.max_batch);
+    m.max_log = c.max_seq;
+    m.tok_log = cv.take<long long>((size_t)m.max_log * c.max_batch);
+    m.d_step = cv.take<int>(1);
+    *total = cv.off;
+}
+
+static int derive(Model& m) {
+    const rotor_b200_model_config& c = m.cfg;
+    if (c.vocab_size <= 0 || c.n_layers <= 0 || c.max_batch <= 0 || c.max_seq <= 0 || c.max_rows <= 0)
+        return ROTOR_B200_ERR_ARG;
+    int rc = derive_ctx(m.c, c.d_model, c.n_heads, c.n_kv_heads, c.d_ff, c.act_terms);
+    if (rc) return rc;
+    if (c.d_model % 256) return ROTOR_B200_ERR_SHAPE;  // LM head reads 256 columns per warp step
+    m.c.ffn_act = c.ffn_act;
+    m.c.causal = c.causal;
+    m.c.variant = c.gemv_variant;
+    m.c.max_seq = c.max_seq;
+    m.c.rope_theta = c.rope_theta;
+    m.c.eps = c.eps;
+    return ROTOR_B200_OK;
+}
+
+__global__ void set_int_kernel(int* p, int v) { *p = v; }
+
+__global__ void begin_kernel(long long* cur, const long long* first, int batch, int* pos, int past, int* step) {
+    if (threadIdx.x < batch) cur[threadIdx.x] = first[threadIdx.x];
+    if (threadIdx.x == 0) {
+        *pos = past;
+        *step = 0;
+    }
+}
+
+// After a generation step: log the picked tokens and move the position on.
+__global__ void advance_kernel(const long long* cur, long long* log, int batch, int max_log, int* pos, int* step) {
+    const int s = *step;
+    if (threadIdx.x < batch && s < max_log) log[(size_t)s * batch + threadIdx.x] = cur[threadIdx.x];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        *pos += 1;
+        *step = s + 1;
+    }
+}
+
+#define RB_TRY(expr)              \
+    do {                          \
+        int rc_ = (expr);         \
+        if (rc_) return rc_;      \
+    } while (0)
+
+static int gemv(Ctx& c, const void* tiles, size_t out, size_t in, int ncols, int xs, int32_t* acc, AccView* view,
+                cudaStream_t st) {
+    GemvPlan plan = plan_gemv(out, in, ncols < 8 ? ncols : 8);
+    const size_t plane_stride = (size_t)ncols * out;
+    RB_TRY(launch_gemv_planes(tiles, out, in, c.xq, c.xsum[xs], ncols, acc, plane_stride, plan, c.variant, st));
+    view->acc = acc;
+    view->plane_stride = plane_stride;
+    view->planes = plan.ksplit;
+    view->out = (int)out;
+    return ROTOR_B200_OK;
+}
+
+static void quant_sink(const Ctx& c, VecStageParams& p, int slot, int n) {
+    p.xq = c.xq;
+    p.sx_out = c.sx[slot];
+    p.xsum_out = c.xsum[slot];
+    p.terms_out = c.terms;
+    p.kpad = (int)kpad_of(n);
+}
+
+// Attention half of a block.  In: quantised pre-normed rows in xq/sx[0]/xsum[0].
+// Out: accumulators of the output projection (view *vo), activation scales in sx[1].
+static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, int seq, AccView* vo,
+                          cudaStream_t st) {
+    const int rows = batch * seq, cols = rows * c.terms;
+    const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
+    AccView va;
+    RB_TRY(gemv(c, L.qkv_tiles, qkv_out, c.d, cols, 0, c.accA, &va, st));
+    QkvFinishParams qf = {};
+    qf.acc = va;
+    qf.sx = c.sx[0];
+    qf.terms = c.terms;
+    qf.sq = L.q_scale;
+    qf.sk = L.k_scale;
+    qf.sv = L.v_scale;
+    qf.n_heads = c.n_heads;
+    qf.n_kv_heads = c.n_kv_heads;
+    qf.head_dim = c.head_dim;
+    qf.seq = seq;
+    qf.past_len = c.d_pos;
+    qf.max_seq = c.max_seq;
+    qf.rope_theta = c.rope_theta;
+    qf.q = c.qbuf;
+    qf.k_cache = L.k_cache;
+    qf.v_cache = L.v_cache;
+    RB_TRY(launch_qkv_finish(qf, rows, st));
+    AttnParams ap = {};
+    ap.q = c.qbuf;
+    ap.k_cache = L.k_cache;
+    ap.v_cache = L.v_cache;
+    ap.out = c.attn;
+    ap.n_heads = c.n_heads;
+    ap.n_kv_heads = c.n_kv_heads;
+    ap.head_dim = c.head_dim;
+    ap.seq = seq;
+    ap.past_len = c.d_pos;
+    ap.max_seq = c.max_seq;
+    ap.causal = c.causal;
+    RB_TRY(launch_attention(ap, rows, st));
+    VecStageParams qa = {};
+    qa.mode = VS_PLAIN;
+    qa.n = c.dq;
+    qa.src = c.attn;
+    qa.eps = c.eps;
+    quant_sink(c, qa, 1, c.dq);
+    RB_TRY(launch_vec_stage(qa, rows, st));
+    return gemv(c, L.o_tiles, c.d, c.dq, cols, 1, c.accB, vo, st);
+}
+
+// FFN half of a block.  In: quantised pre-normed rows in xq/sx[0]/xsum[0].
+// Out: accumulators of the down projection (view *vd), activation scales in sx[1].
+static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView* vd, cudaStream_t st) {
+    const int cols = rows * c.terms;
+    AccView va;
+    RB_TRY(gemv(c, L.gate_up_tiles, 2 * (size_t)c.ff, c.d, cols, 0, c.accA, &va, st));
+    VecStageParams fp = {};
+    fp.mode = VS_FFN;
+    fp.n = c.ff;
+    fp.acc = va;
+    fp.sx_in = c.sx[0];
+    fp.terms = c.terms;
+    fp.wscale0 = L.gate_scale;
+    fp.wscale1 = L.up_scale;
+    fp.ffn_act = c.ffn_act;
+    fp.norm1 = L.ffn_sub_norm;
+    fp.eps = c.eps;
+    quant_sink(c, fp, 1, c.ff);
+    RB_TRY(launch_vec_stage(fp, rows, st));
+    return gemv(c, L.down_tiles, c.d, c.ff, cols, 1, c.accB, vd, st);
+}
+
+// Blocks [l0, l1) on the residual stream c.h, whose pre-normed quantised copy is already in
+// xq/sx[0].  `next_norm` is the norm weight that follows block l1-1 (the next block's
+// pre-norm or the model's final norm); with `to_float` the normed rows go to c.hn instead
+// of the quantiser.
+static int run_blocks(Ctx& c, const rotor_b200_layer_weights* layers, int l0, int l1, const float* next_norm,
+                      bool to_float, int batch, int seq, cudaStream_t st) {
+    const int rows = batch * seq;
+    for (int l = l0; l < l1; ++l) {
+        const rotor_b200_layer_weights& L = layers[l];
+        AccView vo, vd;
+        RB_TRY(attention_part(c, L, batch, seq, &vo, st));
+        VecStageParams op = {};
+        op.mode = VS_OPROJ;
+        op.n = c.d;
+        op.acc = vo;
+        op.sx_in = c.sx[1];
+        op.terms = c.terms;
+        op.wscale0 = L.o_scale;
+        op.norm0 = L.attn_sub_norm;
+        op.h = c.h;
+        op.norm1 = L.post_attn_norm;
+        op.eps = c.eps;
+        quant_sink(c, op, 0, c.d);
+        RB_TRY(launch_vec_stage(op, rows, st));
+        RB_TRY(ffn_part(c, L, rows, &vd, st));
+        VecStageParams dn = {};
+        dn.mode = VS_DOWN;
+        dn.n = c.d;
+        dn.acc = vd;
+        dn.sx_in = c.sx[1];
+        dn.terms = c.terms;
+        dn.wscale0 = L.down_scale;
+        dn.h = c.h;
+        dn.eps = c.eps;
+        const bool last = l + 1 == l1;
+        dn.norm1 = last ? next_norm : layers[l + 1].input_norm;
+        if (last && to_float)
+            dn.y_out = c.hn;
+        else
+            quant_sink(c, dn, 0, c.d);
+        RB_TRY(launch_vec_stage(dn, rows, st));
+    }
+    return ROTOR_B200_OK;
+}
+
+// ids: device [batch*seq]; the position is read from c.d_pos by the kernels.
+static int run_layers(Model& m, const long long* ids, int batch, int seq, int logits_mode, float* logits,
+                      long long* next_ids, cudaStream_t st) {
+    Ctx& c = m.c;
+    const int rows = batch * seq, d = c.d;
+    VecStageParams e = {};
+    e.mode = VS_EMBED;
+    e.n = d;
+    e.ids = ids;
+    e.embed = m.embed;
+    e.h = c.h;
+    e.norm1 = m.layers[0].input_norm;
+    e.eps = c.eps;
+    quant_sink(c, e, 0, d);
+    RB_TRY(launch_vec_stage(e, rows, st));
+    RB_TRY(run_blocks(c, m.layers, 0, m.cfg.n_layers, m.final_norm, true, batch, seq, st));
+    if (logits_mode == ROTOR_B200_LOGITS_NONE && !next_ids) return ROTOR_B200_OK;
+
+    // LM head over the last position of each sequence, or over every position
+    const bool all = logits_mode == ROTOR_B200_LOGITS_ALL;
+    const float* x = c.hn;
+    int lm_rows = rows;
+    if (!all && seq > 1) {
+        // compact the last rows: hn[b*seq + seq-1] -> qbuf[b] (qbuf is free by now)
+        for (int b = 0; b < batch; ++b)
+            RB_CUDA(cudaMemcpyAsync(c.qbuf + (size_t)b * d, c.hn + ((size_t)b * seq + seq - 1) * d, d * sizeof(float),
+                                    cudaMemcpyDeviceToDevice, st));
+        x = c.qbuf;
+        lm_rows = batch;
+    }
+    LmHeadParams lp = {};
+    lp.embed = m.embed;
+    lp.x = x;
+    lp.vocab = m.cfg.vocab_size;
+    lp.d = d;
+    lp.logits = logits_mode == ROTOR_B200_LOGITS_NONE ? nullptr : logits;
+    lp.part_val = m.part_val;
+    lp.part_idx = m.part_idx;
+    lp.argmax_out = (all && seq > 1) ? nullptr : next_ids;
+    lp.nparts = lmhead_parts();
+    return launch_lmhead(lp, lm_rows, st);
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" {
+
+size_t rotor_b200_model_workspace_bytes(const rotor_b200_model_config* cfg) {
+    if (!cfg) return 0;
+    Model m;
+    memset(&m, 0, sizeof(m));
+    m.cfg = *cfg;
+    if (derive(m)) return 0;
+    size_t total = 0;
+    carve(m, nullptr, &total);
+    return total;
+}
+
+int rotor_b200_model_create(const rotor_b200_model_config* cfg, const rotor_b200_layer_weights* layers,
+                            const void* embed_bf16, const float* final_norm, void* workspace,
+                            size_t workspace_bytes, void** handle) {
+    RB_REQUIRE(cfg && layers && embed_bf16 && final_norm && workspace && handle);
+    RB_REQUIRE(((uintptr_t)workspace & 255) == 0);
+    Model* m = new (std::nothrow) Model;
+    if (!m) return ROTOR_B200_ERR_ARG;
+    memset(m, 0, sizeof(*m));
+    m->cfg = *cfg;
+    int rc = derive(*m);
+    if (rc) {
+        delete m;
+        return rc;
+    }
+    size_t total = 0;
+    carve(*m, (unsigned char*)workspace, &total);
+    if (total > workspace_bytes) {
+        delete m;
+        return ROTOR_B200_ERR_WORKSPACE;
+    }
+    m->layers = (rotor_b200_layer_weights*)malloc(sizeof(rotor_b200_layer_weights) * cfg->n_layers);
+    memcpy(m->layers, layers, sizeof(rotor_b200_layer_weights) * cfg->n_layers);
+    for (int l = 0; l < cfg->n_layers; ++l) {
+        const rotor_b200_layer_weights& L = m->layers[l];
+        if (!L.qkv_tiles || !L.o_tiles || !L.gate_up_tiles || !L.down_tiles || !L.input_norm ||
+            !L.post_attn_norm || !L.attn_sub_norm || !L.ffn_sub_norm || !L.k_cache || !L.v_cache) {
+            free(m->layers);
+            delete m;
+            return ROTOR_B200_ERR_ARG;
+        }
+    }
+    m->embed = (const __nv_bfloat16*)embed_bf16;
+    m->final_norm = final_norm;
+    // one-time kernel configuration happens here so that nothing but launches runs inside a capture
+    if ((rc = configure_gemv_kernels()) || (rc = configure_vec_stage()) || (rc = configure_lmhead())) {
+        free(m->layers);
+        delete m;
+        return rc;
+    }
+    *handle = m;
+    return ROTOR_B200_OK;
+}
+
+void rotor_b200_model_destroy(void* handle) {
+    Model* m = (Model*)handle;
+    if (!m) return;
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    free(m->layers);
+    delete m;
+}
+
+int rotor_b200_model_forward(void* handle, const int64_t* ids, int batch, int seq, int past_len, int logits_mode,
+                             float* logits, int64_t* next_ids, void* stream) {
+    Model* m = (Model*)handle;
+    RB_REQUIRE(m && ids && batch > 0 && seq > 0 && past_len >= 0);
+    RB_REQUIRE(batch <= m->cfg.max_batch && (long)batch * seq <= m->cfg.max_rows);
+    RB_REQUIRE(past_len + seq <= m->cfg.max_seq);
+    RB_REQUIRE(logits_mode >= ROTOR_B200_LOGITS_NONE && logits_mode <= ROTOR_B200_LOGITS_ALL);
+    RB_REQUIRE(logits_mode == ROTOR_B200_LOGITS_NONE || logits);
+    cudaStream_t st = as_stream(stream);
+    set_int_kernel<<<1, 1, 0, st>>>(m->c.d_pos, past_len);
+    RB_TRY(run_layers(*m, (const long long*)ids, batch, seq, logits_mode, logits, (long long*)next_ids, st));
+    m->pos = past_len + seq;
+    return launch_status();
+}
+
+int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int batch, int past_len, void* stream) {
+    Model* m = (Model*)handle;
+    RB_REQUIRE(m && first_ids && batch > 0 && batch <= m->cfg.max_batch && batch <= 1024);
+    RB_REQUIRE(past_len >= 0 && past_len < m->cfg.max_seq);
+    begin_kernel<<<1, 1024, 0, as_stream(stream)>>>(m->cur_ids, (const long long*)first_ids, batch, m->c.d_pos,
+                                                    past_len, m->d_step);
+    m->pos = past_len;
+    m->step = 0;
+    m->batch = batch;
+    return launch_status();
+}
+
+static int one_step(Model& m, cudaStream_t st) {
+    RB_TRY(run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st));
+    advance_kernel<<<1, 1024, 0, st>>>(m.cur_ids, m.tok_log, m.batch, m.max_log, m.c.d_pos, m.d_step);
+    return launch_status();
+}
+
+int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void* stream) {
+    Model* m = (Model*)handle;
+    RB_REQUIRE(m && nsteps > 0 && m->batch > 0);
+    RB_REQUIRE(m->pos + nsteps <= m->cfg.max_seq && m->step + nsteps <= m->max_log);
+    cudaStream_t st = as_stream(stream);
+    if (!use_graph) {
+        for (int i = 0; i < nsteps; ++i) RB_TRY(one_step(*m, st));
+    } else {
+        if (m->graph && m->graph_batch != m->batch) {
+            cudaGraphExecDestroy(m->graph);
+            m->graph = nullptr;
+        }
+        if (!m->graph) {
+            RB_REQUIRE(st != nullptr);  // the legacy default stream cannot be captured
+            cudaGraph_t g = nullptr;
+            RB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            int rc = one_step(*m, st);
+            cudaError_t e = cudaStreamEndCapture(st, &g);
+            if (rc || e != cudaSuccess) {
+                if (g) cudaGraphDestroy(g);
+                return rc ? rc : ROTOR_B200_ERR_CUDA;
+            }
+            e = cudaGraphInstantiate(&m->graph, g, 0);
+            cudaGraphDestroy(g);
+            if (e != cudaSuccess) return ROTOR_B200_ERR_CUDA;
+            m->graph_batch = m->batch;
+        }
+        for (int i = 0; i < nsteps; ++i) RB_CUDA(cudaGraphLaunch(m->graph, st));
+    }
+    m->pos += nsteps;
+    m->step += nsteps;
+    return ROTOR_B200_OK;
+}
+
+int rotor_b200_model_read_tokens(void* handle, int first_step, int count, int64_t* tokens_host, void* stream) {
+    Model* m = (Model*)handle;
+    RB_REQUIRE(m && tokens_host && first_step >= 0 && count > 0 && first_step + count <= m->step);
+    cudaStream_t st = as_stream(stream);
+    RB_CUDA(cudaMemcpyAsync(tokens_host, m->tok_log + (size_t)first_step * m->batch,
+                            (size_t)count * m->batch * sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    RB_CUDA(cudaStreamSynchronize(st));
+    return ROTOR_B200_OK;
+}
+
+int rotor_b200_model_position(void* handle) {
+    Model* m = (Model*)handle;
+    return m ? m->pos : -1;
+}
+
+/* Runs blocks [layer_begin, layer_end) of the model on caller-provided hidden rows
+ * (float32 [batch*seq][d_model], device).  With apply_final_norm the model's final norm is
+ * applied to the result (BitNetModel.forward(return_logits=False), bitnet_model.py:231-243);
+ * otherwise the raw residual stream is returned (TransformerBlock.forward, transformer.py:383-413). */
+int rotor_b200_model_forward_hidden(void* handle, const float* hidden_in, int batch, int seq, int past_len,
+                                    int layer_begin, int layer_end, int apply_final_norm, float* hidden_out,
+                                    void* stream) {
+    Model* m = (Model*)handle;
+    RB_REQUIRE(m && hidden_in && hidden_out && batch > 0 && seq > 0 && past_len >= 0);
+    RB_REQUIRE(batch <= m->cfg.max_batch && (long)batch * seq <= m->cfg.max_rows);
+    RB_REQUIRE(past_len + seq <= m->cfg.max_seq);
+    RB_REQUIRE(layer_begin >= 0 && layer_begin < layer_end && layer_end <= m->cfg.n_layers);
+    cudaStream_t st = as_stream(stream);
+    Ctx& c = m->c;
+    const int rows = batch * seq;
+    set_int_kernel<<<1, 1, 0, st>>>(c.d_pos, past_len);
+    RB_CUDA(cudaMemcpyAsync(c.h, hidden_in, (size_t)rows * c.d * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    VecStageParams e = {};
+    e.mode = VS_PLAIN;
+    e.n = c.d;
+    e.src = c.h;
+    e.norm1 = m->layers[layer_begin].input_norm;
+    e.eps = c.eps;
+    quant_sink(c, e, 0, c.d);
+    RB_TRY(launch_vec_stage(e, rows, st));
+    const float* next_norm = layer_end < m->cfg.n_layers ? m->layers[layer_end].input_norm : m->final_norm;
+    RB_TRY(run_blocks(c, m->layers, layer_begin, layer_end, next_norm, true, batch, seq, st));
+    RB_CUDA(cudaMemcpyAsync(hidden_out, apply_final_norm ? c.hn : c.h, (size_t)rows * c.d * sizeof(float),
+                            cudaMemcpyDeviceToDevice, st));
+    m->pos = past_len + seq;
+    return launch_status();
+}
+
+/* Workspace for the two stand-alone block halves below. */
+size_t rotor_b200_block_workspace_bytes(int d_model, int n_heads, int n_kv_heads, int d_ff, int terms, int rows) {
+    Ctx c;
+    memset(&c, 0, sizeof(c));
+    if (rows <= 0 || derive_ctx(c, d_model, n_heads, n_kv_heads, d_ff, terms)) return 0;
+    Carve cv{nullptr, 0};
+    carve_ctx(c, cv, (size_t)rows);
+    return cv.off;
+}
+
+static int block_ctx(Ctx& c, const rotor_b200_model_config* cfg, int rows, void* workspace, size_t workspace_bytes) {
+    memset(&c, 0, sizeof(c));
+    int rc = derive_ctx(c, cfg->d_model, cfg->n_heads, cfg->n_kv_heads, cfg->d_ff, cfg->act_terms);
+    if (rc) return rc;
+    c.ffn_act = cfg->ffn_act;
+    c.causal = cfg->causal;
+    c.variant = cfg->gemv_variant;
+    c.max_seq = cfg->max_seq;
+    c.rope_theta = cfg->rope_theta;
+    c.eps = cfg->eps;
+    Carve cv{(unsigned char*)workspace, 0};
+    carve_ctx(c, cv, (size_t)rows);
+    if (cv.off > workspace_bytes) return ROTOR_B200_ERR_WORKSPACE;
+    if ((rc = configure_gemv_kernels()) || (rc = configure_vec_stage())) return rc;
+    return ROTOR_B200_OK;
+}
+
+/* GatedFFN.forward (src/rotor/transformer.py:320-341) on device rows x float32 [rows][d_model]
+ * -> y float32 [rows][d_model]; with pre_norm != NULL an RMSNorm with that weight is applied
+ * to x first (the block's post-attention norm).  Uses from `cfg`: d_model, n_heads,
+ * n_kv_heads, d_ff, act_terms, ffn_act, eps, gemv_variant; from `layer`: gate_up_tiles,
+ * down_tiles, their scales, ffn_sub_norm. */
+int rotor_b200_ffn_forward(const rotor_b200_model_config* cfg, const rotor_b200_layer_weights* layer,
+                           const float* pre_norm, const float* x, int rows, float* y, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+    RB_REQUIRE(cfg && layer && x && y && workspace && rows > 0);
+    RB_REQUIRE(layer->gate_up_tiles && layer->down_tiles && layer->ffn_sub_norm);
+    RB_REQUIRE(((uintptr_t)workspace & 255) == 0);
+    Ctx c;
+    RB_TRY(block_ctx(c, cfg, rows, workspace, workspace_bytes));
+    cudaStream_t st = as_stream(stream);
+    VecStageParams e = {};
+    e.mode = VS_PLAIN;
+    e.n = c.d;
+    e.src = x;
+    e.norm1 = pre_norm;
+    e.eps = c.eps;
+    quant_sink(c, e, 0, c.d);
+    RB_TRY(launch_vec_stage(e, rows, st));
+    AccView vd;
+    RB_TRY(ffn_part(c, *layer, rows, &vd, st));
+    VecStageParams o = {};
+    o.mode = VS_DEQ;
+    o.n = c.d;
+    o.acc = vd;
+    o.sx_in = c.sx[1];
+    o.terms = c.terms;
+    o.wscale0 = layer->down_scale;
+    o.eps = c.eps;
+    o.y_out = y;
+    return launch_vec_stage(o, rows, st);
+}
+
+/* MultiHeadAttention.forward (src/rotor/transformer.py:206-292) on device rows x float32
+ * [batch*seq][d_model] -> y float32 [batch*seq][d_model], including the output projection and
+ * the sub-norm that follows it.  The new K/V are written into layer->k_cache / v_cache at
+ * positions past_len .. past_len+seq-1.  Uses from `cfg` additionally: causal, rope_theta,
+ * max_seq; from `layer`: qkv_tiles, o_tiles, their scales, attn_sub_norm, the caches. */
+int rotor_b200_attention_forward(const rotor_b200_model_config* cfg, const rotor_b200_layer_weights* layer,
+                                 const float* x, int batch, int seq, int past_len, float* y, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+    RB_REQUIRE(cfg && layer && x && y && workspace && batch > 0 && seq > 0 && past_len >= 0);
+    RB_REQUIRE(layer->qkv_tiles && layer->o_tiles && layer->attn_sub_norm && layer->k_cache && layer->v_cache);
+    RB_REQUIRE(past_len + seq <= cfg->max_seq && batch <= cfg->max_batch);
+    RB_REQUIRE(((uintptr_t)workspace & 255) == 0);
+    const int rows = batch * seq;
+    Ctx c;
+    RB_TRY(block_ctx(c, cfg, rows, workspace, workspace_bytes));
+    cudaStream_t st = as_stream(stream);
+    set_int_kernel<<<1, 1, 0, st>>>(c.d_pos, past_len);
+    VecStageParams e = {};
+    e.mode = VS_PLAIN;
+    e.n = c.d;
+    e.src = x;
+    e.eps = c.eps;
+    quant_sink(c, e, 0, c.d);
+    RB_TRY(launch_vec_stage(e, rows, st));
+    AccView vo;
+    RB_TRY(attention_part(c, *layer, batch, seq, &vo, st));
+    VecStageParams o = {};
+    o.mode = VS_DEQ;
+    o.n = c.d;
+    o.acc = vo;
+    o.sx_in = c.sx[1];
+    o.terms = c.terms;
+    o.wscale0 = layer->o_scale;
+    o.norm1 = layer->attn_sub_norm;
+    o.eps = c.eps;
+    o.y_out = y;
+    return launch_vec_stage(o, rows, st);
+}
+
+}  // extern "C"

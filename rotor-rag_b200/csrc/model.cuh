@@ -1,0 +1,101 @@
+// Internal declarations shared by the decode-path kernels and the model driver.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace rb {
+
+// int32 accumulators of one BitLinear product: `planes` partial planes (one per K split),
+// each [ncols][out]; consumers add the planes (exact, order independent).
+struct AccView {
+    const int32_t* acc;
+    size_t plane_stride;  // elements between planes
+    int planes;
+    int out;
+};
+
+enum VecStageMode { VS_EMBED = 0, VS_PLAIN = 1, VS_OPROJ = 2, VS_FFN = 3, VS_DOWN = 4, VS_DEQ = 5 };
+
+struct VecStageParams {
+    int mode;
+    int n;                       // row width
+    // sources
+    const long long* ids;        // VS_EMBED: token ids [rows]
+    const __nv_bfloat16* embed;  // VS_EMBED: table [vocab][n]
+    const float* src;            // VS_PLAIN: float rows
+    AccView acc;                 // accumulators of the previous product
+    const float* sx_in;          // its activation scales [rows*terms]
+    int terms;
+    float wscale0, wscale1;      // weight scale(s) of the previous product
+    int ffn_act;
+    const float* norm0;          // VS_OPROJ: sub-norm weight
+    float* h;                    // residual stream [rows][n] (read/modify/write)
+    // sinks
+    const float* norm1;          // optional pre-norm weight applied before the sinks
+    float eps;
+    float* y_out;                // optional float copy of the (normed) row
+    int8_t* xq;                  // optional quantised output [rows*terms_out][kpad]
+    float* sx_out;
+    int32_t* xsum_out;
+    int terms_out;
+    int kpad;
+};
+
+int launch_vec_stage(const VecStageParams& p, int rows, cudaStream_t st);
+int configure_vec_stage();
+int configure_gemv_kernels();
+int configure_lmhead();
+
+// BitLinear product into partial planes (no atomics, no memset): returns the view.
+struct GemvPlan {
+    int ksplit;
+    int kt_per_split;
+};
+GemvPlan plan_gemv(size_t out, size_t in, int ncols);
+int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
+                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st);
+
+struct QkvFinishParams {
+    AccView acc;          // rows of the stacked [q;k;v] product
+    const float* sx;
+    int terms;
+    float sq, sk, sv;
+    int n_heads, n_kv_heads, head_dim;
+    int seq;              // tokens per sequence in this call
+    const int* past_len;  // device scalar: tokens already cached
+    int max_seq;          // cache capacity per sequence
+    float rope_theta;     // 0 = none
+    float* q;             // [rows][n_heads*head_dim]
+    float* k_cache;       // [batch][n_kv][max_seq][head_dim]
+    float* v_cache;
+};
+int launch_qkv_finish(const QkvFinishParams& p, int rows, cudaStream_t st);
+
+struct AttnParams {
+    const float* q;       // [rows][n_heads*head_dim]
+    const float* k_cache;
+    const float* v_cache;
+    float* out;           // [rows][n_heads*head_dim]
+    int n_heads, n_kv_heads, head_dim;
+    int seq;
+    const int* past_len;
+    int max_seq;
+    int causal;
+};
+int launch_attention(const AttnParams& p, int rows, cudaStream_t st);
+
+struct LmHeadParams {
+    const __nv_bfloat16* embed;  // [vocab][d]
+    const float* x;              // [rows][d], already normed
+    int vocab, d;
+    float* logits;               // optional [rows][vocab]
+    float* part_val;             // [rows][nparts]
+    int* part_idx;
+    long long* argmax_out;       // [rows]
+    int nparts;
+};
+int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st);
+int lmhead_parts();
+
+}  // namespace rb

@@ -60,6 +60,46 @@ _SIGNATURES = {
 }
 
 
+class ModelConfig(C.Structure):
+    """rotor_b200_model_config"""
+    _fields_ = [("vocab_size", C.c_int32), ("d_model", C.c_int32), ("n_layers", C.c_int32),
+                ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("d_ff", C.c_int32),
+                ("act_terms", C.c_int32), ("ffn_act", C.c_int32), ("causal", C.c_int32),
+                ("rope_theta", C.c_float), ("eps", C.c_float),
+                ("max_batch", C.c_int32), ("max_seq", C.c_int32), ("max_rows", C.c_int32),
+                ("gemv_variant", C.c_int32)]
+
+
+class LayerWeights(C.Structure):
+    """rotor_b200_layer_weights"""
+    _fields_ = [("qkv_tiles", _p), ("o_tiles", _p), ("gate_up_tiles", _p), ("down_tiles", _p),
+                ("q_scale", _f), ("k_scale", _f), ("v_scale", _f), ("o_scale", _f),
+                ("gate_scale", _f), ("up_scale", _f), ("down_scale", _f),
+                ("input_norm", _p), ("post_attn_norm", _p), ("attn_sub_norm", _p), ("ffn_sub_norm", _p),
+                ("k_cache", _p), ("v_cache", _p)]
+
+
+FFN_SILU_CLIP20, FFN_RELU2 = 0, 1
+LOGITS_NONE, LOGITS_LAST, LOGITS_ALL = 0, 1, 2
+_cfgp, _lwp = C.POINTER(ModelConfig), C.POINTER(LayerWeights)
+
+_SIGNATURES.update({
+    "rotor_b200_rmsnorm": (_i, [_p, _sz, _sz, _p, _f, _p, _p]),
+    "rotor_b200_model_workspace_bytes": (_sz, [_cfgp]),
+    "rotor_b200_model_create": (_i, [_cfgp, _lwp, _p, _p, _p, _sz, C.POINTER(_p)]),
+    "rotor_b200_model_destroy": (None, [_p]),
+    "rotor_b200_model_forward": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _p]),
+    "rotor_b200_model_forward_hidden": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _p, _p]),
+    "rotor_b200_model_decode_begin": (_i, [_p, _p, _i, _i, _p]),
+    "rotor_b200_model_decode_steps": (_i, [_p, _i, _i, _p]),
+    "rotor_b200_model_read_tokens": (_i, [_p, _i, _i, _p, _p]),
+    "rotor_b200_model_position": (_i, [_p]),
+    "rotor_b200_block_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
+    "rotor_b200_ffn_forward": (_i, [_cfgp, _lwp, _p, _p, _i, _p, _p, _sz, _p]),
+    "rotor_b200_attention_forward": (_i, [_cfgp, _lwp, _p, _i, _i, _i, _p, _p, _sz, _p]),
+})
+
+
 def _declare(signatures):
     for name, (res, args) in signatures.items():
         fn = getattr(lib, name)  # AttributeError here = header and library out of step

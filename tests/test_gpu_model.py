@@ -1,0 +1,262 @@
+"""GPU: the decode path above BitLinear (a6-a12) through the reference-shaped Python API,
+against the fixtures produced by the unmodified reference and against the oracle.
+Tolerance for floating outputs: max-abs error below 1e-3 of the output RMS."""
+import os
+
+import numpy as np
+import pytest
+
+import golden_inputs as G
+from oracle import bitlinear_np as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def rel_err(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.max(np.abs(a - b)) / np.sqrt(np.mean(b ** 2)))
+
+
+@pytest.fixture(scope="module")
+def rb():
+    import rotor_b200.transformer as tr
+    import rotor_b200.bitnet_model as bm
+    import rotor_b200.generation as gen
+    import rotor_b200.synth as synth
+    from rotor_b200 import semantics
+    class NS: pass
+    ns = NS()
+    ns.tr, ns.bm, ns.gen, ns.synth, ns.sem = tr, bm, gen, synth, semantics
+    return ns
+
+
+def o_sem(s):
+    """rotor_b200 semantics -> oracle semantics (three-term int8 stands for the float path)."""
+    return O.Semantics(act_terms=0 if s.act_terms == 3 else s.act_terms, ffn_act=s.ffn_act,
+                       rope_theta=s.rope_theta, causal=s.causal, eps=s.eps)
+
+
+def test_rmsnorm(rb):
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((3, 5, 2560)).astype(np.float32)
+    n = rb.tr.RMSNorm(2560)
+    n.weight = 1.0 + 0.1 * rng.standard_normal(2560).astype(np.float32)
+    assert rel_err(n.forward(x), O.rmsnorm(x, n.weight, 1e-6)) < 1e-5
+
+
+def test_ternary_linear_api(rb, golden_dir):
+    """TernaryLinear with the reference's call pattern (examples/test_gpu_layer.py:34-46)."""
+    z = np.load(os.path.join(golden_dir, "bitlinear_2560x6912.npz"))
+    w, scale, x1, x16 = G.bitlinear_case()
+    lin = rb.tr.TernaryLinear(2560, 6912, use_gpu=True)
+    assert lin.weights_cache is None
+    lin.load_from_bitnet(O.pack_ternary_matrix(w), scale)
+    assert lin.in_features == 2560 and lin.out_features == 6912 and lin.scale == scale
+    assert np.array_equal(lin.weights_cache, w)
+    assert rel_err(lin.forward(x1), z["y1"]) < TOL
+    y = lin.forward(x16.reshape(2, 8, 2560))          # 3-D input keeps its leading dims
+    assert y.shape == (2, 8, 6912) and rel_err(y.reshape(16, -1), z["y16"]) < TOL
+    with pytest.raises(Exception):
+        rb.tr.TernaryLinear(8, 8, use_gpu=False)       # no CPU path
+    with pytest.raises(Exception):
+        rb.tr.TernaryLinear(128, 16).forward(np.zeros((1, 128), np.float32))   # never loaded
+    with pytest.raises(ValueError):
+        lin.load_from_bitnet(np.zeros((4, 4), np.uint8), 1.0)
+
+
+@pytest.mark.parametrize("mode", ["reference", "baseline"])
+def test_ffn_block_config2(rb, golden_dir, mode):
+    """Config 2: RMSNorm(2560) -> gate/up -> gating -> sub-norm(6912) -> down, batch 1 and 16."""
+    z = np.load(os.path.join(golden_dir, "ffn_block.npz"))
+    lw, x1, x16 = G.ffn_case()
+    sem = rb.sem.REFERENCE if mode == "reference" else rb.sem.BASELINE
+    ffn = rb.tr.GatedFFN(2560, 6912, semantics=sem)
+    pre = rb.tr.RMSNorm(2560, eps=sem.eps)
+    pre.weight = lw["post_attn_norm"]
+    ffn.ffn_norm.weight = lw["ffn_sub_norm"]
+    for nm, proj in (("gate", ffn.gate_proj), ("up", ffn.up_proj), ("down", ffn.down_proj)):
+        proj.load_from_bitnet(O.pack_ternary_matrix(lw[nm][0]), lw[nm][1])
+    from rotor_b200 import ops
+    import torch
+    for tag, x in (("m1", x1), ("m16", x16)):
+        y_fused = ffn.forward_device(ops.to_device(x, torch.float32), pre_norm=pre).cpu().numpy()
+        y_api = ffn.forward(pre.forward(x))
+        want = O.ffn(O.rmsnorm(x, lw["post_attn_norm"], sem.eps), lw, o_sem(sem))
+        if mode == "reference":
+            assert rel_err(y_fused, z[tag]) < TOL and rel_err(y_api, z[tag]) < TOL
+        assert rel_err(y_fused, want) < TOL, (mode, tag, rel_err(y_fused, want))
+        assert rel_err(y_api, want) < TOL
+
+
+def _tiny(rb, name, sem, **kw):
+    om, prompt = G.tiny_model(name)
+    return om, prompt, rb.synth.model_from_oracle_params(om, semantics=sem, max_seq=64, **kw)
+
+
+@pytest.mark.parametrize("name", list(G.TINY_MODELS))
+def test_attention_and_block_standalone(rb, name):
+    om, prompt, model = _tiny(rb, name, rb.sem.REFERENCE)
+    cfg, lw = om["cfg"], om["layers"][0]
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((1, 6, cfg["d_model"])).astype(np.float32)
+    blk = model.layers[0]
+    want, wc = O.attention(x, lw, cfg, O.REFERENCE, None, True)
+    got, cache = blk.attention.forward(x, use_cache=True)
+    assert rel_err(got, want) < TOL
+    assert rel_err(cache["k"], wc["k"]) < TOL and rel_err(cache["v"], wc["v"]) < TOL
+    # one more token against the cache
+    x2 = rng.standard_normal((1, 1, cfg["d_model"])).astype(np.float32)
+    want2, _ = O.attention(x2, lw, cfg, O.REFERENCE, wc, True)
+    got2, cache2 = blk.attention.forward(x2, kv_cache=cache, use_cache=True)
+    assert rel_err(got2, want2) < TOL and cache2.length == 7
+    # whole block, 2-D input like the reference accepts
+    wantb, _ = O.block(x, lw, cfg, O.REFERENCE)
+    gotb, none = blk.forward(x[0])
+    assert none is None and gotb.shape == x[0].shape and rel_err(gotb, wantb[0]) < TOL
+    # causal mask through the mask argument
+    mask = O.causal_mask(6, 6)
+    wantc, _ = O.block(x, lw, cfg, O.with_semantics(O.REFERENCE, causal=True))
+    gotc, _ = blk.forward(x, mask=mask)
+    assert rel_err(gotc, wantc) < TOL
+    with pytest.raises(NotImplementedError):
+        blk.forward(x, mask=np.zeros((6, 6)) + 1.0)
+
+
+@pytest.mark.parametrize("name", list(G.TINY_MODELS))
+def test_model_forward_matches_reference_fixture(rb, golden_dir, name):
+    z = np.load(os.path.join(golden_dir, f"model_{name}.npz"))
+    om, prompt, model = _tiny(rb, name, rb.sem.REFERENCE)
+    logits, caches = model.forward(prompt[None, :], use_cache=True)
+    assert logits.shape == z["prompt_logits"][None].shape
+    assert rel_err(logits[0], z["prompt_logits"]) < TOL
+    assert len(caches) == om["cfg"]["n_layers"]
+    assert rel_err(caches[-1]["k"], z["last_k"]) < TOL
+    l1, _ = model.forward(prompt)                      # 1-D ids -> [S, V]
+    assert l1.shape == z["prompt_logits"].shape and rel_err(l1, z["prompt_logits"]) < TOL
+    last, _ = model.forward(prompt[None, :], logits_positions="last")
+    assert rel_err(last[0, -1], z["prompt_logits"][-1]) < TOL
+    hid, _ = model.forward(prompt[None, :], return_logits=False)
+    want_h, _ = O.model_forward(om, prompt[None, :], O.REFERENCE, return_logits=False)
+    assert rel_err(hid, want_h) < TOL
+    mc = rb.synth.model_from_oracle_params(om, semantics=rb.sem.REFERENCE.with_(causal=True), max_seq=64)
+    lc, _ = mc.forward(prompt[None, :])
+    assert rel_err(lc[0], z["prompt_logits_causal"]) < TOL
+
+
+@pytest.mark.parametrize("name", list(G.TINY_MODELS))
+def test_greedy_generation_identical_to_reference(rb, golden_dir, name):
+    """First 32 greedy tokens equal the reference's (TextGenerator, use_cache=True), through the
+    device-resident graph path, the eager step path, and the host-sampling path."""
+    z = np.load(os.path.join(golden_dir, f"model_{name}.npz"))
+    om, prompt, model = _tiny(rb, name, rb.sem.REFERENCE)
+    want = z["greedy_ids"].tolist()
+    n_new = len(want) - len(prompt)
+    assert n_new == G.N_NEW
+    tok = rb.synth.PassThroughTokenizer()
+    text = " ".join(map(str, prompt))
+    tg = rb.gen.TextGenerator(model, tok, max_length=len(want), use_cache=True)
+    seen = []
+    out = tg.generate(text, max_new_tokens=n_new, stop_on_eos=False, callback=seen.append)
+    assert [int(t) for t in out.split()] == want
+    assert [int(t) for t in seen] == want[len(prompt):]
+    assert model.generate_greedy(prompt, n_new, use_graph=False) == want[len(prompt):]
+    assert model.generate_greedy(prompt, n_new, use_graph=True, chunk=0) == want[len(prompt):]
+    # host-side sampling strategy object -> logits come back each step
+    class Argmax(rb.gen.SamplingStrategy):
+        def sample(self, logits, temperature=1.0):
+            return int(np.argmax(logits))
+    tg2 = rb.gen.TextGenerator(model, tok, sampling_strategy=Argmax(), max_length=len(want), use_cache=True)
+    out2 = tg2.generate(text, max_new_tokens=n_new, stop_on_eos=False)
+    assert [int(t) for t in out2.split()] == want
+    # per-step logits stay within tolerance of the reference's
+    logits, cache = model.forward(prompt[None, :], use_cache=True, logits_positions="last")
+    assert rel_err(logits[0, -1], z["step_logits"][0]) < TOL
+    l2, cache = model.forward(np.array([[want[len(prompt)]]]), past_kv_cache=cache, use_cache=True)
+    assert rel_err(l2[0, -1], z["step_logits"][1]) < TOL
+
+
+@pytest.mark.parametrize("name", list(G.TINY_MODELS))
+def test_baseline_semantics_against_oracle(rb, name):
+    """Published semantics (int8 activations, relu^2, rotary, causal, eps 1e-5): logits within
+    tolerance of the oracle that quantises identically, and the same greedy tokens."""
+    om, prompt, model = _tiny(rb, name, rb.sem.BASELINE)
+    want_logits, _ = O.model_forward(om, prompt[None, :], O.BASELINE)
+    logits, _ = model.forward(prompt[None, :])
+    err = rel_err(logits, want_logits)
+    assert err < 2e-2, err     # one flipped int8 rounding moves a logit by more than 1e-3 of RMS
+    ids = O.generate_greedy(om, prompt, 32, O.BASELINE)
+    got = model.generate_greedy(prompt, 32)
+    same = sum(int(a == b) for a, b in zip(got, ids[len(prompt):]))
+    assert same >= 24, (same, got, ids[len(prompt):])
+
+
+def test_generation_loop_rules(rb):
+    """max_length caps prompt + new tokens, EOS stops without being appended, streaming yields
+    the prompt first (reference src/rotor/generation.py:210, 228-229, 315)."""
+    om, prompt, model = _tiny(rb, "hd64", rb.sem.REFERENCE)
+    tok = rb.synth.PassThroughTokenizer()
+    text = " ".join(map(str, prompt))
+    full = model.generate_greedy(prompt, 12)
+    tg = rb.gen.TextGenerator(model, tok, max_length=len(prompt) + 4)
+    assert len(tg.generate(text, max_new_tokens=50, stop_on_eos=False).split()) == len(prompt) + 4
+    tg0 = rb.gen.TextGenerator(model, tok, max_length=len(prompt))
+    assert tg0.generate(text) == text                      # nothing to generate
+    tok_eos = rb.synth.PassThroughTokenizer(eos_token_id=full[3])
+    tg_eos = rb.gen.TextGenerator(model, tok_eos, max_length=64)
+    out = [int(t) for t in tg_eos.generate(text, max_new_tokens=12).split()]
+    assert out == list(prompt) + full[:full.index(full[3])]
+    pieces = list(rb.gen.TextGenerator(model, tok, max_length=64).generate_streaming(text, max_new_tokens=5,
+                                                                                   stop_on_eos=False))
+    assert pieces[0] == text and [int(p) for p in pieces[1:]] == full[:5]
+    # top-k / top-p run on host logits and return valid ids
+    np.random.seed(0)
+    for strat in (rb.gen.TopKSampling(k=5), rb.gen.TopPSampling(p=0.8)):
+        tgs = rb.gen.TextGenerator(model, tok, sampling_strategy=strat, temperature=0.7, max_length=64)
+        ids = [int(t) for t in tgs.generate(text, max_new_tokens=4, stop_on_eos=False).split()]
+        assert len(ids) == len(prompt) + 4 and all(0 <= t < om["cfg"]["vocab_size"] for t in ids)
+
+
+def test_load_bitnet_model_from_checkpoint(rb, tmp_path, golden_dir):
+    """load_bitnet_model(dir, use_gpu=True) on a synthetic config.json + model.safetensors."""
+    z = np.load(os.path.join(golden_dir, "model_hd64.npz"))
+    om, prompt = G.tiny_model("hd64")
+    rb.synth.write_checkpoint(om, str(tmp_path))
+    model = rb.bm.load_bitnet_model(str(tmp_path), use_gpu=True, max_seq=64)
+    logits, _ = model.forward(prompt[None, :])
+    assert rel_err(logits[0], z["prompt_logits"]) < TOL
+    with pytest.raises(Exception):
+        rb.bm.load_bitnet_model(str(tmp_path), use_gpu=False)
+
+
+def test_plugin_backend_object(rb):
+    """get_gpu() -> pack_ternary_weights / ternary_matmul with the reference's argument shapes
+    (src/rotor/transformer.py:107-109, 136-142)."""
+    from rotor_b200.gpu_layers import get_gpu
+    gpu = get_gpu()
+    assert gpu is get_gpu()
+    rng = np.random.default_rng(12)
+    w = O.synth_ternary(rng, 2560, 2560)
+    packed = gpu.pack_ternary_weights(w)
+    scales = np.full(2560, 1.2, dtype=np.float32)
+    x = rng.standard_normal(2560).astype(np.float32)
+    y = gpu.ternary_matmul(packed, scales, x, 2560, 2560)
+    want = (w.astype(np.float32) @ x) * scales
+    assert y.dtype == np.float32 and y.shape == (2560,)
+    assert np.abs(y - want).max() < 1e-2          # the authors' own GPU-vs-CPU gate (gpu_layers.py:181)
+    assert rel_err(y, want) < TOL
+    with pytest.raises(ValueError):
+        gpu.ternary_matmul(packed, scales, x, 2560, 100)
+
+
+def test_batched_forward_and_cache_growth(rb):
+    om, prompt, model = _tiny(rb, "hd64", rb.sem.REFERENCE, max_batch=1)
+    rng = np.random.default_rng(3)
+    ids = rng.integers(0, om["cfg"]["vocab_size"], size=(3, 7))
+    want, _ = O.model_forward(om, ids, O.REFERENCE)
+    got, caches = model.forward(ids, use_cache=True)        # batch 3 > max_batch 1: handle regrows
+    assert rel_err(got, want) < TOL and caches[0]["k"].shape[0] == 3
+    long_ids = rng.integers(0, om["cfg"]["vocab_size"], size=(1, 90))   # > max_seq 64
+    want2, _ = O.model_forward(om, long_ids, O.REFERENCE)
+    got2, _ = model.forward(long_ids)
+    assert rel_err(got2, want2) < TOL
