@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""Benchmark of the ternary BitLinear decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (N = 1 and, as independent replicas, N > 1): random-init BitNet-b1.58-2B
+architecture (30 layers, hidden 2560, 20 query / 5 KV heads, FFN 6912, vocab 128256,
+bf16 tied embeddings, ternary projections), greedy decode, batch 1, 128-token seeded
+prompt, published semantics (int8 absmax activations, relu^2 gating, rotary, causal).
+A step is one generated token.  The prompt prefill is not timed; W warm-up tokens are
+generated, then exactly K tokens are timed with CUDA events on the launching stream
+(barrier + synchronize on both sides, max over ranks).
+
+One JSON line is printed by rank 0:
+  value      tokens/s of the whole job, weights and KV cache resident in HBM
+  e2e        the same through TextGenerator.generate(): host prompt string in, token ids
+             back on the host every step
+  roofline   the ternary GEMV kernel on config 1 (2560 -> 6912, batch 1): 64 distinct
+             matrices (283 MB > L2) back to back in one CUDA graph, algorithmic bytes per
+             launch / mean launch time, against the measured HBM copy bandwidth
+  cpu_baseline  the NumPy oracle port of the reference's path on this box's host cores,
+             bounded sample (N = 1 only)
+--impl reference times that same CPU port as the reference arm.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "rotor-rag_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+METRIC = "BitNet-2B-shape greedy decode tokens/s (batch 1); roofline = ternary GEMV HBM GB/s"
+UNIT = "tokens/s"
+CFG_2B = dict(vocab_size=128256, d_model=2560, n_layers=30, n_heads=20, n_kv_heads=5, d_ff=6912)
+PROMPT_LEN = 128
+WORKLOAD = ("BitNet-b1.58-2B-shape random-init model (30 layers, d 2560, 20q/5kv heads, ffn 6912, vocab 128256), "
+            "greedy decode batch 1 after a 128-token prompt; int8-activation semantics")
+
+
+def algorithmic_bytes_per_token(cfg, context, kv_bytes=4):
+    """Bytes one decode step has to read: ternary tiles, bf16 LM head, norm weights, one
+    embedding row, and the KV cache at `context` positions."""
+    d, ff, L = cfg["d_model"], cfg["d_ff"], cfg["n_layers"]
+    hd = d // cfg["n_heads"]
+    dq, dkv = cfg["n_heads"] * hd, cfg["n_kv_heads"] * hd
+    ternary = L * ((dq + 2 * dkv) * d + d * dq + 2 * ff * d + d * ff) // 4
+    lm = cfg["vocab_size"] * d * 2
+    norms = L * (3 * d + ff) * 4 + d * 4
+    kv = L * 2 * dkv * context * kv_bytes
+    return ternary + lm + norms + d * 2 + kv
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for (t, r) in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 7] or \
+               [r for (_, r) in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[0]) for r in rows]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][1]), "reasons": reasons,
+                "samples": len(rows)}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- CPU port
+def cpu_decode_sample(n_tokens, n_warm, seed=0, budget_s=None):
+    """The oracle's restatement of the reference path (NumPy + its int8 weight cache) on the
+    host cores: 2B-shape model, KV cache pre-filled with N(0,1) at 128 positions (timing is
+    the same as after a real prefill), greedy one-token steps.  Returns tokens/s and notes."""
+    import numpy as np
+    from oracle import bitlinear_np as O
+    try:
+        from threadpoolctl import threadpool_info
+        threads = max([p.get("num_threads", 1) for p in threadpool_info()] or [os.cpu_count() or 1])
+    except Exception:
+        threads = os.cpu_count() or 1
+    cfg = CFG_2B
+    model = O.synth_model(cfg, seed, random_norms=False, fast_embed=True)
+    rng = np.random.default_rng(seed + 1)
+    hd = cfg["d_model"] // cfg["n_heads"]
+    cache = [{"k": rng.standard_normal((1, cfg["n_kv_heads"], PROMPT_LEN, hd)).astype(np.float32),
+              "v": rng.standard_normal((1, cfg["n_kv_heads"], PROMPT_LEN, hd)).astype(np.float32)}
+             for _ in range(cfg["n_layers"])]
+    tok = int(rng.integers(0, cfg["vocab_size"]))
+    times = []
+    t_start = time.perf_counter()
+    for i in range(n_warm + n_tokens):
+        t0 = time.perf_counter()
+        logits, cache = O.model_forward(model, np.array([[tok]]), O.REFERENCE, past_kv_cache=cache, use_cache=True)
+        tok = O.greedy(logits[0, -1])
+        dt = time.perf_counter() - t0
+        if i >= n_warm:
+            times.append(dt)
+        if budget_s is not None and i >= n_warm and time.perf_counter() - t_start > budget_s:
+            break
+    per_tok = sum(times) / len(times)
+    return 1.0 / per_tok, threads, len(times)
+
+
+def run_reference(args, rank):
+    """Reference arm: the reference's CPU implementation of the path.  Its Python modules
+    cannot travel to the GPU box, so this is the NumPy port under oracle/ (kind "port"): the
+    same np.dot(x, int8_cache.T) * scale, RMSNorm, attention and LM-head statements."""
+    if rank != 0:
+        return
+    n_tok = max(1, min(args.steps, 24))
+    n_warm = max(1, min(args.warmup, 2))
+    t0 = time.perf_counter()
+    tps, threads, done = cpu_decode_sample(n_tok, n_warm, budget_s=150.0)
+    sample = (f"{done} timed one-token steps (+{n_warm} warm-up) of the full 30-layer 2B-shape model on the host, "
+              f"KV cache pre-filled at {PROMPT_LEN} positions; reference float semantics")
+    line = {"metric": METRIC, "value": tps, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+            "steps": done, "warmup": n_warm, "ms_per_step": 1000.0 / tps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f64 (NumPy promotion) over int8 weight cache",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "global_batch": 1, "prompt_len": PROMPT_LEN},
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "wall_s": time.perf_counter() - t0}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def gemv_roofline(torch, abi, nmat=64, iters=20):
+    """Config 1: ternary GEMV 2560 -> 6912, batch 1 (int8 activations), 64 distinct matrices
+    back to back in one CUDA graph so that weights come from HBM, not L2."""
+    lib = abi.lib
+    out, inn = 6912, 2560
+    tb = lib.rotor_b200_tiles_bytes(out, inn)
+    tiles = torch.randint(0, 256, (nmat, tb), dtype=torch.uint8, device="cuda")
+    tiles &= 0xAA  # codes {0, 2}: valid weights -1/+1; timing does not depend on the values
+    kpad = lib.rotor_b200_in_padded(inn)
+    xq = torch.randint(-127, 128, (1, kpad), dtype=torch.int8, device="cuda")
+    xsum = xq.to(torch.int32).sum(1).to(torch.int32)
+    acc = torch.empty((nmat, 1, out), dtype=torch.int32, device="cuda")
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        s = st.cuda_stream
+
+        def body():
+            for i in range(nmat):
+                abi.check(lib.rotor_b200_bitlinear_acc(tiles[i].data_ptr(), out, inn, xq.data_ptr(), xsum.data_ptr(),
+                                                       1, acc[i].data_ptr(), abi.VARIANT_AUTO, s), "gemv")
+        body()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            body()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(iters):
+            g.replay()
+        e1.record(st)
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) * 1e-3 / (iters * nmat)
+    alg = out * inn // 4 + inn + 4 * out + 4   # packed weights + int8 activations + int32 outputs + scale
+    return alg, sec
+
+
+def run_b200(args, rank, world):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from rotor_b200 import abi, semantics
+    from rotor_b200.generation import TextGenerator
+    from rotor_b200.synth import PassThroughTokenizer, random_model_on_device
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    K, W = args.steps, max(args.warmup, 3)
+    total_new = 1 + W + K                       # first token comes out of the prefill
+    max_seq = PROMPT_LEN + total_new + 8
+    model = random_model_on_device(CFG_2B, seed=1234 + rank, semantics=semantics.BASELINE, max_seq=max_seq,
+                                   max_rows=PROMPT_LEN)
+    rng = np.random.default_rng(99 + rank)
+    prompt = rng.integers(0, CFG_2B["vocab_size"], size=PROMPT_LEN).astype(np.int64)
+
+    # ---- device-resident timing (value)
+    h = model._ensure_handle(1, PROMPT_LEN, max_seq)
+    st = torch.cuda.Stream()
+    launches0 = abi.lib.rotor_b200_launch_count()
+    with torch.cuda.stream(st):
+        s = st.cuda_stream
+        ids_d = torch.from_numpy(prompt.reshape(1, -1)).cuda()
+        first = torch.empty(1, dtype=torch.int64, device="cuda")
+        abi.check(abi.lib.rotor_b200_model_forward(h.h, ids_d.data_ptr(), 1, PROMPT_LEN, 0, abi.LOGITS_NONE, None,
+                                                   first.data_ptr(), s), "prefill")
+        abi.check(abi.lib.rotor_b200_model_decode_begin(h.h, first.data_ptr(), 1, PROMPT_LEN, s), "begin")
+        abi.check(abi.lib.rotor_b200_model_decode_steps(h.h, W, 1, s), "warmup")
+        barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
+        time.sleep(0.25)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        launches_before = abi.lib.rotor_b200_launch_count()
+        t0 = time.time()
+        e0.record(st)
+        abi.check(abi.lib.rotor_b200_model_decode_steps(h.h, K, 1, s), "timed steps")
+        e1.record(st)
+        barrier()
+        t1 = time.time()
+        clocks = sampler.stop(t0, t1)
+        launches = abi.lib.rotor_b200_launch_count() - launches_before
+        sec = e0.elapsed_time(e1) * 1e-3
+    abi.device_status()
+    del launches0
+
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "tokens_per_s": K / sec, "gpu_launches": int(launches)}), flush=True)
+        return
+
+    # ---- end to end through the public API (host prompt in, tokens to the host every step)
+    tok = PassThroughTokenizer()
+    text = " ".join(map(str, prompt))
+    gen = TextGenerator(model, tok, max_length=PROMPT_LEN + 1 + W + K, use_cache=True, readback_chunk=1)
+    stamps = []
+    gen.generate(text, max_new_tokens=4, stop_on_eos=False)            # warm: graph already built
+    barrier()
+    t0 = time.perf_counter()
+    gen.generate(text, max_new_tokens=1 + W + K, stop_on_eos=False, callback=lambda _t: stamps.append(time.perf_counter()))
+    torch.cuda.synchronize()
+    t_end = time.perf_counter()
+    e2e_sec = stamps[-1] - stamps[W]           # the last K tokens of the call, as seen by the host callback
+    e2e_total = t_end - t0
+
+    secs = torch.tensor([sec, e2e_sec, e2e_total], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(secs, op=dist.ReduceOp.MAX)
+    sec, e2e_sec, e2e_total = [float(v) for v in secs.cpu()]
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak_gbs()
+    alg, gsec = gemv_roofline(torch, abi)
+    ctx_mid = PROMPT_LEN + 1 + W + K // 2
+    step_bytes = algorithmic_bytes_per_token(CFG_2B, ctx_mid)
+    line = {
+        "metric": METRIC, "value": world * K / sec, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": sec * 1e3 / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 activations x ternary weights -> int32 (float32 glue, bf16 LM head)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": world, "prompt_len": PROMPT_LEN,
+                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (2B shape does not shard 2/4/8-way)",
+                   "l2": "inputs larger than L2 (1.18 GB of weights per step)"},
+        "e2e": {"value": world * K / e2e_sec, "unit": UNIT,
+                "h2d_bytes_per_step": PROMPT_LEN * 8 / (1 + W + K), "d2h_bytes_per_step": 8,
+                "call": "TextGenerator.generate (host string in, per-token ids out)",
+                "whole_call_tokens_per_s": world * (1 + W + K) / e2e_total},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "bitlinear_acc_kernel (ternary GEMV 2560->6912, batch 1)",
+                     "achieved": alg / gsec / 1e9, "peak": peak, "unit": "GB/s", "frac": alg / gsec / 1e9 / peak,
+                     "peak_kind": f"{peak_kind} HBM copy bandwidth", "traffic": None,
+                     "bytes_per_launch": alg, "us_per_launch": gsec * 1e6},
+        "step_roofline": {"algorithmic_bytes_per_token": step_bytes, "achieved_gbs": step_bytes * K / sec / 1e9,
+                          "frac_of_peak": step_bytes * K / sec / 1e9 / peak},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        tps, threads, done = cpu_decode_sample(6, 1, budget_s=40.0)
+        line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"{done} timed one-token steps (+1 warm-up), full 30-layer 2B-shape model, "
+                                          f"NumPy oracle port of the reference path, KV cache pre-filled at {PROMPT_LEN}"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "gemv"],
+                    help="profiling aid: run only the device-resident decode section or only the GEMV section")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.only == "gemv":
+        import torch
+        from rotor_b200 import abi
+        torch.cuda.set_device(0)
+        alg, gsec = gemv_roofline(torch, abi)
+        print(json.dumps({"only": "gemv", "bytes_per_launch": alg, "us_per_launch": gsec * 1e6,
+                          "gbs": alg / gsec / 1e9}), flush=True)
+        return
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_b200(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

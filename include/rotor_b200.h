@@ -61,6 +61,8 @@ const char* rotor_b200_status_string(int status);
 /* Reads and clears the device status word that bounded device-side waits write to
  * (0, or ROTOR_B200_ERR_TIMEOUT).  Synchronises with the device. */
 int rotor_b200_device_status(void);
+/* Number of kernels this library has launched in this process, graph replays included. */
+unsigned long long rotor_b200_launch_count(void);
 
 /* ---------------------------------------------------------------- format (a1-a3)
  * Device twins of the reference's format primitives.

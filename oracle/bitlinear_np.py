@@ -360,7 +360,7 @@ def synth_ternary(rng, out, inn):
 SYNTH_SCALE = np.float32(0.015955)  # mean |N(0, 0.02)|
 
 
-def synth_model(cfg, seed, random_norms=True):
+def synth_model(cfg, seed, random_norms=True, fast_embed=False):
     """Random-init model of the BitNet-b1.58 layout: ternary projections uniform over
     {-1,0,+1}, one float32 scale per matrix, bf16-representable N(0, 0.02) embeddings
     (tied LM head), norm weights near one."""
@@ -387,7 +387,13 @@ def synth_model(cfg, seed, random_norms=True):
             "q": lin(dq, d), "k": lin(dkv, d), "v": lin(dkv, d), "o": lin(d, dq),
             "gate": lin(ff, d), "up": lin(ff, d), "down": lin(d, ff),
         })
-    embed = bf16_round((0.02 * rng.standard_normal((cfg["vocab_size"], d))).astype(np.float32))
+    if fast_embed:
+        # timing-only variant for full-size tables: float32 draws, bf16 by truncation, in place
+        embed = rng.standard_normal((cfg["vocab_size"], d), dtype=np.float32)
+        embed *= np.float32(0.02)
+        embed.view(np.uint32)[...] &= np.uint32(0xFFFF0000)
+    else:
+        embed = bf16_round((0.02 * rng.standard_normal((cfg["vocab_size"], d))).astype(np.float32))
     return {"cfg": dict(cfg), "embed": embed, "norm": norm_w(d), "layers": layers}
 
 

@@ -19,8 +19,14 @@ __host__ __device__ inline size_t opad_of(size_t out) { return round_up(out, TIL
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
-// Launch-status helper: maps the last CUDA error to the library's status codes.
+// Kernel launches issued by this library in this process (graph replays add the launches
+// the graph holds).  Defined in format.cu.
+extern unsigned long long g_launch_count;
+
+// Called right after every kernel launch: counts it and maps the last CUDA error to the
+// library's status codes.
 inline int launch_status() {
+    ++g_launch_count;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? ROTOR_B200_OK : ROTOR_B200_ERR_CUDA;
 }

@@ -9,6 +9,8 @@
 
 namespace rb {
 
+unsigned long long g_launch_count = 0;
+
 __global__ void encode_kernel(const int8_t* __restrict__ w, size_t n, uint8_t* __restrict__ plus,
                               uint8_t* __restrict__ minus) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -160,6 +162,8 @@ using namespace rb;
 extern "C" {
 
 int rotor_b200_version(void) { return 100; }
+
+unsigned long long rotor_b200_launch_count(void) { return g_launch_count; }
 
 const char* rotor_b200_status_string(int status) {
     switch (status) {

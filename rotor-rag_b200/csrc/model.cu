@@ -55,6 +55,7 @@ struct Model {
     int pos, step, batch;
     cudaGraphExec_t graph;
     int graph_batch;
+    unsigned long long graph_launches;  // kernels inside the captured step
 };
 
 struct Carve {
@@ -465,7 +466,10 @@ int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void*
             RB_REQUIRE(st != nullptr);  // the legacy default stream cannot be captured
             cudaGraph_t g = nullptr;
             RB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            const unsigned long long before = g_launch_count;
             int rc = one_step(*m, st);
+            m->graph_launches = g_launch_count - before;
+            g_launch_count = before;  // captured, not run
             cudaError_t e = cudaStreamEndCapture(st, &g);
             if (rc || e != cudaSuccess) {
                 if (g) cudaGraphDestroy(g);
@@ -477,6 +481,7 @@ int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void*
             m->graph_batch = m->batch;
         }
         for (int i = 0; i < nsteps; ++i) RB_CUDA(cudaGraphLaunch(m->graph, st));
+        g_launch_count += m->graph_launches * (unsigned long long)nsteps;
     }
     m->pos += nsteps;
     m->step += nsteps;
