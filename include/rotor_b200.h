@@ -220,6 +220,12 @@ int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void*
 int rotor_b200_model_read_tokens(void* handle, int first_step, int count, int64_t* tokens_host, void* stream);
 int rotor_b200_model_position(void* handle);
 
+/* Programmatic dependent launch for the decode chain: with 1, every kernel of a step may start
+ * and prefetch its weight tiles while its predecessor drains (the kernels order themselves with
+ * griddepcontrol.wait).  Affects later launches and graphs captured afterwards; returns the
+ * previous setting.  No counterpart in the reference. */
+int rotor_b200_set_pdl(int enable);
+
 /* Blocks [layer_begin, layer_end) of the model on caller-provided hidden rows (float32
  * [batch*seq][d_model]).  apply_final_norm != 0 applies the model's final norm, as
  * BitNetModel.forward(return_logits=False) does (src/rotor/bitnet_model.py:231-243);
@@ -235,8 +241,8 @@ int rotor_b200_model_forward_hidden(void* handle, const float* hidden_in, int ba
  * [batch*seq][d_model] -> y, output projection and sub-norm included; appends K/V to the
  * layer's caches at past_len.  Both read dimensions and switches from cfg and pointers from
  * layer (only the members of their half need to be set) and need
- * rotor_b200_block_workspace_bytes(...) bytes of 256-byte aligned device workspace. */
-size_t rotor_b200_block_workspace_bytes(int d_model, int n_heads, int n_kv_heads, int d_ff, int terms, int rows);
+ * rotor_b200_block_workspace_bytes(cfg, rows) bytes of 256-byte aligned device workspace. */
+size_t rotor_b200_block_workspace_bytes(const rotor_b200_model_config* cfg, int rows);
 int rotor_b200_ffn_forward(const rotor_b200_model_config* cfg, const rotor_b200_layer_weights* layer,
                            const float* pre_norm, const float* x, int rows, float* y,
                            void* workspace, size_t workspace_bytes, void* stream);

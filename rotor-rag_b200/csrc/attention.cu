@@ -9,6 +9,7 @@
 // The cache is a fixed [batch][n_kv][max_seq][D] float32 buffer written in place at
 // position past_len + s instead of the reference's per-step np.concatenate.
 #include "model.cuh"
+#include "quant.cuh"
 
 namespace rb {
 
@@ -18,8 +19,8 @@ __device__ __forceinline__ float deq_acc(const AccView& a, const float* __restri
     for (int t = 0; t < terms; ++t) {
         const size_t col = (size_t)m * terms + t;
         int s = 0;
-        for (int p = 0; p < a.planes; ++p) s += a.acc[(size_t)p * a.plane_stride + col * a.out + o];
-        v += (float)s * sx[col];
+        for (int p = 0; p < a.planes; ++p) s += __ldcg(&a.acc[(size_t)p * a.plane_stride + col * a.out + o]);
+        v += (float)s * __ldcg(&sx[col]);
     }
     return v * wscale;
 }
@@ -42,12 +43,10 @@ __global__ void __launch_bounds__(256) qkv_finish_kernel(QkvFinishParams p) {
         const float sc = is_q ? p.sq : p.sk;
         float a = deq_acc(p.acc, p.sx, m, p.terms, base + i, sc);
         float c = deq_acc(p.acc, p.sx, m, p.terms, base + i + half, sc);
-        if (p.rope_theta > 0.f) {
-            const double ang = (double)pos * pow((double)p.rope_theta, -2.0 * (double)i / (double)D);
-            double sn, cs;
-            sincos(ang, &sn, &cs);
-            const float ra = (float)((double)a * cs - (double)c * sn);
-            const float rc = (float)((double)c * cs + (double)a * sn);
+        if (p.rope) {
+            const float2 cs = p.rope[(size_t)pos * half + i];
+            const float ra = a * cs.x - c * cs.y;
+            const float rc = c * cs.x + a * cs.y;
             a = ra;
             c = rc;
         }
@@ -66,6 +65,23 @@ __global__ void __launch_bounds__(256) qkv_finish_kernel(QkvFinishParams p) {
         p.v_cache[(((size_t)b * p.n_kv_heads + head) * p.max_seq + pos) * D + i] =
             deq_acc(p.acc, p.sx, m, p.terms, dq + dkv + e, p.sv);
     }
+}
+
+// cos/sin of pos * theta^(-2i/D), evaluated in double, stored as float2 [max_seq][D/2].
+__global__ void rope_table_kernel(float2* table, int max_seq, int half, double theta) {
+    const int total = max_seq * half;
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        const int pos = e / half, i = e % half;
+        const double ang = (double)pos * pow(theta, -(double)i / (double)half);
+        double sn, cs;
+        sincos(ang, &sn, &cs);
+        table[e] = make_float2((float)cs, (float)sn);
+    }
+}
+
+int launch_rope_table(float2* table, int max_seq, int head_dim, float theta, cudaStream_t st) {
+    rope_table_kernel<<<148, 256, 0, st>>>(table, max_seq, head_dim / 2, (double)theta);
+    return launch_status();
 }
 
 int launch_qkv_finish(const QkvFinishParams& p, int rows, cudaStream_t st) {
@@ -159,6 +175,223 @@ int launch_attention(const AttnParams& p, int rows, cudaStream_t st) {
         default: return ROTOR_B200_ERR_SHAPE;
     }
     return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// One-token attention for generation steps.  Grid (n_kv_heads * nsplit, batch): a CTA owns
+// one KV head and one slice of the cached positions, serves the G query heads that share
+// that KV head, and leaves (max, sum, weighted V) partials.  The CTA that finishes last for
+// a sequence merges the partials of all heads and quantises the merged row for the output
+// projection, so the step needs no separate combine or quantise launch.
+template <int D>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ AttnDecodeParams p) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int half = D / 2, DL = D / 8;  // DL floats of a key per lane, 8 lanes per key
+    const int G = p.n_heads / p.n_kv_heads;
+    const int b = blockIdx.y, hk = blockIdx.x / p.nsplit, sp = blockIdx.x % p.nsplit;
+    const int dq = p.n_heads * D, dkv = p.n_kv_heads * D;
+    const int lcmax = (p.max_seq + p.nsplit - 1) / p.nsplit;
+    float* q_s = sm;                    // [G][D], pre-scaled by 1/sqrt(D)
+    float* k_new = q_s + G * D;         // [D]
+    float* v_new = k_new + D;           // [D]
+    float* sc = v_new + D;              // [G][lcmax]
+    float* scratch = sc + G * lcmax;    // [64]
+    float* row = scratch + 64;          // [dq]   (tail only)
+
+    pdl_trigger();
+    pdl_wait();
+    const int pos = *p.past_len;
+    const int T = min(pos + 1, p.max_seq);
+    const int lc = (T + p.nsplit - 1) / p.nsplit;
+    const int t0 = sp * lc, t1 = min(T, t0 + lc);
+    const int m = b;  // one token per sequence
+    const float scale = 1.0f / sqrtf((float)D);
+
+    // ---- q of the G heads, and the new k / v of this KV head
+    for (int w = threadIdx.x; w < (G + 1) * half; w += blockDim.x) {
+        const bool is_q = w < G * half;
+        const int hh = is_q ? w / half : 0, i = w % half;
+        const int base = is_q ? (hk * G + hh) * D : dq + hk * D;
+        const float ws = is_q ? p.sq : p.sk;
+        float a = deq_acc(p.acc, p.sx, m, p.terms, base + i, ws);
+        float c = deq_acc(p.acc, p.sx, m, p.terms, base + i + half, ws);
+        if (p.rope) {
+            const float2 cs = p.rope[(size_t)pos * half + i];
+            const float ra = a * cs.x - c * cs.y, rc = c * cs.x + a * cs.y;
+            a = ra;
+            c = rc;
+        }
+        if (is_q) {
+            q_s[hh * D + i] = a * scale;
+            q_s[hh * D + i + half] = c * scale;
+        } else {
+            k_new[i] = a;
+            k_new[i + half] = c;
+        }
+    }
+    for (int i = threadIdx.x; i < D; i += blockDim.x)
+        v_new[i] = deq_acc(p.acc, p.sx, m, p.terms, dq + dkv + hk * D + i, p.sv);
+    __syncthreads();
+    float* kc = p.k_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
+    float* vc = p.v_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
+    if (pos < p.max_seq && pos >= t0 && pos < t1)
+        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+            kc[(size_t)pos * D + i] = k_new[i];
+            vc[(size_t)pos * D + i] = v_new[i];
+        }
+
+    // ---- scores of this slice: 8 lanes per key, 16 keys per pass
+    const int l8 = threadIdx.x & 7;
+    // The loop bound is the same for every thread (the shuffles below need whole warps);
+    // key groups past the end of the slice compute on zeros and store nothing.
+    for (int tb = t0; tb < t1; tb += 16) {
+        const int t = tb + (threadIdx.x >> 3);
+        const bool valid = t < t1;
+        float kv[DL];
+#pragma unroll
+        for (int e = 0; e < DL; ++e) kv[e] = 0.f;
+        if (valid) {
+            const float* kp = (t == pos) ? k_new + l8 * DL : kc + (size_t)t * D + l8 * DL;
+#pragma unroll
+            for (int e = 0; e < DL; e += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kp + e);
+                kv[e] = k4.x; kv[e + 1] = k4.y; kv[e + 2] = k4.z; kv[e + 3] = k4.w;
+            }
+        }
+        for (int g = 0; g < G; ++g) {
+            const float* qp = q_s + g * D + l8 * DL;
+            float s = 0.f;
+#pragma unroll
+            for (int e = 0; e < DL; ++e) s += qp[e] * kv[e];
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if (valid && l8 == 0) sc[g * lcmax + (t - t0)] = s;
+        }
+    }
+    __syncthreads();
+
+    // ---- softmax statistics of the slice, one warp per head
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = t1 - t0;
+    for (int g = warp; g < G; g += 4) {
+        float mx = -INFINITY;
+        for (int i = lane; i < n; i += 32) mx = fmaxf(mx, sc[g * lcmax + i]);
+        mx = warp_max(mx);
+        float l = 0.f;
+        for (int i = lane; i < n; i += 32) {
+            const float e = __expf(sc[g * lcmax + i] - mx);
+            sc[g * lcmax + i] = e;
+            l += e;
+        }
+        l = warp_sum(l);
+        if (lane == 0) {
+            const size_t pi = ((size_t)b * p.n_heads + hk * G + g) * p.nsplit + sp;
+            p.part_m[pi] = n > 0 ? mx : -INFINITY;
+            p.part_l[pi] = l;
+        }
+    }
+    __syncthreads();
+
+    // ---- weighted V of the slice: thread d owns one output dimension
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        for (int g0 = 0; g0 < G; g0 += 4) {
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int t = t0; t < t1; ++t) {
+                const float v = (t == pos) ? v_new[d] : vc[(size_t)t * D + d];
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    if (g0 + g < G) o[g] += sc[(g0 + g) * lcmax + (t - t0)] * v;
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+                if (g0 + g < G)
+                    p.part_o[(((size_t)b * p.n_heads + hk * G + g0 + g) * p.nsplit + sp) * D + d] = o[g];
+        }
+    }
+
+    // ---- last CTA of this sequence: merge all heads, quantise the row for the o projection
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(p.counter + b, 1u) == (unsigned)(gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) p.counter[b] = 0;
+    for (int idx = threadIdx.x; idx < dq; idx += blockDim.x) {
+        const int h = idx / D, d = idx % D;
+        const size_t pb = ((size_t)b * p.n_heads + h) * p.nsplit;
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < p.nsplit; ++s2) M = fmaxf(M, __ldcg(p.part_m + pb + s2));
+        float L = 0.f, o = 0.f;
+        for (int s2 = 0; s2 < p.nsplit; ++s2) {
+            const float ms = __ldcg(p.part_m + pb + s2);
+            if (ms == -INFINITY) continue;
+            const float f = __expf(ms - M);
+            L += __ldcg(p.part_l + pb + s2) * f;
+            o += __ldcg(p.part_o + (pb + s2) * D + d) * f;
+        }
+        const float r = o / L;
+        row[idx] = r;
+        if (p.attn_out) p.attn_out[(size_t)b * dq + idx] = r;
+    }
+    __syncthreads();
+    if (p.xq)
+        quantize_row_from_smem(row, dq, p.kpad, p.terms_out, p.xq + (size_t)b * p.terms_out * p.kpad,
+                               p.sx_out + (size_t)b * p.terms_out, p.xsum_out + (size_t)b * p.terms_out, scratch);
+}
+
+int attn_decode_nsplit(int max_seq) {
+    int n = max_seq / 128;
+    return n < 8 ? 8 : (n > 32 ? 32 : n);
+}
+
+size_t attn_decode_part_floats(int batch, int n_heads, int head_dim, int max_seq) {
+    return (size_t)batch * n_heads * attn_decode_nsplit(max_seq) * (head_dim + 2);
+}
+
+template <int D>
+static int launch_attn_decode_d(const AttnDecodeParams& p, int batch, cudaStream_t st) {
+    const int G = p.n_heads / p.n_kv_heads;
+    const int lcmax = (p.max_seq + p.nsplit - 1) / p.nsplit;
+    const size_t smem = ((size_t)G * D + 2 * D + (size_t)G * lcmax + 64 + (size_t)p.n_heads * D) * sizeof(float);
+    if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured = 200 * 1024;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.n_kv_heads * p.nsplit, batch);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, attn_decode_kernel<D>, p) != cudaSuccess) {
+        ++g_launch_count;
+        return ROTOR_B200_ERR_CUDA;
+    }
+    return launch_status();
+}
+
+int launch_attn_decode(const AttnDecodeParams& p, int batch, cudaStream_t st) {
+    switch (p.head_dim) {
+        case 32: return launch_attn_decode_d<32>(p, batch, st);
+        case 64: return launch_attn_decode_d<64>(p, batch, st);
+        case 128: return launch_attn_decode_d<128>(p, batch, st);
+    }
+    return ROTOR_B200_ERR_SHAPE;
+}
+
+int configure_attention() {
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    return ROTOR_B200_OK;
 }
 
 }  // namespace rb

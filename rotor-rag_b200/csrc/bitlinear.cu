@@ -13,7 +13,7 @@
 //   MMA  : mma.sync m16n8k32 u8 x s8 -> s32; the tile IS the A fragment, 8 columns
 //          per pass at the cost of one, which also carries the residual terms of the
 //          multi-term activation quantiser.
-#include "model.cuh"
+#include "vecstage.cuh"
 
 namespace rb {
 
@@ -34,15 +34,21 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Stage `ncols` activation columns, `bytes` each, into shared memory with bulk async
-// copies signalled on an mbarrier, then wait with a bounded spin.  Returns false when
-// the wait gave up (the caller records it; results are then undefined but every access
+// Activation columns are staged into shared memory with bulk async (TMA) copies that
+// signal an mbarrier.  stage_init() may run before the producer of xq has finished;
+// stage_issue() must run after it; stage_wait() spins with a bound and returns false
+// when it gave up (the caller records it; results are then undefined but every access
 // stays in bounds).
-__device__ __forceinline__ void stage_begin(uint64_t* bar, int8_t* xs, int xs_stride, const int8_t* src,
-                                            size_t src_stride, int ncols, uint32_t bytes) {
+__device__ __forceinline__ void stage_init(uint64_t* bar) {
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)));
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+}
+
+__device__ __forceinline__ void stage_issue(uint64_t* bar, int8_t* xs, int xs_stride, const int8_t* src,
+                                            size_t src_stride, int ncols, uint32_t bytes) {
+    if (threadIdx.x == 0) {
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                      "r"(bytes * (uint32_t)ncols)
                      : "memory");
@@ -55,15 +61,19 @@ __device__ __forceinline__ void stage_begin(uint64_t* bar, int8_t* xs, int xs_st
     }
 }
 
-// Call after a __syncthreads() that follows stage_begin.
+// Call after a __syncthreads() that follows stage_issue.
 __device__ __forceinline__ bool stage_wait(uint64_t* bar) {
     uint32_t ok = 0;
-    for (int spin = 0; spin < (1 << 20) && !ok; ++spin)
+    const long long start = clock64();
+    // bounded: gives up after ~2e8 SM cycles (about 0.1 s) instead of waiting for ever
+    while (!ok) {
         asm volatile(
             "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0; selp.u32 %0, 1, 0, p; }"
             : "=r"(ok)
             : "r"(smem_u32(bar))
             : "memory");
+        if (!ok && clock64() - start > 200000000LL) break;
+    }
     return ok != 0;
 }
 
@@ -83,8 +93,17 @@ struct AccParams {
     size_t plane_stride;   // != 0: K split s stores its partial sums to acc + s*plane_stride instead
 };
 
+// Work the last CTA of the grid does once every partial sum is stored: the vector stage
+// that consumes this product, for `rows` token rows (0 = no tail).
+struct TailParams {
+    VecStageParams vs;
+    int rows;
+    unsigned* counter;  // zero before the launch; the last CTA resets it
+};
+
 template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
-__global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(AccParams p) {
+__global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(const __grid_constant__ AccParams p,
+                                                                   const __grid_constant__ TailParams tp) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int rt = blockIdx.x;
@@ -97,7 +116,8 @@ __global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(AccParams p) 
     int* red = reinterpret_cast<int*>(smem_raw + 16);            // [WARPS][128]
     int8_t* xs = reinterpret_cast<int8_t*>(smem_raw + 16 + WARPS * 128 * 4);
 
-    stage_begin(bar, xs, xs_stride, p.xq + (size_t)kt0 * TILE_K, (size_t)p.nkt * TILE_K, p.ncols, (uint32_t)ks);
+    pdl_trigger();
+    stage_init(bar);
 
     const uint4* trow = p.tiles + ((size_t)rt * p.nkt) * 32 + lane;
 
@@ -117,6 +137,8 @@ __global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(AccParams p) 
 #pragma unroll
     for (int u = 0; u < UMAX; ++u)
         if (base + u * WARPS < kt1) wv[u] = ld_stream_v4(trow + (size_t)(base + u * WARPS) * 32);
+    pdl_wait();  // weights above are constants; everything below depends on the producer of xq
+    stage_issue(bar, xs, xs_stride, p.xq + (size_t)kt0 * TILE_K, (size_t)p.nkt * TILE_K, p.ncols, (uint32_t)ks);
     __syncthreads();  // mbarrier initialised, bulk copies issued
     if (!stage_wait(bar) && threadIdx.x == 0) atomicMax(p.status, (unsigned)ROTOR_B200_ERR_TIMEOUT);
 
@@ -199,6 +221,28 @@ __global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(AccParams p) 
                 *dst = s;
         }
     }
+
+    // ---- tail: the last CTA to finish runs the consuming vector stage
+    if (tp.rows > 0) {
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned total = gridDim.x * gridDim.y;
+            s_last = atomicAdd(tp.counter, 1u) == total - 1;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            if (threadIdx.x == 0) *tp.counter = 0;
+            float* scratch = reinterpret_cast<float*>(smem_raw + 16 + WARPS * 128 * 4 +
+                                                      (size_t)p.ncols * xs_stride);
+            for (int m = 0; m < tp.rows; ++m) {
+                vec_stage_row(tp.vs, m, scratch + 64, scratch);
+                __syncthreads();
+            }
+        }
+    }
 }
 
 __global__ void dequant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ sx, int m, int terms,
@@ -223,10 +267,14 @@ static int ensure_status() {
     return ROTOR_B200_OK;
 }
 
+int g_use_pdl = 0;  // programmatic dependent launch for the kernels that call pdl_wait()
+
 template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
-static int launch_acc(const AccParams& p, int nrt, int ksplit, cudaStream_t st) {
+static int launch_acc(const AccParams& p, const TailParams& tp, int nrt, int ksplit, cudaStream_t st) {
     auto kern = bitlinear_acc_kernel<WARPS, UMAX, USE_MMA, NCOL>;
-    const size_t smem = 16 + WARPS * 128 * 4 + (size_t)p.ncols * (p.kt_per_split * TILE_K + XS_PAD);
+    size_t smem = 16 + WARPS * 128 * 4 + (size_t)p.ncols * (p.kt_per_split * TILE_K + XS_PAD);
+    if (tp.rows > 0) smem += (64 + (size_t)tp.vs.n) * sizeof(float);
+    if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     if (smem > 48 * 1024) {
         static size_t configured = 0;
         if (smem > configured) {
@@ -234,7 +282,20 @@ static int launch_acc(const AccParams& p, int nrt, int ksplit, cudaStream_t st) 
             configured = 200 * 1024;
         }
     }
-    kern<<<dim3(nrt, ksplit), WARPS * 32, smem, st>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nrt, ksplit);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, p, tp) != cudaSuccess) {
+        ++g_launch_count;
+        return ROTOR_B200_ERR_CUDA;
+    }
     return launch_status();
 }
 
@@ -253,14 +314,15 @@ static int choose_ksplit(int nrt, int nkt, int ncols, int warps) {
     return ks > nkt ? nkt : ks;
 }
 
-static int dispatch_acc(const AccParams& p, int nrt, int ksplit, int variant, cudaStream_t st) {
+static int dispatch_acc(const AccParams& p, const TailParams& tp, int nrt, int ksplit, int variant,
+                        cudaStream_t st) {
     constexpr int WARPS = 4, UMAX = 8;
-    if (variant == ROTOR_B200_VARIANT_MMA) return launch_acc<WARPS, UMAX, true, 1>(p, nrt, ksplit, st);
+    if (variant == ROTOR_B200_VARIANT_MMA) return launch_acc<WARPS, UMAX, true, 1>(p, tp, nrt, ksplit, st);
     switch (p.ncols) {
-        case 1: return launch_acc<WARPS, UMAX, false, 1>(p, nrt, ksplit, st);
-        case 2: return launch_acc<WARPS, UMAX, false, 2>(p, nrt, ksplit, st);
-        case 3: return launch_acc<WARPS, UMAX, false, 3>(p, nrt, ksplit, st);
-        case 4: return launch_acc<WARPS, UMAX, false, 4>(p, nrt, ksplit, st);
+        case 1: return launch_acc<WARPS, UMAX, false, 1>(p, tp, nrt, ksplit, st);
+        case 2: return launch_acc<WARPS, UMAX, false, 2>(p, tp, nrt, ksplit, st);
+        case 3: return launch_acc<WARPS, UMAX, false, 3>(p, tp, nrt, ksplit, st);
+        case 4: return launch_acc<WARPS, UMAX, false, 4>(p, tp, nrt, ksplit, st);
     }
     return ROTOR_B200_ERR_ARG;
 }
@@ -288,6 +350,10 @@ static int pick_variant(int variant, int ncols) {
     return ncols <= 2 ? ROTOR_B200_VARIANT_DP4A : ROTOR_B200_VARIANT_MMA;
 }
 
+int gemv_cols_per_launch(int variant, int ncols) {
+    return pick_variant(variant, ncols < 8 ? ncols : 8) == ROTOR_B200_VARIANT_MMA ? 8 : 4;
+}
+
 GemvPlan plan_gemv(size_t out, size_t in, int ncols) {
     const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
     const int per_pass = ncols < 8 ? ncols : 8;
@@ -299,7 +365,8 @@ GemvPlan plan_gemv(size_t out, size_t in, int ncols) {
 }
 
 int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
-                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st) {
+                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st,
+                       const VecStageParams* tail, int tail_rows, unsigned* tail_counter) {
     int rc = ensure_status();
     if (rc) return rc;
     const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
@@ -319,7 +386,14 @@ int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* x
         p.ncols = (ncols - c0) < chunk ? (ncols - c0) : chunk;
         p.atomic = 0;
         p.plane_stride = plane_stride;
-        rc = dispatch_acc(p, nrt, plan.ksplit, variant, st);
+        TailParams tp = {};
+        if (tail && tail_rows > 0) {
+            if (ncols > chunk) return ROTOR_B200_ERR_ARG;  // a tail needs the whole product in one launch
+            tp.vs = *tail;
+            tp.rows = tail_rows;
+            tp.counter = tail_counter;
+        }
+        rc = dispatch_acc(p, tp, nrt, plan.ksplit, variant, st);
         if (rc) return rc;
     }
     return ROTOR_B200_OK;
@@ -361,7 +435,8 @@ int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int
         p.atomic = ksplit_eff > 1;
         p.plane_stride = 0;
         if (p.atomic) RB_CUDA(cudaMemsetAsync(p.acc, 0, (size_t)nc * out * sizeof(int32_t), st));
-        rc = dispatch_acc(p, nrt, ksplit_eff, variant, st);
+        TailParams tp = {};
+        rc = dispatch_acc(p, tp, nrt, ksplit_eff, variant, st);
         if (rc) return rc;
     }
     return ROTOR_B200_OK;

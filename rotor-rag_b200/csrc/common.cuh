@@ -99,6 +99,13 @@ __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
     return r;
 }
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while its
+// predecessor in the stream is still running.  pdl_trigger() lets the successor start
+// early; pdl_wait() blocks until every predecessor grid has completed and its writes are
+// visible.  Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 #endif  // __CUDACC__
 
 }  // namespace rb

@@ -37,6 +37,14 @@ struct Ctx {
     int32_t* accA;  // q/k/v and gate/up accumulators
     int32_t* accB;  // o and down accumulators
     int* d_pos;
+    float2* rope;        // cos/sin table, or null
+    float2* rope_buf;    // storage for it
+    float* part_o;       // decode-attention partials
+    float* part_m;
+    float* part_l;
+    int nsplit;
+    int max_batch;
+    unsigned* counters;  // [8 + max_batch] zeroed words for last-CTA tails
 };
 
 struct Model {
@@ -111,6 +119,25 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     c.accA = cv.take<int32_t>(pa1 > pa2 ? pa1 : pa2);
     c.accB = cv.take<int32_t>(pb1 > pb2 ? pb1 : pb2);
     c.d_pos = cv.take<int>(1);
+    c.rope_buf = cv.take<float2>((size_t)c.max_seq * (c.head_dim / 2));
+    c.nsplit = attn_decode_nsplit(c.max_seq);
+    const size_t heads = (size_t)c.max_batch * c.n_heads * c.nsplit;
+    c.part_o = cv.take<float>(heads * c.head_dim);
+    c.part_m = cv.take<float>(heads);
+    c.part_l = cv.take<float>(heads);
+    c.counters = cv.take<unsigned>(8 + (size_t)c.max_batch);
+}
+
+// One-time device initialisation of a carved context: tail counters and the rotary table.
+static int init_ctx(Ctx& c, cudaStream_t st) {
+    RB_CUDA(cudaMemsetAsync(c.counters, 0, (8 + (size_t)c.max_batch) * sizeof(unsigned), st));
+    c.rope = nullptr;
+    if (c.rope_theta > 0.f) {
+        int rc = launch_rope_table(c.rope_buf, c.max_seq, c.head_dim, c.rope_theta, st);
+        if (rc) return rc;
+        c.rope = c.rope_buf;
+    }
+    return ROTOR_B200_OK;
 }
 
 static void carve(Model& m, unsigned char* base, size_t* total) {
@@ -133,6 +160,7 @@ static int derive(Model& m) {
         return ROTOR_B200_ERR_ARG;
     int rc = derive_ctx(m.c, c.d_model, c.n_heads, c.n_kv_heads, c.d_ff, c.act_terms);
     if (rc) return rc;
+    m.c.max_batch = c.max_batch;
     if (c.d_model % 256) return ROTOR_B200_ERR_SHAPE;  // LM head reads 256 columns per warp step
     m.c.ffn_act = c.ffn_act;
     m.c.causal = c.causal;
@@ -170,16 +198,27 @@ __global__ void advance_kernel(const long long* cur, long long* log, int batch, 
         if (rc_) return rc_;      \
     } while (0)
 
+// Largest row a fused tail keeps in shared memory next to the staged activations.
+constexpr int TAIL_MAX_N = 12288;
+
+// One BitLinear product into partial planes.  When `tail` is given and the product is a
+// single launch with few rows, the consuming vector stage runs in the product's last CTA
+// (*tail_done = true); the stage reads the product through tail->acc, which is filled here.
 static int gemv(Ctx& c, const void* tiles, size_t out, size_t in, int ncols, int xs, int32_t* acc, AccView* view,
-                cudaStream_t st) {
+                cudaStream_t st, VecStageParams* tail = nullptr, int tail_rows = 0, unsigned* counter = nullptr,
+                bool* tail_done = nullptr) {
     GemvPlan plan = plan_gemv(out, in, ncols < 8 ? ncols : 8);
     const size_t plane_stride = (size_t)ncols * out;
-    RB_TRY(launch_gemv_planes(tiles, out, in, c.xq, c.xsum[xs], ncols, acc, plane_stride, plan, c.variant, st));
     view->acc = acc;
     view->plane_stride = plane_stride;
     view->planes = plan.ksplit;
     view->out = (int)out;
-    return ROTOR_B200_OK;
+    const bool fuse = tail && tail_rows > 0 && tail_rows <= 4 && tail->n <= TAIL_MAX_N &&
+                      ncols <= gemv_cols_per_launch(c.variant, ncols);
+    if (fuse) tail->acc = *view;
+    if (tail_done) *tail_done = fuse;
+    return launch_gemv_planes(tiles, out, in, c.xq, c.xsum[xs], ncols, acc, plane_stride, plan, c.variant, st,
+                              fuse ? tail : nullptr, fuse ? tail_rows : 0, counter);
 }
 
 static void quant_sink(const Ctx& c, VecStageParams& p, int slot, int n) {
@@ -192,12 +231,45 @@ static void quant_sink(const Ctx& c, VecStageParams& p, int slot, int n) {
 
 // Attention half of a block.  In: quantised pre-normed rows in xq/sx[0]/xsum[0].
 // Out: accumulators of the output projection (view *vo), activation scales in sx[1].
+// `tail` (optional) is the vector stage that consumes the output projection; it is fused
+// into that product when the whole product is one launch.  *tail_done tells the caller.
 static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, int seq, AccView* vo,
-                          cudaStream_t st) {
+                          cudaStream_t st, VecStageParams* tail = nullptr, bool* tail_done = nullptr) {
+    if (tail_done) *tail_done = false;
     const int rows = batch * seq, cols = rows * c.terms;
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
     AccView va;
     RB_TRY(gemv(c, L.qkv_tiles, qkv_out, c.d, cols, 0, c.accA, &va, st));
+    if (seq == 1 && batch <= c.max_batch) {
+        // generation step: dequantise, rotate, append to the cache, attend, merge and quantise in one launch
+        AttnDecodeParams dp = {};
+        dp.acc = va;
+        dp.sx = c.sx[0];
+        dp.terms = c.terms;
+        dp.sq = L.q_scale;
+        dp.sk = L.k_scale;
+        dp.sv = L.v_scale;
+        dp.n_heads = c.n_heads;
+        dp.n_kv_heads = c.n_kv_heads;
+        dp.head_dim = c.head_dim;
+        dp.max_seq = c.max_seq;
+        dp.nsplit = c.nsplit;
+        dp.past_len = c.d_pos;
+        dp.rope = c.rope;
+        dp.k_cache = L.k_cache;
+        dp.v_cache = L.v_cache;
+        dp.part_o = c.part_o;
+        dp.part_m = c.part_m;
+        dp.part_l = c.part_l;
+        dp.counter = c.counters + 8;
+        dp.xq = c.xq;
+        dp.sx_out = c.sx[1];
+        dp.xsum_out = c.xsum[1];
+        dp.terms_out = c.terms;
+        dp.kpad = (int)kpad_of(c.dq);
+        RB_TRY(launch_attn_decode(dp, batch, st));
+        return gemv(c, L.o_tiles, c.d, c.dq, cols, 1, c.accB, vo, st, tail, batch, c.counters + 0, tail_done);
+    }
     QkvFinishParams qf = {};
     qf.acc = va;
     qf.sx = c.sx[0];
@@ -211,7 +283,7 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     qf.seq = seq;
     qf.past_len = c.d_pos;
     qf.max_seq = c.max_seq;
-    qf.rope_theta = c.rope_theta;
+    qf.rope = c.rope;
     qf.q = c.qbuf;
     qf.k_cache = L.k_cache;
     qf.v_cache = L.v_cache;
@@ -236,19 +308,19 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     qa.eps = c.eps;
     quant_sink(c, qa, 1, c.dq);
     RB_TRY(launch_vec_stage(qa, rows, st));
-    return gemv(c, L.o_tiles, c.d, c.dq, cols, 1, c.accB, vo, st);
+    return gemv(c, L.o_tiles, c.d, c.dq, cols, 1, c.accB, vo, st, tail, rows, c.counters + 0, tail_done);
 }
 
 // FFN half of a block.  In: quantised pre-normed rows in xq/sx[0]/xsum[0].
 // Out: accumulators of the down projection (view *vd), activation scales in sx[1].
-static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView* vd, cudaStream_t st) {
+// `tail` (optional) is the vector stage that consumes the down projection.
+static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView* vd, cudaStream_t st,
+                    VecStageParams* tail = nullptr, bool* tail_done = nullptr) {
     const int cols = rows * c.terms;
     AccView va;
-    RB_TRY(gemv(c, L.gate_up_tiles, 2 * (size_t)c.ff, c.d, cols, 0, c.accA, &va, st));
     VecStageParams fp = {};
     fp.mode = VS_FFN;
     fp.n = c.ff;
-    fp.acc = va;
     fp.sx_in = c.sx[0];
     fp.terms = c.terms;
     fp.wscale0 = L.gate_scale;
@@ -257,8 +329,14 @@ static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView
     fp.norm1 = L.ffn_sub_norm;
     fp.eps = c.eps;
     quant_sink(c, fp, 1, c.ff);
-    RB_TRY(launch_vec_stage(fp, rows, st));
-    return gemv(c, L.down_tiles, c.d, c.ff, cols, 1, c.accB, vd, st);
+    bool fused = false;
+    RB_TRY(gemv(c, L.gate_up_tiles, 2 * (size_t)c.ff, c.d, cols, 0, c.accA, &va, st, &fp, rows, c.counters + 1,
+                &fused));
+    if (!fused) {
+        fp.acc = va;
+        RB_TRY(launch_vec_stage(fp, rows, st));
+    }
+    return gemv(c, L.down_tiles, c.d, c.ff, cols, 1, c.accB, vd, st, tail, rows, c.counters + 2, tail_done);
 }
 
 // Blocks [l0, l1) on the residual stream c.h, whose pre-normed quantised copy is already in
@@ -271,11 +349,10 @@ static int run_blocks(Ctx& c, const rotor_b200_layer_weights* layers, int l0, in
     for (int l = l0; l < l1; ++l) {
         const rotor_b200_layer_weights& L = layers[l];
         AccView vo, vd;
-        RB_TRY(attention_part(c, L, batch, seq, &vo, st));
+        bool fused = false;
         VecStageParams op = {};
         op.mode = VS_OPROJ;
         op.n = c.d;
-        op.acc = vo;
         op.sx_in = c.sx[1];
         op.terms = c.terms;
         op.wscale0 = L.o_scale;
@@ -284,12 +361,14 @@ static int run_blocks(Ctx& c, const rotor_b200_layer_weights* layers, int l0, in
         op.norm1 = L.post_attn_norm;
         op.eps = c.eps;
         quant_sink(c, op, 0, c.d);
-        RB_TRY(launch_vec_stage(op, rows, st));
-        RB_TRY(ffn_part(c, L, rows, &vd, st));
+        RB_TRY(attention_part(c, L, batch, seq, &vo, st, &op, &fused));
+        if (!fused) {
+            op.acc = vo;
+            RB_TRY(launch_vec_stage(op, rows, st));
+        }
         VecStageParams dn = {};
         dn.mode = VS_DOWN;
         dn.n = c.d;
-        dn.acc = vd;
         dn.sx_in = c.sx[1];
         dn.terms = c.terms;
         dn.wscale0 = L.down_scale;
@@ -301,7 +380,11 @@ static int run_blocks(Ctx& c, const rotor_b200_layer_weights* layers, int l0, in
             dn.y_out = c.hn;
         else
             quant_sink(c, dn, 0, c.d);
-        RB_TRY(launch_vec_stage(dn, rows, st));
+        RB_TRY(ffn_part(c, L, rows, &vd, st, &dn, &fused));
+        if (!fused) {
+            dn.acc = vd;
+            RB_TRY(launch_vec_stage(dn, rows, st));
+        }
     }
     return ROTOR_B200_OK;
 }
@@ -400,7 +483,9 @@ int rotor_b200_model_create(const rotor_b200_model_config* cfg, const rotor_b200
     m->embed = (const __nv_bfloat16*)embed_bf16;
     m->final_norm = final_norm;
     // one-time kernel configuration happens here so that nothing but launches runs inside a capture
-    if ((rc = configure_gemv_kernels()) || (rc = configure_vec_stage()) || (rc = configure_lmhead())) {
+    if ((rc = configure_gemv_kernels()) || (rc = configure_vec_stage()) || (rc = configure_lmhead()) ||
+        (rc = configure_attention()) || (rc = init_ctx(m->c, nullptr)) ||
+        (cudaDeviceSynchronize() != cudaSuccess ? (rc = ROTOR_B200_ERR_CUDA) : 0)) {
         free(m->layers);
         delete m;
         return rc;
@@ -498,6 +583,15 @@ int rotor_b200_model_read_tokens(void* handle, int first_step, int count, int64_
     return ROTOR_B200_OK;
 }
 
+/* Programmatic dependent launch for the kernels of the decode chain: 1 lets each kernel start
+ * (and prefetch its weight tiles) while its predecessor drains.  Applies to later launches and
+ * to graphs captured afterwards.  Returns the previous setting. */
+int rotor_b200_set_pdl(int enable) {
+    const int old = g_use_pdl;
+    g_use_pdl = enable ? 1 : 0;
+    return old;
+}
+
 int rotor_b200_model_position(void* handle) {
     Model* m = (Model*)handle;
     return m ? m->pos : -1;
@@ -537,30 +631,38 @@ int rotor_b200_model_forward_hidden(void* handle, const float* hidden_in, int ba
 }
 
 /* Workspace for the two stand-alone block halves below. */
-size_t rotor_b200_block_workspace_bytes(int d_model, int n_heads, int n_kv_heads, int d_ff, int terms, int rows) {
-    Ctx c;
+static int block_derive(Ctx& c, const rotor_b200_model_config* cfg) {
     memset(&c, 0, sizeof(c));
-    if (rows <= 0 || derive_ctx(c, d_model, n_heads, n_kv_heads, d_ff, terms)) return 0;
-    Carve cv{nullptr, 0};
-    carve_ctx(c, cv, (size_t)rows);
-    return cv.off;
-}
-
-static int block_ctx(Ctx& c, const rotor_b200_model_config* cfg, int rows, void* workspace, size_t workspace_bytes) {
-    memset(&c, 0, sizeof(c));
+    if (cfg->max_seq <= 0 || cfg->max_batch <= 0) return ROTOR_B200_ERR_ARG;
     int rc = derive_ctx(c, cfg->d_model, cfg->n_heads, cfg->n_kv_heads, cfg->d_ff, cfg->act_terms);
     if (rc) return rc;
     c.ffn_act = cfg->ffn_act;
     c.causal = cfg->causal;
     c.variant = cfg->gemv_variant;
     c.max_seq = cfg->max_seq;
+    c.max_batch = cfg->max_batch;
     c.rope_theta = cfg->rope_theta;
     c.eps = cfg->eps;
+    return ROTOR_B200_OK;
+}
+
+size_t rotor_b200_block_workspace_bytes(const rotor_b200_model_config* cfg, int rows) {
+    Ctx c;
+    if (!cfg || rows <= 0 || block_derive(c, cfg)) return 0;
+    Carve cv{nullptr, 0};
+    carve_ctx(c, cv, (size_t)rows);
+    return cv.off;
+}
+
+static int block_ctx(Ctx& c, const rotor_b200_model_config* cfg, int rows, void* workspace, size_t workspace_bytes,
+                     cudaStream_t st) {
+    int rc = block_derive(c, cfg);
+    if (rc) return rc;
     Carve cv{(unsigned char*)workspace, 0};
     carve_ctx(c, cv, (size_t)rows);
     if (cv.off > workspace_bytes) return ROTOR_B200_ERR_WORKSPACE;
-    if ((rc = configure_gemv_kernels()) || (rc = configure_vec_stage())) return rc;
-    return ROTOR_B200_OK;
+    if ((rc = configure_gemv_kernels()) || (rc = configure_vec_stage()) || (rc = configure_attention())) return rc;
+    return init_ctx(c, st);
 }
 
 /* GatedFFN.forward (src/rotor/transformer.py:320-341) on device rows x float32 [rows][d_model]
@@ -575,8 +677,8 @@ int rotor_b200_ffn_forward(const rotor_b200_model_config* cfg, const rotor_b200_
     RB_REQUIRE(layer->gate_up_tiles && layer->down_tiles && layer->ffn_sub_norm);
     RB_REQUIRE(((uintptr_t)workspace & 255) == 0);
     Ctx c;
-    RB_TRY(block_ctx(c, cfg, rows, workspace, workspace_bytes));
     cudaStream_t st = as_stream(stream);
+    RB_TRY(block_ctx(c, cfg, rows, workspace, workspace_bytes, st));
     VecStageParams e = {};
     e.mode = VS_PLAIN;
     e.n = c.d;
@@ -613,8 +715,8 @@ int rotor_b200_attention_forward(const rotor_b200_model_config* cfg, const rotor
     RB_REQUIRE(((uintptr_t)workspace & 255) == 0);
     const int rows = batch * seq;
     Ctx c;
-    RB_TRY(block_ctx(c, cfg, rows, workspace, workspace_bytes));
     cudaStream_t st = as_stream(stream);
+    RB_TRY(block_ctx(c, cfg, rows, workspace, workspace_bytes, st));
     set_int_kernel<<<1, 1, 0, st>>>(c.d_pos, past_len);
     VecStageParams e = {};
     e.mode = VS_PLAIN;

@@ -53,8 +53,14 @@ struct GemvPlan {
     int kt_per_split;
 };
 GemvPlan plan_gemv(size_t out, size_t in, int ncols);
+// `tail` (optional): vector stage the last CTA runs for `tail_rows` rows once the product
+// is complete; tail_counter is a zeroed device word.  Only valid when the product fits one
+// launch (ncols <= 8 for the tensor-core variant, <= 4 for the dot-product variant).
 int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
-                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st);
+                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st,
+                       const VecStageParams* tail = nullptr, int tail_rows = 0, unsigned* tail_counter = nullptr);
+int gemv_cols_per_launch(int variant, int ncols);
+extern int g_use_pdl;
 
 struct QkvFinishParams {
     AccView acc;          // rows of the stacked [q;k;v] product
@@ -65,12 +71,39 @@ struct QkvFinishParams {
     int seq;              // tokens per sequence in this call
     const int* past_len;  // device scalar: tokens already cached
     int max_seq;          // cache capacity per sequence
-    float rope_theta;     // 0 = none
+    const float2* rope;   // cos/sin table [max_seq][head_dim/2], or null for no rotation
     float* q;             // [rows][n_heads*head_dim]
     float* k_cache;       // [batch][n_kv][max_seq][head_dim]
     float* v_cache;
 };
 int launch_qkv_finish(const QkvFinishParams& p, int rows, cudaStream_t st);
+int launch_rope_table(float2* table, int max_seq, int head_dim, float theta, cudaStream_t st);
+
+struct AttnDecodeParams {
+    AccView acc;          // stacked [q;k;v] product of one token per sequence
+    const float* sx;
+    int terms;
+    float sq, sk, sv;
+    int n_heads, n_kv_heads, head_dim, max_seq, nsplit;
+    const int* past_len;
+    const float2* rope;
+    float* k_cache;
+    float* v_cache;
+    float* part_o;        // [batch][n_heads][nsplit][head_dim]
+    float* part_m;        // [batch][n_heads][nsplit]
+    float* part_l;
+    unsigned* counter;    // [batch], zero before the launch
+    float* attn_out;      // optional float copy of the merged rows [batch][n_heads*head_dim]
+    int8_t* xq;           // quantised merged rows for the output projection
+    float* sx_out;
+    int32_t* xsum_out;
+    int terms_out;
+    int kpad;
+};
+int launch_attn_decode(const AttnDecodeParams& p, int batch, cudaStream_t st);
+int attn_decode_nsplit(int max_seq);
+size_t attn_decode_part_floats(int batch, int n_heads, int head_dim, int max_seq);
+int configure_attention();
 
 struct AttnParams {
     const float* q;       // [rows][n_heads*head_dim]

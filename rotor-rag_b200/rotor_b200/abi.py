@@ -95,7 +95,8 @@ _SIGNATURES.update({
     "rotor_b200_model_decode_steps": (_i, [_p, _i, _i, _p]),
     "rotor_b200_model_read_tokens": (_i, [_p, _i, _i, _p, _p]),
     "rotor_b200_model_position": (_i, [_p]),
-    "rotor_b200_block_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
+    "rotor_b200_block_workspace_bytes": (_sz, [_cfgp, _i]),
+    "rotor_b200_set_pdl": (_i, [_i]),
     "rotor_b200_ffn_forward": (_i, [_cfgp, _lwp, _p, _p, _i, _p, _p, _sz, _p]),
     "rotor_b200_attention_forward": (_i, [_cfgp, _lwp, _p, _i, _i, _i, _p, _p, _sz, _p]),
 })
@@ -142,3 +143,12 @@ def require_cuda():
     if not torch.cuda.is_available():
         raise RotorB200Error("no CUDA device: the rotor_b200 path runs on a B200 only (no CPU fallback)")
     return torch
+
+
+def set_pdl(enable: bool) -> bool:
+    """Programmatic dependent launch for the decode chain (see rotor_b200_set_pdl)."""
+    return bool(lib.rotor_b200_set_pdl(int(bool(enable))))
+
+
+if os.environ.get("ROTOR_B200_PDL") is not None:
+    set_pdl(os.environ["ROTOR_B200_PDL"] not in ("", "0"))

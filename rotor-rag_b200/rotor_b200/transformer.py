@@ -188,10 +188,9 @@ class _BlockBase:
                                max_batch=max_batch, max_seq=max_seq, max_rows=rows,
                                gemv_variant=sem.gemv_variant)
 
-    def _workspace_for(self, sem, rows):
+    def _workspace_for(self, cfg, rows):
         torch = abi.require_cuda()
-        need = lib.rotor_b200_block_workspace_bytes(self.d_model, self.n_heads, self.n_kv_heads, self.d_ff,
-                                                    sem.act_terms, rows)
+        need = lib.rotor_b200_block_workspace_bytes(C.byref(cfg), rows)
         if need == 0:
             raise RotorB200Error("shape not supported by the GPU path (head_dim must be 32/64/128, "
                                  "projection widths multiples of 16)")
@@ -282,7 +281,7 @@ class MultiHeadAttention(_BlockBase):
         self.fill_layer_struct(lw)
         xd = ops.to_device(x.reshape(rows, self.d_model), torch.float32)
         y = torch.empty_like(xd)
-        ws = self._workspace_for(sem, rows)
+        ws = self._workspace_for(cfg, rows)
         check(lib.rotor_b200_attention_forward(C.byref(cfg), C.byref(lw), ptr(xd), batch, seq, past, ptr(y),
                                                ptr(ws), ws.numel(), abi.stream()), "attention_forward")
         out = y.cpu().numpy().reshape(batch, seq, self.d_model)
@@ -344,7 +343,7 @@ class GatedFFN(_BlockBase):
         lw = abi.LayerWeights()
         self.fill_layer_struct(lw)
         y = torch.empty_like(xd)
-        ws = self._workspace_for(sem, rows)
+        ws = self._workspace_for(cfg, rows)
         check(lib.rotor_b200_ffn_forward(C.byref(cfg), C.byref(lw),
                                          ptr(pre_norm.device_weight()) if pre_norm is not None else None,
                                          ptr(xd), rows, ptr(y), ptr(ws), ws.numel(), abi.stream()), "ffn_forward")
