@@ -13,8 +13,35 @@
 
 namespace rb {
 
+template <int TERMS, int PLANES>
+__device__ __forceinline__ float deq_acc_t(const AccView& a, const float* __restrict__ sx, int m, int o, float wscale) {
+    int s[TERMS];
+    float f[TERMS];
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) {
+        const size_t col = (size_t)m * TERMS + t;
+        s[t] = 0;
+#pragma unroll
+        for (int p = 0; p < PLANES; ++p) s[t] += __ldcg(&a.acc[(size_t)p * a.plane_stride + col * a.out + o]);
+        f[t] = __ldcg(&sx[col]);
+    }
+    float v = 0.f;
+#pragma unroll
+    for (int t = 0; t < TERMS; ++t) v += (float)s[t] * f[t];
+    return v * wscale;
+}
+
+// Dequantised element o of token row m.  The common (terms, planes) pairs are straight-line
+// code so that independent calls overlap their loads.
 __device__ __forceinline__ float deq_acc(const AccView& a, const float* __restrict__ sx, int m, int terms, int o,
                                          float wscale) {
+    if (a.planes == 1) {
+        if (terms == 1) return deq_acc_t<1, 1>(a, sx, m, o, wscale);
+        if (terms == 3) return deq_acc_t<3, 1>(a, sx, m, o, wscale);
+    } else if (a.planes == 2) {
+        if (terms == 1) return deq_acc_t<1, 2>(a, sx, m, o, wscale);
+        if (terms == 3) return deq_acc_t<3, 2>(a, sx, m, o, wscale);
+    }
     float v = 0.f;
     for (int t = 0; t < terms; ++t) {
         const size_t col = (size_t)m * terms + t;
@@ -292,15 +319,27 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     }
     __syncthreads();
 
-    // ---- weighted V of the slice: thread d owns one output dimension
+    // ---- weighted V of the slice: thread d owns one output dimension; V rows are fetched
+    // eight at a time so that the loads overlap instead of queueing behind each other
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         for (int g0 = 0; g0 < G; g0 += 4) {
             float o[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int t = t0; t < t1; ++t) {
-                const float v = (t == pos) ? v_new[d] : vc[(size_t)t * D + d];
+            for (int tb = t0; tb < t1; tb += 8) {
+                float vv[8];
 #pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    if (g0 + g < G) o[g] += sc[(g0 + g) * lcmax + (t - t0)] * v;
+                for (int u = 0; u < 8; ++u) {
+                    const int t = tb + u;
+                    vv[u] = t < t1 ? ((t == pos) ? v_new[d] : vc[(size_t)t * D + d]) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int t = tb + u;
+                    if (t < t1) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                            if (g0 + g < G) o[g] += sc[(g0 + g) * lcmax + (t - t0)] * vv[u];
+                    }
+                }
             }
 #pragma unroll
             for (int g = 0; g < 4; ++g)
@@ -310,6 +349,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     }
 
     // ---- last CTA of this sequence: merge all heads, quantise the row for the o projection
+    // (skipped when the consumer merges the partials itself: counter == null)
+    if (!p.counter) return;
     __shared__ int s_last;
     __threadfence();
     __syncthreads();
@@ -318,22 +359,55 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     if (!s_last) return;
     __threadfence();
     if (threadIdx.x == 0) p.counter[b] = 0;
-    for (int idx = threadIdx.x; idx < dq; idx += blockDim.x) {
-        const int h = idx / D, d = idx % D;
-        const size_t pb = ((size_t)b * p.n_heads + h) * p.nsplit;
+    // merge weights of every (head, slice): f = exp(m_s - M) / L, all loads of a phase in flight together
+    float* wf = row + dq;              // [n_heads][nsplit]
+    float* wl = wf + p.n_heads * p.nsplit;
+    const size_t hb = (size_t)b * p.n_heads * p.nsplit;
+    for (int e = threadIdx.x; e < p.n_heads * p.nsplit; e += blockDim.x) {
+        wf[e] = __ldcg(p.part_m + hb + e);
+        wl[e] = __ldcg(p.part_l + hb + e);
+    }
+    __syncthreads();
+    for (int h = threadIdx.x; h < p.n_heads; h += blockDim.x) {
         float M = -INFINITY;
-        for (int s2 = 0; s2 < p.nsplit; ++s2) M = fmaxf(M, __ldcg(p.part_m + pb + s2));
-        float L = 0.f, o = 0.f;
+        for (int s2 = 0; s2 < p.nsplit; ++s2) M = fmaxf(M, wf[h * p.nsplit + s2]);
+        float L = 0.f;
         for (int s2 = 0; s2 < p.nsplit; ++s2) {
-            const float ms = __ldcg(p.part_m + pb + s2);
-            if (ms == -INFINITY) continue;
-            const float f = __expf(ms - M);
-            L += __ldcg(p.part_l + pb + s2) * f;
-            o += __ldcg(p.part_o + (pb + s2) * D + d) * f;
+            const float ms = wf[h * p.nsplit + s2];
+            const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
+            L += wl[h * p.nsplit + s2] * f;
+            wf[h * p.nsplit + s2] = f;
         }
-        const float r = o / L;
-        row[idx] = r;
-        if (p.attn_out) p.attn_out[(size_t)b * dq + idx] = r;
+        const float inv = 1.0f / L;
+        for (int s2 = 0; s2 < p.nsplit; ++s2) wf[h * p.nsplit + s2] *= inv;
+    }
+    __syncthreads();
+    constexpr int MU = 4;
+    for (int i0 = threadIdx.x; i0 < dq; i0 += MU * blockDim.x) {
+        float o[MU];
+#pragma unroll
+        for (int u = 0; u < MU; ++u) o[u] = 0.f;
+        for (int s2 = 0; s2 < p.nsplit; ++s2) {
+            float pv[MU];
+#pragma unroll
+            for (int u = 0; u < MU; ++u) {
+                const int idx = i0 + u * blockDim.x;
+                pv[u] = idx < dq ? __ldcg(p.part_o + (hb + (size_t)(idx / D) * p.nsplit + s2) * D + idx % D) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < MU; ++u) {
+                const int idx = i0 + u * blockDim.x;
+                if (idx < dq) o[u] += pv[u] * wf[(idx / D) * p.nsplit + s2];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < MU; ++u) {
+            const int idx = i0 + u * blockDim.x;
+            if (idx < dq) {
+                row[idx] = o[u];
+                if (p.attn_out) p.attn_out[(size_t)b * dq + idx] = o[u];
+            }
+        }
     }
     __syncthreads();
     if (p.xq)
@@ -354,7 +428,8 @@ template <int D>
 static int launch_attn_decode_d(const AttnDecodeParams& p, int batch, cudaStream_t st) {
     const int G = p.n_heads / p.n_kv_heads;
     const int lcmax = (p.max_seq + p.nsplit - 1) / p.nsplit;
-    const size_t smem = ((size_t)G * D + 2 * D + (size_t)G * lcmax + 64 + (size_t)p.n_heads * D) * sizeof(float);
+    const size_t smem = ((size_t)G * D + 2 * D + (size_t)G * lcmax + 64 + (size_t)p.n_heads * D +
+                         2 * (size_t)p.n_heads * p.nsplit) * sizeof(float);
     if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     static size_t configured = 48 * 1024;
     if (smem > configured) {

@@ -13,26 +13,10 @@
 //   MMA  : mma.sync m16n8k32 u8 x s8 -> s32; the tile IS the A fragment, 8 columns
 //          per pass at the cost of one, which also carries the residual terms of the
 //          multi-term activation quantiser.
-#include "vecstage.cuh"
+#include "gemv_core.cuh"
+#include "model.cuh"
 
 namespace rb {
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 // Activation columns are staged into shared memory with bulk async (TMA) copies that
 // signal an mbarrier.  stage_init() may run before the producer of xq has finished;
@@ -77,8 +61,6 @@ __device__ __forceinline__ bool stage_wait(uint64_t* bar) {
     return ok != 0;
 }
 
-constexpr int XS_PAD = 16;  // bytes between staged columns: keeps 128-bit fragment loads conflict-free
-
 struct AccParams {
     const uint4* tiles;
     const int8_t* xq;      // [ncols][kpad]
@@ -93,17 +75,8 @@ struct AccParams {
     size_t plane_stride;   // != 0: K split s stores its partial sums to acc + s*plane_stride instead
 };
 
-// Work the last CTA of the grid does once every partial sum is stored: the vector stage
-// that consumes this product, for `rows` token rows (0 = no tail).
-struct TailParams {
-    VecStageParams vs;
-    int rows;
-    unsigned* counter;  // zero before the launch; the last CTA resets it
-};
-
 template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
-__global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(const __grid_constant__ AccParams p,
-                                                                   const __grid_constant__ TailParams tp) {
+__global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(const __grid_constant__ AccParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int rt = blockIdx.x;
@@ -111,6 +84,7 @@ __global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(const __grid_
     const int kt1 = min(p.nkt, kt0 + p.kt_per_split);
     const int ks = (kt1 - kt0) * TILE_K;
     const int xs_stride = p.kt_per_split * TILE_K + XS_PAD;
+    const int kbase = kt0 * TILE_K;
 
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
     int* red = reinterpret_cast<int*>(smem_raw + 16);            // [WARPS][128]
@@ -137,7 +111,7 @@ __global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(const __grid_
 #pragma unroll
     for (int u = 0; u < UMAX; ++u)
         if (base + u * WARPS < kt1) wv[u] = ld_stream_v4(trow + (size_t)(base + u * WARPS) * 32);
-    pdl_wait();  // weights above are constants; everything below depends on the producer of xq
+    pdl_wait();  // weights above are constants; everything below depends on the producer kernel
     stage_issue(bar, xs, xs_stride, p.xq + (size_t)kt0 * TILE_K, (size_t)p.nkt * TILE_K, p.ncols, (uint32_t)ks);
     __syncthreads();  // mbarrier initialised, bulk copies issued
     if (!stage_wait(bar) && threadIdx.x == 0) atomicMax(p.status, (unsigned)ROTOR_B200_ERR_TIMEOUT);
@@ -148,35 +122,8 @@ __global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(const __grid_
             const int kt = base + u * WARPS;
             if (kt < kt1) {
                 const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-                const int koff = (kt - kt0) * TILE_K + 32 * t;
-                if constexpr (USE_MMA) {
-                    uint4 xa = make_uint4(0, 0, 0, 0), xb = xa;
-                    if (g < p.ncols) {
-                        const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)g * xs_stride + koff);
-                        xa = xp[0];
-                        xb = xp[1];
-                    }
-                    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t m = 0x03030303u << (2 * j);
-                        mma_u8s8(accm[j], pw[0] & m, pw[1] & m, pw[2] & m, pw[3] & m, xw[2 * j], xw[2 * j + 1]);
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < NCOL; ++c) {
-                        const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)c * xs_stride + koff);
-                        const uint4 xa = xp[0], xb = xp[1];
-                        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t m = 0x03030303u << (2 * j);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                accd[i & 1][j][c] = dp4a_us(pw[i] & m, xw[2 * j + (i >> 1)], accd[i & 1][j][c]);
-                        }
-                    }
-                }
+                const int koff = kt * TILE_K - kbase + 32 * t;
+                tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, koff, g, p.ncols, accm, accd);
             }
         }
         base += UMAX * WARPS;
@@ -222,27 +169,6 @@ __global__ void __launch_bounds__(WARPS * 32) bitlinear_acc_kernel(const __grid_
         }
     }
 
-    // ---- tail: the last CTA to finish runs the consuming vector stage
-    if (tp.rows > 0) {
-        __shared__ int s_last;
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const unsigned total = gridDim.x * gridDim.y;
-            s_last = atomicAdd(tp.counter, 1u) == total - 1;
-        }
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-            if (threadIdx.x == 0) *tp.counter = 0;
-            float* scratch = reinterpret_cast<float*>(smem_raw + 16 + WARPS * 128 * 4 +
-                                                      (size_t)p.ncols * xs_stride);
-            for (int m = 0; m < tp.rows; ++m) {
-                vec_stage_row(tp.vs, m, scratch + 64, scratch);
-                __syncthreads();
-            }
-        }
-    }
 }
 
 __global__ void dequant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ sx, int m, int terms,
@@ -270,10 +196,9 @@ static int ensure_status() {
 int g_use_pdl = 0;  // programmatic dependent launch for the kernels that call pdl_wait()
 
 template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
-static int launch_acc(const AccParams& p, const TailParams& tp, int nrt, int ksplit, cudaStream_t st) {
+static int launch_acc(const AccParams& p, int nrt, int ksplit, cudaStream_t st) {
     auto kern = bitlinear_acc_kernel<WARPS, UMAX, USE_MMA, NCOL>;
-    size_t smem = 16 + WARPS * 128 * 4 + (size_t)p.ncols * (p.kt_per_split * TILE_K + XS_PAD);
-    if (tp.rows > 0) smem += (64 + (size_t)tp.vs.n) * sizeof(float);
+    const size_t smem = 16 + WARPS * 128 * 4 + (size_t)p.ncols * (p.kt_per_split * TILE_K + XS_PAD);
     if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     if (smem > 48 * 1024) {
         static size_t configured = 0;
@@ -292,7 +217,7 @@ static int launch_acc(const AccParams& p, const TailParams& tp, int nrt, int ksp
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_use_pdl ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, kern, p, tp) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
         ++g_launch_count;
         return ROTOR_B200_ERR_CUDA;
     }
@@ -314,15 +239,14 @@ static int choose_ksplit(int nrt, int nkt, int ncols, int warps) {
     return ks > nkt ? nkt : ks;
 }
 
-static int dispatch_acc(const AccParams& p, const TailParams& tp, int nrt, int ksplit, int variant,
-                        cudaStream_t st) {
+static int dispatch_acc(const AccParams& p, int nrt, int ksplit, int variant, cudaStream_t st) {
     constexpr int WARPS = 4, UMAX = 8;
-    if (variant == ROTOR_B200_VARIANT_MMA) return launch_acc<WARPS, UMAX, true, 1>(p, tp, nrt, ksplit, st);
+    if (variant == ROTOR_B200_VARIANT_MMA) return launch_acc<WARPS, UMAX, true, 1>(p, nrt, ksplit, st);
     switch (p.ncols) {
-        case 1: return launch_acc<WARPS, UMAX, false, 1>(p, tp, nrt, ksplit, st);
-        case 2: return launch_acc<WARPS, UMAX, false, 2>(p, tp, nrt, ksplit, st);
-        case 3: return launch_acc<WARPS, UMAX, false, 3>(p, tp, nrt, ksplit, st);
-        case 4: return launch_acc<WARPS, UMAX, false, 4>(p, tp, nrt, ksplit, st);
+        case 1: return launch_acc<WARPS, UMAX, false, 1>(p, nrt, ksplit, st);
+        case 2: return launch_acc<WARPS, UMAX, false, 2>(p, nrt, ksplit, st);
+        case 3: return launch_acc<WARPS, UMAX, false, 3>(p, nrt, ksplit, st);
+        case 4: return launch_acc<WARPS, UMAX, false, 4>(p, nrt, ksplit, st);
     }
     return ROTOR_B200_ERR_ARG;
 }
@@ -365,8 +289,7 @@ GemvPlan plan_gemv(size_t out, size_t in, int ncols) {
 }
 
 int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
-                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st,
-                       const VecStageParams* tail, int tail_rows, unsigned* tail_counter) {
+                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st) {
     int rc = ensure_status();
     if (rc) return rc;
     const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
@@ -386,14 +309,7 @@ int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* x
         p.ncols = (ncols - c0) < chunk ? (ncols - c0) : chunk;
         p.atomic = 0;
         p.plane_stride = plane_stride;
-        TailParams tp = {};
-        if (tail && tail_rows > 0) {
-            if (ncols > chunk) return ROTOR_B200_ERR_ARG;  // a tail needs the whole product in one launch
-            tp.vs = *tail;
-            tp.rows = tail_rows;
-            tp.counter = tail_counter;
-        }
-        rc = dispatch_acc(p, tp, nrt, plan.ksplit, variant, st);
+        rc = dispatch_acc(p, nrt, plan.ksplit, variant, st);
         if (rc) return rc;
     }
     return ROTOR_B200_OK;
@@ -435,8 +351,7 @@ int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int
         p.atomic = ksplit_eff > 1;
         p.plane_stride = 0;
         if (p.atomic) RB_CUDA(cudaMemsetAsync(p.acc, 0, (size_t)nc * out * sizeof(int32_t), st));
-        TailParams tp = {};
-        rc = dispatch_acc(p, tp, nrt, ksplit_eff, variant, st);
+        rc = dispatch_acc(p, nrt, ksplit_eff, variant, st);
         if (rc) return rc;
     }
     return ROTOR_B200_OK;

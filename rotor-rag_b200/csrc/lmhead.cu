@@ -6,7 +6,7 @@
 // table four at a time; a lane reads 8 bf16 (one 128-bit load) per row per 256 columns
 // and keeps the activation slice it needs in shared memory.  Up to LM_ROWS token rows
 // share one pass over the table.
-#include "model.cuh"
+#include "vecstage.cuh"
 
 namespace rb {
 
@@ -27,11 +27,22 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4& u, float (&f)[8]) {
 }
 
 template <int NROWS>
-__global__ void __launch_bounds__(LM_WARPS * 32) lmhead_kernel(LmHeadParams p, int row0) {
+__global__ void __launch_bounds__(LM_WARPS * 32) lmhead_kernel(const __grid_constant__ LmHeadParams p, int row0) {
     extern __shared__ __align__(16) float xs[];  // [NROWS][d]
     const int d = p.d;
-    for (int i = threadIdx.x; i < NROWS * d; i += blockDim.x) xs[i] = p.x[(size_t)row0 * d + i];
-    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+    if (p.pro_rows > 0) {
+        // fused prologue: every CTA rebuilds the final-normed rows from the last down projection
+        float* scratch = xs + NROWS * d;
+        for (int r = 0; r < NROWS; ++r) {
+            vec_stage_row(p.pro, row0 + r, xs + r * d, scratch, blockIdx.x == 0, nullptr);
+            __syncthreads();
+        }
+    } else {
+        for (int i = threadIdx.x; i < NROWS * d; i += blockDim.x) xs[i] = __ldcg(&p.x[(size_t)row0 * d + i]);
+        __syncthreads();
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gw = blockIdx.x * LM_WARPS + warp, nw = gridDim.x * LM_WARPS;
     const int nchunk = d / 256;  // d is a multiple of 256 (checked on the host)
@@ -112,6 +123,63 @@ __global__ void __launch_bounds__(LM_WARPS * 32) lmhead_kernel(LmHeadParams p, i
         p.part_val[(size_t)(row0 + r) * p.nparts + blockIdx.x] = bv;
         p.part_idx[(size_t)(row0 + r) * p.nparts + blockIdx.x] = bi;
     }
+
+    // ---- tail (single-launch case): the last CTA merges the per-CTA picks, and when the
+    // launch closes a generation step it also logs the tokens and advances the position.
+    if (!p.tail_counter) return;
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(p.tail_counter, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) *p.tail_counter = 0;
+    __shared__ float tv[LM_WARPS];
+    __shared__ int ti[LM_WARPS];
+    for (int r = 0; r < NROWS; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < p.nparts; i += blockDim.x) {
+            const float v = __ldcg(&p.part_val[(size_t)(row0 + r) * p.nparts + i]);
+            const int id = __ldcg(&p.part_idx[(size_t)(row0 + r) * p.nparts + i]);
+            if (v > bv || (v == bv && id < bi)) {
+                bv = v;
+                bi = id;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        __syncthreads();
+        if (lane == 0) {
+            tv[warp] = bv;
+            ti[warp] = bi;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < LM_WARPS; ++w)
+                if (tv[w] > bv || (tv[w] == bv && ti[w] < bi)) {
+                    bv = tv[w];
+                    bi = ti[w];
+                }
+            p.argmax_out[row0 + r] = bi;
+            if (p.adv_log) {
+                const int st = *p.adv_step;
+                if (st < p.adv_max_log) p.adv_log[(size_t)st * NROWS + r] = bi;
+            }
+        }
+    }
+    if (p.adv_log && threadIdx.x == 0) {
+        *p.adv_pos += 1;
+        *p.adv_step += 1;
+    }
 }
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int nparts,
@@ -155,7 +223,7 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
 
 template <int NROWS>
 static int launch_lm(const LmHeadParams& p, int row0, cudaStream_t st) {
-    const size_t smem = (size_t)NROWS * p.d * sizeof(float);
+    const size_t smem = ((size_t)NROWS * p.d + (p.pro_rows > 0 ? 64 : 0)) * sizeof(float);
     if (smem > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
@@ -165,7 +233,20 @@ static int launch_lm(const LmHeadParams& p, int row0, cudaStream_t st) {
         }
         if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     }
-    lmhead_kernel<NROWS><<<LM_PARTS, LM_WARPS * 32, smem, st>>>(p, row0);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(LM_PARTS);
+    cfg.blockDim = dim3(LM_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, lmhead_kernel<NROWS>, p, row0) != cudaSuccess) {
+        ++g_launch_count;
+        return ROTOR_B200_ERR_CUDA;
+    }
     return launch_status();
 }
 
@@ -177,8 +258,16 @@ int configure_lmhead() {
     return ROTOR_B200_OK;
 }
 
-int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st) {
-    if (p.d % 256 != 0) return ROTOR_B200_ERR_SHAPE;
+int launch_lmhead(const LmHeadParams& pin, int rows, cudaStream_t st) {
+    if (pin.d % 256 != 0) return ROTOR_B200_ERR_SHAPE;
+    LmHeadParams p = pin;
+    // the fused pick needs every partial in one launch; otherwise a separate kernel merges them
+    const bool fused = p.tail_counter && p.argmax_out && rows <= LM_ROWS;
+    if (p.pro_rows > 0 && (rows > LM_ROWS || p.pro_rows != rows || p.pro.n != p.d)) return ROTOR_B200_ERR_ARG;
+    if (!fused) {
+        if (p.adv_log) return ROTOR_B200_ERR_ARG;
+        p.tail_counter = nullptr;
+    }
     int rc = ROTOR_B200_OK;
     for (int r0 = 0; r0 < rows && !rc; r0 += LM_ROWS) {
         const int n = rows - r0 < LM_ROWS ? rows - r0 : LM_ROWS;
@@ -190,7 +279,7 @@ int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st) {
         }
     }
     if (rc) return rc;
-    if (p.argmax_out) {
+    if (p.argmax_out && !fused) {
         argmax_final_kernel<<<rows, 256, 0, st>>>(p.part_val, p.part_idx, p.nparts, p.argmax_out);
         rc = launch_status();
     }

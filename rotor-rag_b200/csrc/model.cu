@@ -28,6 +28,7 @@ struct Ctx {
     float rope_theta, eps;
     size_t kmax;  // widest padded BitLinear input
     float* h;     // residual stream [rows][d]
+    float* h2;    // second copy: fused generation steps ping-pong between the two
     float* hn;    // final-normed rows
     float* qbuf;
     float* attn;
@@ -45,7 +46,14 @@ struct Ctx {
     int nsplit;
     int max_batch;
     unsigned* counters;  // [8 + max_batch] zeroed words for last-CTA tails
+    // accumulators of the fused generation step: q/k/v, o, gate/up, down.  Each is cleared by
+    // an earlier kernel of the chain; ring_cols is the column count they are currently clean for
+    int32_t* ring[4];
+    size_t ring_words[4];
+    int ring_cols;
 };
+
+constexpr int RING_MAX_COLS = 8;
 
 struct Model {
     rotor_b200_model_config cfg;
@@ -104,6 +112,7 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     const size_t d = c.d, ff = c.ff;
     const size_t qkv_out = c.dq + 2 * (size_t)c.dkv;
     c.h = cv.take<float>(rows * d);
+    c.h2 = cv.take<float>(rows * d);
     c.hn = cv.take<float>(rows * d);
     c.qbuf = cv.take<float>(rows * c.dq);
     c.attn = cv.take<float>(rows * c.dq);
@@ -126,11 +135,18 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     c.part_m = cv.take<float>(heads);
     c.part_l = cv.take<float>(heads);
     c.counters = cv.take<unsigned>(8 + (size_t)c.max_batch);
+    const size_t outs[4] = {qkv_out, d, 2 * ff, d};
+    for (int i = 0; i < 4; ++i) {
+        c.ring_words[i] = RING_MAX_COLS * outs[i];
+        c.ring[i] = cv.take<int32_t>(c.ring_words[i]);
+    }
 }
 
 // One-time device initialisation of a carved context: tail counters and the rotary table.
 static int init_ctx(Ctx& c, cudaStream_t st) {
     RB_CUDA(cudaMemsetAsync(c.counters, 0, (8 + (size_t)c.max_batch) * sizeof(unsigned), st));
+    for (int i = 0; i < 4; ++i) RB_CUDA(cudaMemsetAsync(c.ring[i], 0, c.ring_words[i] * sizeof(int32_t), st));
+    c.ring_cols = 0;
     c.rope = nullptr;
     if (c.rope_theta > 0.f) {
         int rc = launch_rope_table(c.rope_buf, c.max_seq, c.head_dim, c.rope_theta, st);
@@ -198,27 +214,16 @@ __global__ void advance_kernel(const long long* cur, long long* log, int batch, 
         if (rc_) return rc_;      \
     } while (0)
 
-// Largest row a fused tail keeps in shared memory next to the staged activations.
-constexpr int TAIL_MAX_N = 12288;
-
-// One BitLinear product into partial planes.  When `tail` is given and the product is a
-// single launch with few rows, the consuming vector stage runs in the product's last CTA
-// (*tail_done = true); the stage reads the product through tail->acc, which is filled here.
+// One BitLinear product into partial planes, activations taken from xq/xsum[xs].
 static int gemv(Ctx& c, const void* tiles, size_t out, size_t in, int ncols, int xs, int32_t* acc, AccView* view,
-                cudaStream_t st, VecStageParams* tail = nullptr, int tail_rows = 0, unsigned* counter = nullptr,
-                bool* tail_done = nullptr) {
+                cudaStream_t st) {
     GemvPlan plan = plan_gemv(out, in, ncols < 8 ? ncols : 8);
     const size_t plane_stride = (size_t)ncols * out;
     view->acc = acc;
     view->plane_stride = plane_stride;
     view->planes = plan.ksplit;
     view->out = (int)out;
-    const bool fuse = tail && tail_rows > 0 && tail_rows <= 4 && tail->n <= TAIL_MAX_N &&
-                      ncols <= gemv_cols_per_launch(c.variant, ncols);
-    if (fuse) tail->acc = *view;
-    if (tail_done) *tail_done = fuse;
-    return launch_gemv_planes(tiles, out, in, c.xq, c.xsum[xs], ncols, acc, plane_stride, plan, c.variant, st,
-                              fuse ? tail : nullptr, fuse ? tail_rows : 0, counter);
+    return launch_gemv_planes(tiles, out, in, c.xq, c.xsum[xs], ncols, acc, plane_stride, plan, c.variant, st);
 }
 
 static void quant_sink(const Ctx& c, VecStageParams& p, int slot, int n) {
@@ -231,11 +236,8 @@ static void quant_sink(const Ctx& c, VecStageParams& p, int slot, int n) {
 
 // Attention half of a block.  In: quantised pre-normed rows in xq/sx[0]/xsum[0].
 // Out: accumulators of the output projection (view *vo), activation scales in sx[1].
-// `tail` (optional) is the vector stage that consumes the output projection; it is fused
-// into that product when the whole product is one launch.  *tail_done tells the caller.
 static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, int seq, AccView* vo,
-                          cudaStream_t st, VecStageParams* tail = nullptr, bool* tail_done = nullptr) {
-    if (tail_done) *tail_done = false;
+                          cudaStream_t st) {
     const int rows = batch * seq, cols = rows * c.terms;
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
     AccView va;
@@ -268,7 +270,7 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
         dp.terms_out = c.terms;
         dp.kpad = (int)kpad_of(c.dq);
         RB_TRY(launch_attn_decode(dp, batch, st));
-        return gemv(c, L.o_tiles, c.d, c.dq, cols, 1, c.accB, vo, st, tail, batch, c.counters + 0, tail_done);
+        return gemv(c, L.o_tiles, c.d, c.dq, cols, 1, c.accB, vo, st);
     }
     QkvFinishParams qf = {};
     qf.acc = va;
@@ -308,19 +310,19 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     qa.eps = c.eps;
     quant_sink(c, qa, 1, c.dq);
     RB_TRY(launch_vec_stage(qa, rows, st));
-    return gemv(c, L.o_tiles, c.d, c.dq, cols, 1, c.accB, vo, st, tail, rows, c.counters + 0, tail_done);
+    return gemv(c, L.o_tiles, c.d, c.dq, cols, 1, c.accB, vo, st);
 }
 
 // FFN half of a block.  In: quantised pre-normed rows in xq/sx[0]/xsum[0].
 // Out: accumulators of the down projection (view *vd), activation scales in sx[1].
-// `tail` (optional) is the vector stage that consumes the down projection.
-static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView* vd, cudaStream_t st,
-                    VecStageParams* tail = nullptr, bool* tail_done = nullptr) {
+static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView* vd, cudaStream_t st) {
     const int cols = rows * c.terms;
     AccView va;
+    RB_TRY(gemv(c, L.gate_up_tiles, 2 * (size_t)c.ff, c.d, cols, 0, c.accA, &va, st));
     VecStageParams fp = {};
     fp.mode = VS_FFN;
     fp.n = c.ff;
+    fp.acc = va;
     fp.sx_in = c.sx[0];
     fp.terms = c.terms;
     fp.wscale0 = L.gate_scale;
@@ -329,14 +331,8 @@ static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView
     fp.norm1 = L.ffn_sub_norm;
     fp.eps = c.eps;
     quant_sink(c, fp, 1, c.ff);
-    bool fused = false;
-    RB_TRY(gemv(c, L.gate_up_tiles, 2 * (size_t)c.ff, c.d, cols, 0, c.accA, &va, st, &fp, rows, c.counters + 1,
-                &fused));
-    if (!fused) {
-        fp.acc = va;
-        RB_TRY(launch_vec_stage(fp, rows, st));
-    }
-    return gemv(c, L.down_tiles, c.d, c.ff, cols, 1, c.accB, vd, st, tail, rows, c.counters + 2, tail_done);
+    RB_TRY(launch_vec_stage(fp, rows, st));
+    return gemv(c, L.down_tiles, c.d, c.ff, cols, 1, c.accB, vd, st);
 }
 
 // Blocks [l0, l1) on the residual stream c.h, whose pre-normed quantised copy is already in
@@ -349,10 +345,11 @@ static int run_blocks(Ctx& c, const rotor_b200_layer_weights* layers, int l0, in
     for (int l = l0; l < l1; ++l) {
         const rotor_b200_layer_weights& L = layers[l];
         AccView vo, vd;
-        bool fused = false;
+        RB_TRY(attention_part(c, L, batch, seq, &vo, st));
         VecStageParams op = {};
         op.mode = VS_OPROJ;
         op.n = c.d;
+        op.acc = vo;
         op.sx_in = c.sx[1];
         op.terms = c.terms;
         op.wscale0 = L.o_scale;
@@ -361,14 +358,12 @@ static int run_blocks(Ctx& c, const rotor_b200_layer_weights* layers, int l0, in
         op.norm1 = L.post_attn_norm;
         op.eps = c.eps;
         quant_sink(c, op, 0, c.d);
-        RB_TRY(attention_part(c, L, batch, seq, &vo, st, &op, &fused));
-        if (!fused) {
-            op.acc = vo;
-            RB_TRY(launch_vec_stage(op, rows, st));
-        }
+        RB_TRY(launch_vec_stage(op, rows, st));
+        RB_TRY(ffn_part(c, L, rows, &vd, st));
         VecStageParams dn = {};
         dn.mode = VS_DOWN;
         dn.n = c.d;
+        dn.acc = vd;
         dn.sx_in = c.sx[1];
         dn.terms = c.terms;
         dn.wscale0 = L.down_scale;
@@ -380,19 +375,187 @@ static int run_blocks(Ctx& c, const rotor_b200_layer_weights* layers, int l0, in
             dn.y_out = c.hn;
         else
             quant_sink(c, dn, 0, c.d);
-        RB_TRY(ffn_part(c, L, rows, &vd, st, &dn, &fused));
-        if (!fused) {
-            dn.acc = vd;
-            RB_TRY(launch_vec_stage(dn, rows, st));
-        }
+        RB_TRY(launch_vec_stage(dn, rows, st));
     }
     return ROTOR_B200_OK;
 }
 
+// One generation step (one token per sequence) with every vector stage fused into the
+// prologue of the product that consumes it: 5 launches per block plus the LM head.
+//   q/k/v product   <- [embedding | previous down: residual add] + input norm + quantise
+//   attention       <- dequantise q/k/v, rotate, cache append, slice partials
+//   o product       <- merge attention partials + quantise
+//   gate/up product <- o: sub-norm, residual add, post-attention norm, quantise
+//   down product    <- gating, sub-norm, quantise
+//   LM head         <- last down: residual add, final norm; greedy pick in its last CTA
+// The residual stream alternates between c.h and c.h2 so that the CTA that writes the new
+// stream never races with CTAs still reading the old one.
+static bool fused_step_ok(const Model& m, int batch, int seq) {
+    const Ctx& c = m.c;
+    static const bool off = getenv("ROTOR_B200_NO_FUSED_STEP") != nullptr;  // measurement aid
+    return !off && seq == 1 && batch <= 4 && batch <= c.max_batch && c.terms <= 3 &&
+           batch * c.terms <= RING_MAX_COLS &&
+           fused_gemv_supported(c.d, c.ff, batch, c.terms, c.ff, 0) &&
+           fused_gemv_supported(c.d, c.dq, batch, c.terms, c.dq, c.n_heads * c.nsplit);
+}
+
+static int run_step_fused(Model& m, const long long* ids, int batch, int logits_mode, float* logits,
+                          long long* next_ids, cudaStream_t st, bool advance) {
+    Ctx& c = m.c;
+    const int d = c.d, cols = batch * c.terms;
+    const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
+    const size_t outs[4] = {qkv_out, (size_t)d, 2 * (size_t)c.ff, (size_t)d};
+    auto view = [&](int i) {
+        AccView v;
+        v.acc = c.ring[i];
+        v.plane_stride = 0;
+        v.planes = 1;
+        v.out = (int)outs[i];
+        return v;
+    };
+    // Kernel i of a block accumulates into ring[i] and clears ring[i+1] for its successor.
+    auto product = [&](int i, const void* tiles, size_t in, const VecStageParams& pro, int slot) {
+        const int nx = (i + 1) & 3;
+        return launch_fused_gemv(tiles, outs[i], in, batch, pro, c.ring[i], c.ring[nx], (size_t)cols * outs[nx],
+                                 c.sx[slot], c.xsum[slot], st);
+    };
+    VecStageParams pro;
+    for (int l = 0; l < m.cfg.n_layers; ++l) {
+        const rotor_b200_layer_weights& L = m.layers[l];
+        pro = {};
+        pro.n = d;
+        pro.eps = c.eps;
+        pro.terms_out = c.terms;
+        pro.kpad = (int)kpad_of(d);
+        pro.norm1 = L.input_norm;
+        pro.h_out = c.h;
+        if (l == 0) {
+            pro.mode = VS_EMBED;
+            pro.ids = ids;
+            pro.embed = m.embed;
+            pro.h = c.h;
+        } else {
+            pro.mode = VS_DOWN;
+            pro.acc = view(3);
+            pro.sx_in = c.sx[1];
+            pro.terms = c.terms;
+            pro.wscale0 = m.layers[l - 1].down_scale;
+            pro.h = c.h2;
+        }
+        RB_TRY(product(0, L.qkv_tiles, d, pro, 0));
+
+        AttnDecodeParams dp = {};
+        dp.acc = view(0);
+        dp.sx = c.sx[0];
+        dp.terms = c.terms;
+        dp.sq = L.q_scale;
+        dp.sk = L.k_scale;
+        dp.sv = L.v_scale;
+        dp.n_heads = c.n_heads;
+        dp.n_kv_heads = c.n_kv_heads;
+        dp.head_dim = c.head_dim;
+        dp.max_seq = c.max_seq;
+        dp.nsplit = c.nsplit;
+        dp.past_len = c.d_pos;
+        dp.rope = c.rope;
+        dp.k_cache = L.k_cache;
+        dp.v_cache = L.v_cache;
+        dp.part_o = c.part_o;
+        dp.part_m = c.part_m;
+        dp.part_l = c.part_l;
+        RB_TRY(launch_attn_decode(dp, batch, st));  // no counter: the o product merges the partials
+
+        pro = {};
+        pro.mode = VS_ATTN;
+        pro.n = c.dq;
+        pro.part_o = c.part_o;
+        pro.part_m = c.part_m;
+        pro.part_l = c.part_l;
+        pro.nsplit = c.nsplit;
+        pro.n_heads = c.n_heads;
+        pro.head_dim = c.head_dim;
+        pro.eps = c.eps;
+        pro.terms_out = c.terms;
+        pro.kpad = (int)kpad_of(c.dq);
+        RB_TRY(product(1, L.o_tiles, c.dq, pro, 1));
+
+        pro = {};
+        pro.mode = VS_OPROJ;
+        pro.n = d;
+        pro.acc = view(1);
+        pro.sx_in = c.sx[1];
+        pro.terms = c.terms;
+        pro.wscale0 = L.o_scale;
+        pro.norm0 = L.attn_sub_norm;
+        pro.h = c.h;
+        pro.h_out = c.h2;
+        pro.norm1 = L.post_attn_norm;
+        pro.eps = c.eps;
+        pro.terms_out = c.terms;
+        pro.kpad = (int)kpad_of(d);
+        RB_TRY(product(2, L.gate_up_tiles, d, pro, 0));
+
+        pro = {};
+        pro.mode = VS_FFN;
+        pro.n = c.ff;
+        pro.acc = view(2);
+        pro.sx_in = c.sx[0];
+        pro.terms = c.terms;
+        pro.wscale0 = L.gate_scale;
+        pro.wscale1 = L.up_scale;
+        pro.ffn_act = c.ffn_act;
+        pro.norm1 = L.ffn_sub_norm;
+        pro.eps = c.eps;
+        pro.terms_out = c.terms;
+        pro.kpad = (int)kpad_of(c.ff);
+        RB_TRY(product(3, L.down_tiles, c.ff, pro, 1));
+    }
+    const AccView vb = view(3);
+    // LM head: residual add + final norm in its prologue
+    LmHeadParams lp = {};
+    lp.embed = m.embed;
+    lp.vocab = m.cfg.vocab_size;
+    lp.d = d;
+    lp.logits = logits_mode == ROTOR_B200_LOGITS_NONE ? nullptr : logits;
+    lp.part_val = m.part_val;
+    lp.part_idx = m.part_idx;
+    lp.argmax_out = next_ids;
+    lp.nparts = lmhead_parts();
+    lp.tail_counter = next_ids ? c.counters + 3 : nullptr;
+    if (advance) {
+        lp.adv_log = m.tok_log;
+        lp.adv_pos = c.d_pos;
+        lp.adv_step = m.d_step;
+        lp.adv_max_log = m.max_log;
+    }
+    lp.pro = {};
+    lp.pro.mode = VS_DOWN;
+    lp.pro.n = d;
+    lp.pro.acc = vb;
+    lp.pro.sx_in = c.sx[1];
+    lp.pro.terms = c.terms;
+    lp.pro.wscale0 = m.layers[m.cfg.n_layers - 1].down_scale;
+    lp.pro.h = c.h2;
+    lp.pro.h_out = c.h;
+    lp.pro.norm1 = m.final_norm;
+    lp.pro.eps = c.eps;
+    lp.pro_rows = batch;
+    return launch_lmhead(lp, batch, st);
+}
+
 // ids: device [batch*seq]; the position is read from c.d_pos by the kernels.
 static int run_layers(Model& m, const long long* ids, int batch, int seq, int logits_mode, float* logits,
-                      long long* next_ids, cudaStream_t st) {
+                      long long* next_ids, cudaStream_t st, bool advance = false) {
     Ctx& c = m.c;
+    if (fused_step_ok(m, batch, seq) && (logits_mode != ROTOR_B200_LOGITS_NONE || next_ids)) {
+        if (c.ring_cols != batch * c.terms) {
+            // another column count used the accumulators last: restore the all-zero state.  Never
+            // reached inside a graph capture: decode_begin makes the same check before capturing.
+            for (int i = 0; i < 4; ++i) RB_CUDA(cudaMemsetAsync(c.ring[i], 0, c.ring_words[i] * sizeof(int32_t), st));
+            c.ring_cols = batch * c.terms;
+        }
+        return run_step_fused(m, ids, batch, logits_mode, logits, next_ids, st, advance);
+    }
     const int rows = batch * seq, d = c.d;
     VecStageParams e = {};
     e.mode = VS_EMBED;
@@ -429,6 +592,13 @@ static int run_layers(Model& m, const long long* ids, int batch, int seq, int lo
     lp.part_idx = m.part_idx;
     lp.argmax_out = (all && seq > 1) ? nullptr : next_ids;
     lp.nparts = lmhead_parts();
+    lp.tail_counter = c.counters + 3;
+    if (advance) {
+        lp.adv_log = m.tok_log;
+        lp.adv_pos = c.d_pos;
+        lp.adv_step = m.d_step;
+        lp.adv_max_log = m.max_log;
+    }
     return launch_lmhead(lp, lm_rows, st);
 }
 
@@ -484,7 +654,7 @@ int rotor_b200_model_create(const rotor_b200_model_config* cfg, const rotor_b200
     m->final_norm = final_norm;
     // one-time kernel configuration happens here so that nothing but launches runs inside a capture
     if ((rc = configure_gemv_kernels()) || (rc = configure_vec_stage()) || (rc = configure_lmhead()) ||
-        (rc = configure_attention()) || (rc = init_ctx(m->c, nullptr)) ||
+        (rc = configure_attention()) || (rc = configure_fused_gemv()) || (rc = init_ctx(m->c, nullptr)) ||
         (cudaDeviceSynchronize() != cudaSuccess ? (rc = ROTOR_B200_ERR_CUDA) : 0)) {
         free(m->layers);
         delete m;
@@ -521,6 +691,11 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
     Model* m = (Model*)handle;
     RB_REQUIRE(m && first_ids && batch > 0 && batch <= m->cfg.max_batch && batch <= 1024);
     RB_REQUIRE(past_len >= 0 && past_len < m->cfg.max_seq);
+    if (fused_step_ok(*m, batch, 1) && m->c.ring_cols != batch * m->c.terms) {
+        for (int i = 0; i < 4; ++i)
+            RB_CUDA(cudaMemsetAsync(m->c.ring[i], 0, m->c.ring_words[i] * sizeof(int32_t), as_stream(stream)));
+        m->c.ring_cols = batch * m->c.terms;
+    }
     begin_kernel<<<1, 1024, 0, as_stream(stream)>>>(m->cur_ids, (const long long*)first_ids, batch, m->c.d_pos,
                                                     past_len, m->d_step);
     m->pos = past_len;
@@ -530,6 +705,8 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
 }
 
 static int one_step(Model& m, cudaStream_t st) {
+    if (m.batch <= 4)  // pick, token log and position advance ride in the LM head's last CTA
+        return run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st, true);
     RB_TRY(run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st));
     advance_kernel<<<1, 1024, 0, st>>>(m.cur_ids, m.tok_log, m.batch, m.max_log, m.c.d_pos, m.d_step);
     return launch_status();

@@ -15,7 +15,7 @@ struct AccView {
     int out;
 };
 
-enum VecStageMode { VS_EMBED = 0, VS_PLAIN = 1, VS_OPROJ = 2, VS_FFN = 3, VS_DOWN = 4, VS_DEQ = 5 };
+enum VecStageMode { VS_EMBED = 0, VS_PLAIN = 1, VS_OPROJ = 2, VS_FFN = 3, VS_DOWN = 4, VS_DEQ = 5, VS_ATTN = 6 };
 
 struct VecStageParams {
     int mode;
@@ -30,7 +30,13 @@ struct VecStageParams {
     float wscale0, wscale1;      // weight scale(s) of the previous product
     int ffn_act;
     const float* norm0;          // VS_OPROJ: sub-norm weight
-    float* h;                    // residual stream [rows][n] (read/modify/write)
+    float* h;                    // residual stream [rows][n] (read)
+    float* h_out;                // where the updated stream goes (null = in place, h)
+    // VS_ATTN: merge the decode-attention partials of row m into the row
+    const float* part_o;         // [rows][n_heads][nsplit][head_dim]
+    const float* part_m;         // [rows][n_heads][nsplit]
+    const float* part_l;
+    int nsplit, n_heads, head_dim;
     // sinks
     const float* norm1;          // optional pre-norm weight applied before the sinks
     float eps;
@@ -53,13 +59,16 @@ struct GemvPlan {
     int kt_per_split;
 };
 GemvPlan plan_gemv(size_t out, size_t in, int ncols);
-// `tail` (optional): vector stage the last CTA runs for `tail_rows` rows once the product
-// is complete; tail_counter is a zeroed device word.  Only valid when the product fits one
-// launch (ncols <= 8 for the tensor-core variant, <= 4 for the dot-product variant).
 int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
-                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st,
-                       const VecStageParams* tail = nullptr, int tail_rows = 0, unsigned* tail_counter = nullptr);
+                       int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st);
 int gemv_cols_per_launch(int variant, int ncols);
+
+// Generation-step product with the consuming vector stage fused in (fused.cu).  acc must be
+// all zero on entry; zero_ptr/zero_count name a buffer this kernel clears for a later product.
+int launch_fused_gemv(const void* tiles, size_t out, size_t in, int rows, const VecStageParams& stage, int32_t* acc,
+                      int32_t* zero_ptr, size_t zero_count, float* sx_pub, int32_t* xsum_pub, cudaStream_t st);
+bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int stage_n, int stage_extra);
+int configure_fused_gemv();
 extern int g_use_pdl;
 
 struct QkvFinishParams {
@@ -127,6 +136,13 @@ struct LmHeadParams {
     int* part_idx;
     long long* argmax_out;       // [rows]
     int nparts;
+    unsigned* tail_counter;      // zeroed word: enables the fused pick when rows fit one launch
+    long long* adv_log;          // optional: token log [max_log][rows]; also advances *adv_pos, *adv_step
+    int* adv_pos;
+    int* adv_step;
+    int adv_max_log;
+    VecStageParams pro;          // fused prologue (pro_rows > 0): builds x from the last block's output
+    int pro_rows;
 };
 int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st);
 int lmhead_parts();
