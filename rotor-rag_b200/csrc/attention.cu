@@ -11,6 +11,8 @@
 #include "model.cuh"
 #include "quant.cuh"
 
+RB_TRACE_DEFINE(rotor_b200_trace_read_attn)
+
 namespace rb {
 
 template <int TERMS, int PLANES>
@@ -225,8 +227,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     float* scratch = sc + G * lcmax;    // [64]
     float* row = scratch + 64;          // [dq]   (tail only)
 
+    TraceRec tr;
+    RB_STAMP(tr, 0);
     pdl_trigger();
     pdl_wait();
+    RB_STAMP(tr, 2);
     const int pos = *p.past_len;
     const int T = min(pos + 1, p.max_seq);
     const int lc = (T + p.nsplit - 1) / p.nsplit;
@@ -235,13 +240,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     const float scale = 1.0f / sqrtf((float)D);
 
     // ---- q of the G heads, and the new k / v of this KV head
+    const float* qf = p.qkv_f ? p.qkv_f + (size_t)m * (dq + 2 * dkv) : nullptr;
     for (int w = threadIdx.x; w < (G + 1) * half; w += blockDim.x) {
         const bool is_q = w < G * half;
         const int hh = is_q ? w / half : 0, i = w % half;
         const int base = is_q ? (hk * G + hh) * D : dq + hk * D;
         const float ws = is_q ? p.sq : p.sk;
-        float a = deq_acc(p.acc, p.sx, m, p.terms, base + i, ws);
-        float c = deq_acc(p.acc, p.sx, m, p.terms, base + i + half, ws);
+        float a = qf ? __ldcg(qf + base + i) : deq_acc(p.acc, p.sx, m, p.terms, base + i, ws);
+        float c = qf ? __ldcg(qf + base + i + half) : deq_acc(p.acc, p.sx, m, p.terms, base + i + half, ws);
         if (p.rope) {
             const float2 cs = p.rope[(size_t)pos * half + i];
             const float ra = a * cs.x - c * cs.y, rc = c * cs.x + a * cs.y;
@@ -257,7 +263,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
         }
     }
     for (int i = threadIdx.x; i < D; i += blockDim.x)
-        v_new[i] = deq_acc(p.acc, p.sx, m, p.terms, dq + dkv + hk * D + i, p.sv);
+        v_new[i] = qf ? __ldcg(qf + dq + dkv + hk * D + i) : deq_acc(p.acc, p.sx, m, p.terms, dq + dkv + hk * D + i, p.sv);
     __syncthreads();
     float* kc = p.k_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
     float* vc = p.v_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
@@ -348,6 +354,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
         }
     }
 
+    RB_STAMP(tr, 5);
+    RB_TRACE_COMMIT(tr, 100);
     // ---- last CTA of this sequence: merge all heads, quantise the row for the o projection
     // (skipped when the consumer merges the partials itself: counter == null)
     if (!p.counter) return;

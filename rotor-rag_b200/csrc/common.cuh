@@ -106,6 +106,52 @@ __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Optional device-side timeline (compiled in with -DRB_TRACE): thread 0 of CTA 0 of the
+// instrumented kernels records %globaltimer stamps into a global ring for offline reading.
+#ifdef RB_TRACE
+struct TraceRec {
+    unsigned long long t[8];
+    int kind;
+    int pad;
+};
+// each instrumented .cu file holds its own ring (no relocatable device code is used)
+#define RB_TRACE_DEFINE(name)                                                         \
+    static __device__ rb::TraceRec g_trace[4096];                                       \
+    static __device__ unsigned g_trace_n;                                             \
+    extern "C" int name(void* host_buf, unsigned* n) {                                \
+        unsigned cnt = 0;                                                             \
+        cudaMemcpyFromSymbol(&cnt, g_trace_n, sizeof(cnt));                           \
+        if (cnt > 4096) cnt = 4096;                                                   \
+        cudaMemcpyFromSymbol(host_buf, g_trace, sizeof(rb::TraceRec) * cnt);            \
+        unsigned zero = 0;                                                            \
+        cudaMemcpyToSymbol(g_trace_n, &zero, sizeof(zero));                           \
+        *n = cnt;                                                                     \
+        return 0;                                                                     \
+    }
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+    return v;
+}
+#define RB_STAMP(rec, i) \
+    do {                 \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) (rec).t[i] = gtime(); \
+    } while (0)
+#define RB_TRACE_COMMIT(rec, k)                                              \
+    do {                                                                     \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {        \
+            (rec).kind = (k);                                                \
+            unsigned idx_ = atomicAdd(&g_trace_n, 1u);                       \
+            if (idx_ < 4096) g_trace[idx_] = (rec);                          \
+        }                                                                    \
+    } while (0)
+#else
+struct TraceRec {};
+#define RB_TRACE_DEFINE(name)
+#define RB_STAMP(rec, i) do {} while (0)
+#define RB_TRACE_COMMIT(rec, k) do {} while (0)
+#endif
+
 #endif  // __CUDACC__
 
 }  // namespace rb

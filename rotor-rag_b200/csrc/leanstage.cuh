@@ -1,0 +1,210 @@
+// Register-resident vector stage for generation steps.
+//
+// A generation step's vector stages (residual add, sub-norm, pre-norm, attention merge,
+// absmax quantiser) run in the prologue of the kernel that consumes them, once per CTA.
+// Each thread owns up to V groups of four consecutive elements (V a template parameter), fetched with 128-bit
+// loads that are all issued together, and keeps them in registers through the whole
+// stage: sums of squares and the absolute maximum are block reductions over register
+// values, and the quantised bytes go straight to the staged activation buffer as one
+// 32-bit word per group.  The arithmetic is that of vec_stage_row (vecstage.cuh);
+// producers hand over finished float32 outputs, so no integer accumulator is re-read.
+#pragma once
+#include "model.cuh"
+#include "quant.cuh"
+
+namespace rb {
+
+enum LeanMode { LM_EMBED = 0, LM_ADD = 1, LM_SUBNORM_ADD = 2, LM_PLAIN = 3, LM_ATTN = 4 };
+
+// What a prologue reads.  Rows are indexed [m][n].
+struct LeanStage {
+    int mode;
+    int n;                       // row width (multiple of 4)
+    const long long* ids;        // LM_EMBED
+    const __nv_bfloat16* embed;  // LM_EMBED: table [vocab][n]
+    const float* y;              // producer output [rows][n]: LM_ADD / LM_SUBNORM_ADD / LM_PLAIN
+    const float* h;              // residual stream in  [rows][n]
+    float* h_out;                // residual stream out [rows][n] (written by the writer CTA)
+    const float* norm0;          // LM_SUBNORM_ADD: sub-norm weight applied to y before the add
+    const float* norm1;          // optional pre-norm weight applied last
+    float eps;
+    // LM_ATTN: merge of the decode-attention partials
+    const float* part_o;
+    const float* part_m;
+    const float* part_l;
+    int nsplit, n_heads, head_dim;
+    // quantiser
+    int terms;
+    int kpad;
+};
+
+__device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float sq4(const float4& v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+__device__ __forceinline__ float amax4(const float4& v) {
+    return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+
+// Builds token row m in registers: v[j] holds elements 4*(threadIdx.x + j*blockDim.x) .. +3
+// (groups past n/4 stay zero).  Applies norm1 when given.  `scratch`: 64 shared floats;
+// `aux`: shared floats for the attention merge weights (2 * n_heads * nsplit, LM_ATTN only).
+// All threads of the block must call.
+template <int LEAN_V>
+__device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[LEAN_V], float* scratch, float* aux,
+                                         bool writer) {
+    const int n4 = p.n >> 2, bd = blockDim.x;
+    const size_t ro = (size_t)m * p.n;
+#pragma unroll
+    for (int j = 0; j < LEAN_V; ++j) v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p.mode == LM_ATTN) {
+        const int D = p.head_dim, ns = p.nsplit, nh = p.n_heads;
+        float* wf = aux;
+        float* wl = aux + nh * ns;
+        const size_t hb = (size_t)m * nh * ns;
+        for (int e = threadIdx.x; e < nh * ns; e += bd) {
+            wf[e] = __ldcg(p.part_m + hb + e);
+            wl[e] = __ldcg(p.part_l + hb + e);
+        }
+        __syncthreads();
+        for (int h = threadIdx.x; h < nh; h += bd) {
+            float M = -INFINITY;
+            for (int s = 0; s < ns; ++s) M = fmaxf(M, wf[h * ns + s]);
+            float L = 0.f;
+            for (int s = 0; s < ns; ++s) {
+                const float ms = wf[h * ns + s];
+                const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
+                L += wl[h * ns + s] * f;
+                wf[h * ns + s] = f;
+            }
+            const float inv = 1.0f / L;
+            for (int s = 0; s < ns; ++s) wf[h * ns + s] *= inv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < LEAN_V; ++j) {
+            const int g = threadIdx.x + j * bd;
+            if (g < n4) {
+                const int i = g * 4, h = i / D, dd = i - h * D;  // D is a multiple of 4: one head per group
+                const float* po = p.part_o + (hb + (size_t)h * ns) * D + dd;
+                float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                for (int s0 = 0; s0 < ns; s0 += 8) {  // nsplit is a multiple of 8
+                    float4 pv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) pv[u] = ldcg4(po + (size_t)(s0 + u) * D);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const float f = wf[h * ns + s0 + u];
+                        o.x += pv[u].x * f;
+                        o.y += pv[u].y * f;
+                        o.z += pv[u].z * f;
+                        o.w += pv[u].w * f;
+                    }
+                }
+                v[j] = o;
+            }
+        }
+        return;  // no norm follows the merge
+    }
+
+    // ---- all loads of the stage in flight together
+    float4 a[LEAN_V], hv[LEAN_V], w0[LEAN_V], w1[LEAN_V];
+#pragma unroll
+    for (int j = 0; j < LEAN_V; ++j) {
+        const int g = threadIdx.x + j * bd;
+        a[j] = hv[j] = w0[j] = w1[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g < n4) {
+            const int i = g * 4;
+            if (p.mode == LM_EMBED) {
+                const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.embed + (size_t)__ldcg(p.ids + m) * p.n + i));
+                a[j] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                   __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+            } else {
+                a[j] = ldcg4(p.y + ro + i);
+                if (p.mode == LM_ADD || p.mode == LM_SUBNORM_ADD) hv[j] = ldcg4(p.h + ro + i);
+                if (p.mode == LM_SUBNORM_ADD) w0[j] = ldg4(p.norm0 + i);
+            }
+            if (p.norm1) w1[j] = ldg4(p.norm1 + i);
+        }
+    }
+    if (p.mode == LM_SUBNORM_ADD) {  // a <- subnorm(a)
+        float s0 = 0.f;
+#pragma unroll
+        for (int j = 0; j < LEAN_V; ++j) s0 += sq4(a[j]);
+        s0 = block_sum(s0, scratch);
+        const float inv0 = 1.0f / sqrtf(s0 / (float)p.n + p.eps);
+#pragma unroll
+        for (int j = 0; j < LEAN_V; ++j) {
+            a[j].x *= inv0 * w0[j].x;
+            a[j].y *= inv0 * w0[j].y;
+            a[j].z *= inv0 * w0[j].z;
+            a[j].w *= inv0 * w0[j].w;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < LEAN_V; ++j) {
+        v[j] = make_float4(a[j].x + hv[j].x, a[j].y + hv[j].y, a[j].z + hv[j].z, a[j].w + hv[j].w);
+        const int g = threadIdx.x + j * bd;
+        if (writer && p.h_out && g < n4) *reinterpret_cast<float4*>(p.h_out + ro + g * 4) = v[j];
+    }
+    if (p.norm1) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < LEAN_V; ++j) ss += sq4(v[j]);
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)p.n + p.eps);
+#pragma unroll
+        for (int j = 0; j < LEAN_V; ++j) {
+            v[j].x *= inv * w1[j].x;
+            v[j].y *= inv * w1[j].y;
+            v[j].z *= inv * w1[j].z;
+            v[j].w *= inv * w1[j].w;
+        }
+    }
+}
+
+// Absmax int8 quantiser over the register row: term t of the row goes to xq + t*tstride
+// (shared memory, zero padded to kpad), its scale and sum to sx[t] / xsum[t] (shared).
+// Same results as quantize_row_from_smem.  Requires kpad <= 4 * LEAN_V * blockDim.x.
+template <int LEAN_V>
+__device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LEAN_V], float* scratch, int8_t* xq,
+                                              size_t tstride, float* sx, int* xsum) {
+    const int n4 = p.n >> 2, k4 = p.kpad >> 2, bd = blockDim.x;
+    for (int t = 0; t < p.terms; ++t) {
+        float mx = 0.f;
+#pragma unroll
+        for (int j = 0; j < LEAN_V; ++j) mx = fmaxf(mx, amax4(v[j]));
+        mx = block_max(mx, scratch);
+        const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
+        const float rs = __fdiv_rn(1.0f, s);
+        int lsum = 0;
+#pragma unroll
+        for (int j = 0; j < LEAN_V; ++j) {
+            const int g = threadIdx.x + j * bd;
+            if (g < k4) {
+                int packed = 0;
+                if (g < n4) {
+                    const float q0 = exact_quant(v[j].x, s, rs), q1 = exact_quant(v[j].y, s, rs);
+                    const float q2 = exact_quant(v[j].z, s, rs), q3 = exact_quant(v[j].w, s, rs);
+                    const int i0 = (int)q0, i1 = (int)q1, i2 = (int)q2, i3 = (int)q3;
+                    packed = (i0 & 0xff) | ((i1 & 0xff) << 8) | ((i2 & 0xff) << 16) | ((i3 & 0xff) << 24);
+                    lsum += i0 + i1 + i2 + i3;
+                    if (t + 1 < p.terms) {
+                        v[j].x = __fsub_rn(v[j].x, __fmul_rn(q0, s));
+                        v[j].y = __fsub_rn(v[j].y, __fmul_rn(q1, s));
+                        v[j].z = __fsub_rn(v[j].z, __fmul_rn(q2, s));
+                        v[j].w = __fsub_rn(v[j].w, __fmul_rn(q3, s));
+                    }
+                }
+                *reinterpret_cast<int*>(xq + (size_t)t * tstride + (size_t)g * 4) = packed;
+            }
+        }
+        lsum = block_sum_i(lsum, reinterpret_cast<int*>(scratch));
+        if (threadIdx.x == 0) {
+            sx[t] = s;
+            xsum[t] = lsum;
+        }
+    }
+}
+
+}  // namespace rb

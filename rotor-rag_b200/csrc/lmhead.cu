@@ -6,7 +6,7 @@
 // table four at a time; a lane reads 8 bf16 (one 128-bit load) per row per 256 columns
 // and keeps the activation slice it needs in shared memory.  Up to LM_ROWS token rows
 // share one pass over the table.
-#include "vecstage.cuh"
+#include "model.cuh"
 
 namespace rb {
 
@@ -32,13 +32,44 @@ __global__ void __launch_bounds__(LM_WARPS * 32) lmhead_kernel(const __grid_cons
     const int d = p.d;
     pdl_trigger();
     pdl_wait();
-    if (p.pro_rows > 0) {
-        // fused prologue: every CTA rebuilds the final-normed rows from the last down projection
-        float* scratch = xs + NROWS * d;
+    if (p.pro_y) {
+        // fused prologue: x = final_norm(h + y) built by every CTA from the last block's outputs
+        // (float4 loads issued together; the sum of squares rides along)
+        __shared__ float red[33];
+        const int n4 = d >> 2;
         for (int r = 0; r < NROWS; ++r) {
-            vec_stage_row(p.pro, row0 + r, xs + r * d, scratch, blockIdx.x == 0, nullptr);
-            __syncthreads();
+            const size_t ro = (size_t)(row0 + r) * d;
+            float ss = 0.f;
+            for (int g0 = threadIdx.x; g0 < n4; g0 += 4 * blockDim.x) {
+                float4 a[4], hv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int g = g0 + u * blockDim.x;
+                    if (g < n4) {
+                        a[u] = __ldcg(reinterpret_cast<const float4*>(p.pro_y + ro) + g);
+                        hv[u] = __ldcg(reinterpret_cast<const float4*>(p.pro_h + ro) + g);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int g = g0 + u * blockDim.x;
+                    if (g < n4) {
+                        const float4 v = make_float4(a[u].x + hv[u].x, a[u].y + hv[u].y, a[u].z + hv[u].z, a[u].w + hv[u].w);
+                        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                        *reinterpret_cast<float4*>(xs + r * d + g * 4) = v;
+                    }
+                }
+            }
+            ss = block_sum(ss, red);
+            const float inv = 1.0f / sqrtf(ss / (float)d + p.pro_eps);
+            for (int g = threadIdx.x; g < n4; g += blockDim.x) {  // each thread revisits its own groups
+                float4 v = *reinterpret_cast<float4*>(xs + r * d + g * 4);
+                const float4 w = __ldg(reinterpret_cast<const float4*>(p.pro_norm) + g);
+                v.x *= inv * w.x; v.y *= inv * w.y; v.z *= inv * w.z; v.w *= inv * w.w;
+                *reinterpret_cast<float4*>(xs + r * d + g * 4) = v;
+            }
         }
+        __syncthreads();
     } else {
         for (int i = threadIdx.x; i < NROWS * d; i += blockDim.x) xs[i] = __ldcg(&p.x[(size_t)row0 * d + i]);
         __syncthreads();
@@ -223,7 +254,7 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
 
 template <int NROWS>
 static int launch_lm(const LmHeadParams& p, int row0, cudaStream_t st) {
-    const size_t smem = ((size_t)NROWS * p.d + (p.pro_rows > 0 ? 64 : 0)) * sizeof(float);
+    const size_t smem = (size_t)NROWS * p.d * sizeof(float);
     if (smem > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
@@ -263,7 +294,7 @@ int launch_lmhead(const LmHeadParams& pin, int rows, cudaStream_t st) {
     LmHeadParams p = pin;
     // the fused pick needs every partial in one launch; otherwise a separate kernel merges them
     const bool fused = p.tail_counter && p.argmax_out && rows <= LM_ROWS;
-    if (p.pro_rows > 0 && (rows > LM_ROWS || p.pro_rows != rows || p.pro.n != p.d)) return ROTOR_B200_ERR_ARG;
+    if (p.pro_y && (rows > LM_ROWS || !p.pro_h || !p.pro_norm)) return ROTOR_B200_ERR_ARG;
     if (!fused) {
         if (p.adv_log) return ROTOR_B200_ERR_ARG;
         p.tail_counter = nullptr;

@@ -15,7 +15,7 @@
 #include <cstring>
 #include <new>
 
-#include "model.cuh"
+#include "leanstage.cuh"
 
 namespace rb {
 
@@ -46,14 +46,11 @@ struct Ctx {
     int nsplit;
     int max_batch;
     unsigned* counters;  // [8 + max_batch] zeroed words for last-CTA tails
-    // accumulators of the fused generation step: q/k/v, o, gate/up, down.  Each is cleared by
-    // an earlier kernel of the chain; ring_cols is the column count they are currently clean for
-    int32_t* ring[4];
-    size_t ring_words[4];
-    int ring_cols;
+    // float32 outputs of the fused generation step's products: q/k/v, o, gated, down
+    float* fy[4];
 };
 
-constexpr int RING_MAX_COLS = 8;
+constexpr int FUSED_MAX_ROWS = 4;
 
 struct Model {
     rotor_b200_model_config cfg;
@@ -135,18 +132,13 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     c.part_m = cv.take<float>(heads);
     c.part_l = cv.take<float>(heads);
     c.counters = cv.take<unsigned>(8 + (size_t)c.max_batch);
-    const size_t outs[4] = {qkv_out, d, 2 * ff, d};
-    for (int i = 0; i < 4; ++i) {
-        c.ring_words[i] = RING_MAX_COLS * outs[i];
-        c.ring[i] = cv.take<int32_t>(c.ring_words[i]);
-    }
+    const size_t outs[4] = {qkv_out, d, ff, d};
+    for (int i = 0; i < 4; ++i) c.fy[i] = cv.take<float>(FUSED_MAX_ROWS * outs[i]);
 }
 
 // One-time device initialisation of a carved context: tail counters and the rotary table.
 static int init_ctx(Ctx& c, cudaStream_t st) {
     RB_CUDA(cudaMemsetAsync(c.counters, 0, (8 + (size_t)c.max_batch) * sizeof(unsigned), st));
-    for (int i = 0; i < 4; ++i) RB_CUDA(cudaMemsetAsync(c.ring[i], 0, c.ring_words[i] * sizeof(int32_t), st));
-    c.ring_cols = 0;
     c.rope = nullptr;
     if (c.rope_theta > 0.f) {
         int rc = launch_rope_table(c.rope_buf, c.max_seq, c.head_dim, c.rope_theta, st);
@@ -393,64 +385,48 @@ static int run_blocks(Ctx& c, const rotor_b200_layer_weights* layers, int l0, in
 static bool fused_step_ok(const Model& m, int batch, int seq) {
     const Ctx& c = m.c;
     static const bool off = getenv("ROTOR_B200_NO_FUSED_STEP") != nullptr;  // measurement aid
-    return !off && seq == 1 && batch <= 4 && batch <= c.max_batch && c.terms <= 3 &&
-           batch * c.terms <= RING_MAX_COLS &&
-           fused_gemv_supported(c.d, c.ff, batch, c.terms, c.ff, 0) &&
-           fused_gemv_supported(c.d, c.dq, batch, c.terms, c.dq, c.n_heads * c.nsplit);
+    const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
+    return !off && seq == 1 && batch <= FUSED_MAX_ROWS && batch <= c.max_batch && c.terms <= 3 &&
+           batch * c.terms <= 8 && c.ff % 16 == 0 &&
+           fused_gemv_supported(qkv_out, c.d, batch, c.terms, 1, 0) &&
+           fused_gemv_supported(c.d, c.dq, batch, c.terms, 1, c.n_heads * c.nsplit) &&
+           fused_gemv_supported(c.ff, c.d, batch, c.terms, 2, 0) &&
+           fused_gemv_supported(c.d, c.ff, batch, c.terms, 1, 0);
 }
 
 static int run_step_fused(Model& m, const long long* ids, int batch, int logits_mode, float* logits,
                           long long* next_ids, cudaStream_t st, bool advance) {
     Ctx& c = m.c;
-    const int d = c.d, cols = batch * c.terms;
+    const int d = c.d;
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
-    const size_t outs[4] = {qkv_out, (size_t)d, 2 * (size_t)c.ff, (size_t)d};
-    auto view = [&](int i) {
-        AccView v;
-        v.acc = c.ring[i];
-        v.plane_stride = 0;
-        v.planes = 1;
-        v.out = (int)outs[i];
-        return v;
+    LeanStage ls;
+    auto stage = [&](int mode, int n) {
+        ls = {};
+        ls.mode = mode;
+        ls.n = n;
+        ls.eps = c.eps;
+        ls.terms = c.terms;
+        ls.kpad = (int)kpad_of(n);
     };
-    // Kernel i of a block accumulates into ring[i] and clears ring[i+1] for its successor.
-    auto product = [&](int i, const void* tiles, size_t in, const VecStageParams& pro, int slot) {
-        const int nx = (i + 1) & 3;
-        return launch_fused_gemv(tiles, outs[i], in, batch, pro, c.ring[i], c.ring[nx], (size_t)cols * outs[nx],
-                                 c.sx[slot], c.xsum[slot], st);
-    };
-    VecStageParams pro;
     for (int l = 0; l < m.cfg.n_layers; ++l) {
         const rotor_b200_layer_weights& L = m.layers[l];
-        pro = {};
-        pro.n = d;
-        pro.eps = c.eps;
-        pro.terms_out = c.terms;
-        pro.kpad = (int)kpad_of(d);
-        pro.norm1 = L.input_norm;
-        pro.h_out = c.h;
+        // q/k/v <- [embedding | h2 + previous down] -> h, input norm
         if (l == 0) {
-            pro.mode = VS_EMBED;
-            pro.ids = ids;
-            pro.embed = m.embed;
-            pro.h = c.h;
+            stage(LM_EMBED, d);
+            ls.ids = ids;
+            ls.embed = m.embed;
         } else {
-            pro.mode = VS_DOWN;
-            pro.acc = view(3);
-            pro.sx_in = c.sx[1];
-            pro.terms = c.terms;
-            pro.wscale0 = m.layers[l - 1].down_scale;
-            pro.h = c.h2;
+            stage(LM_ADD, d);
+            ls.y = c.fy[3];
+            ls.h = c.h2;
         }
-        RB_TRY(product(0, L.qkv_tiles, d, pro, 0));
+        ls.h_out = c.h;
+        ls.norm1 = L.input_norm;
+        const float sqkv[3] = {L.q_scale, L.k_scale, L.v_scale};
+        RB_TRY(launch_fused_gemv(L.qkv_tiles, qkv_out, d, 1, batch, ls, c.fy[0], sqkv, c.dq, c.dq + c.dkv, 0, st));
 
         AttnDecodeParams dp = {};
-        dp.acc = view(0);
-        dp.sx = c.sx[0];
-        dp.terms = c.terms;
-        dp.sq = L.q_scale;
-        dp.sk = L.k_scale;
-        dp.sv = L.v_scale;
+        dp.qkv_f = c.fy[0];
         dp.n_heads = c.n_heads;
         dp.n_kv_heads = c.n_kv_heads;
         dp.head_dim = c.head_dim;
@@ -465,53 +441,35 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         dp.part_l = c.part_l;
         RB_TRY(launch_attn_decode(dp, batch, st));  // no counter: the o product merges the partials
 
-        pro = {};
-        pro.mode = VS_ATTN;
-        pro.n = c.dq;
-        pro.part_o = c.part_o;
-        pro.part_m = c.part_m;
-        pro.part_l = c.part_l;
-        pro.nsplit = c.nsplit;
-        pro.n_heads = c.n_heads;
-        pro.head_dim = c.head_dim;
-        pro.eps = c.eps;
-        pro.terms_out = c.terms;
-        pro.kpad = (int)kpad_of(c.dq);
-        RB_TRY(product(1, L.o_tiles, c.dq, pro, 1));
+        // o <- merged attention
+        stage(LM_ATTN, c.dq);
+        ls.part_o = c.part_o;
+        ls.part_m = c.part_m;
+        ls.part_l = c.part_l;
+        ls.nsplit = c.nsplit;
+        ls.n_heads = c.n_heads;
+        ls.head_dim = c.head_dim;
+        const float so[3] = {L.o_scale, L.o_scale, L.o_scale};
+        RB_TRY(launch_fused_gemv(L.o_tiles, d, c.dq, 1, batch, ls, c.fy[1], so, d, d, 0, st));
 
-        pro = {};
-        pro.mode = VS_OPROJ;
-        pro.n = d;
-        pro.acc = view(1);
-        pro.sx_in = c.sx[1];
-        pro.terms = c.terms;
-        pro.wscale0 = L.o_scale;
-        pro.norm0 = L.attn_sub_norm;
-        pro.h = c.h;
-        pro.h_out = c.h2;
-        pro.norm1 = L.post_attn_norm;
-        pro.eps = c.eps;
-        pro.terms_out = c.terms;
-        pro.kpad = (int)kpad_of(d);
-        RB_TRY(product(2, L.gate_up_tiles, d, pro, 0));
+        // gate/up <- h + subnorm(o) -> h2, post-attention norm; gating in the epilogue
+        stage(LM_SUBNORM_ADD, d);
+        ls.y = c.fy[1];
+        ls.h = c.h;
+        ls.h_out = c.h2;
+        ls.norm0 = L.attn_sub_norm;
+        ls.norm1 = L.post_attn_norm;
+        const float sgu[3] = {L.gate_scale, L.up_scale, 0.f};
+        RB_TRY(launch_fused_gemv(L.gate_up_tiles, c.ff, d, 2, batch, ls, c.fy[2], sgu, 0, 0, c.ffn_act, st));
 
-        pro = {};
-        pro.mode = VS_FFN;
-        pro.n = c.ff;
-        pro.acc = view(2);
-        pro.sx_in = c.sx[0];
-        pro.terms = c.terms;
-        pro.wscale0 = L.gate_scale;
-        pro.wscale1 = L.up_scale;
-        pro.ffn_act = c.ffn_act;
-        pro.norm1 = L.ffn_sub_norm;
-        pro.eps = c.eps;
-        pro.terms_out = c.terms;
-        pro.kpad = (int)kpad_of(c.ff);
-        RB_TRY(product(3, L.down_tiles, c.ff, pro, 1));
+        // down <- sub-norm(gated)
+        stage(LM_PLAIN, c.ff);
+        ls.y = c.fy[2];
+        ls.norm1 = L.ffn_sub_norm;
+        const float sd[3] = {L.down_scale, L.down_scale, L.down_scale};
+        RB_TRY(launch_fused_gemv(L.down_tiles, d, c.ff, 1, batch, ls, c.fy[3], sd, d, d, 0, st));
     }
-    const AccView vb = view(3);
-    // LM head: residual add + final norm in its prologue
+    // LM head: h2 + last down, final norm in its prologue; greedy pick in its last CTA
     LmHeadParams lp = {};
     lp.embed = m.embed;
     lp.vocab = m.cfg.vocab_size;
@@ -528,18 +486,10 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         lp.adv_step = m.d_step;
         lp.adv_max_log = m.max_log;
     }
-    lp.pro = {};
-    lp.pro.mode = VS_DOWN;
-    lp.pro.n = d;
-    lp.pro.acc = vb;
-    lp.pro.sx_in = c.sx[1];
-    lp.pro.terms = c.terms;
-    lp.pro.wscale0 = m.layers[m.cfg.n_layers - 1].down_scale;
-    lp.pro.h = c.h2;
-    lp.pro.h_out = c.h;
-    lp.pro.norm1 = m.final_norm;
-    lp.pro.eps = c.eps;
-    lp.pro_rows = batch;
+    lp.pro_y = c.fy[3];
+    lp.pro_h = c.h2;
+    lp.pro_norm = m.final_norm;
+    lp.pro_eps = c.eps;
     return launch_lmhead(lp, batch, st);
 }
 
@@ -547,15 +497,8 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
 static int run_layers(Model& m, const long long* ids, int batch, int seq, int logits_mode, float* logits,
                       long long* next_ids, cudaStream_t st, bool advance = false) {
     Ctx& c = m.c;
-    if (fused_step_ok(m, batch, seq) && (logits_mode != ROTOR_B200_LOGITS_NONE || next_ids)) {
-        if (c.ring_cols != batch * c.terms) {
-            // another column count used the accumulators last: restore the all-zero state.  Never
-            // reached inside a graph capture: decode_begin makes the same check before capturing.
-            for (int i = 0; i < 4; ++i) RB_CUDA(cudaMemsetAsync(c.ring[i], 0, c.ring_words[i] * sizeof(int32_t), st));
-            c.ring_cols = batch * c.terms;
-        }
+    if (fused_step_ok(m, batch, seq) && (logits_mode != ROTOR_B200_LOGITS_NONE || next_ids))
         return run_step_fused(m, ids, batch, logits_mode, logits, next_ids, st, advance);
-    }
     const int rows = batch * seq, d = c.d;
     VecStageParams e = {};
     e.mode = VS_EMBED;
@@ -691,11 +634,6 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
     Model* m = (Model*)handle;
     RB_REQUIRE(m && first_ids && batch > 0 && batch <= m->cfg.max_batch && batch <= 1024);
     RB_REQUIRE(past_len >= 0 && past_len < m->cfg.max_seq);
-    if (fused_step_ok(*m, batch, 1) && m->c.ring_cols != batch * m->c.terms) {
-        for (int i = 0; i < 4; ++i)
-            RB_CUDA(cudaMemsetAsync(m->c.ring[i], 0, m->c.ring_words[i] * sizeof(int32_t), as_stream(stream)));
-        m->c.ring_cols = batch * m->c.terms;
-    }
     begin_kernel<<<1, 1024, 0, as_stream(stream)>>>(m->cur_ids, (const long long*)first_ids, batch, m->c.d_pos,
                                                     past_len, m->d_step);
     m->pos = past_len;

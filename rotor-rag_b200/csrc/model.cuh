@@ -63,11 +63,11 @@ int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* x
                        int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st);
 int gemv_cols_per_launch(int variant, int ncols);
 
-// Generation-step product with the consuming vector stage fused in (fused.cu).  acc must be
-// all zero on entry; zero_ptr/zero_count name a buffer this kernel clears for a later product.
-int launch_fused_gemv(const void* tiles, size_t out, size_t in, int rows, const VecStageParams& stage, int32_t* acc,
-                      int32_t* zero_ptr, size_t zero_count, float* sx_pub, int32_t* xsum_pub, cudaStream_t st);
-bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int stage_n, int stage_extra);
+// Generation-step product with the consuming vector stage fused in (fused.cu, leanstage.cuh).
+struct LeanStage;
+int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int rows, const LeanStage& stage, float* y,
+                      const float* scale, int seg1, int seg2, int ffn_act, cudaStream_t st);
+bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int halves, int merge_weights);
 int configure_fused_gemv();
 extern int g_use_pdl;
 
@@ -89,7 +89,8 @@ int launch_qkv_finish(const QkvFinishParams& p, int rows, cudaStream_t st);
 int launch_rope_table(float2* table, int max_seq, int head_dim, float theta, cudaStream_t st);
 
 struct AttnDecodeParams {
-    AccView acc;          // stacked [q;k;v] product of one token per sequence
+    const float* qkv_f;   // when set: finished float32 [batch][q;k;v] rows, acc/sx/scales unused
+    AccView acc;          // else: stacked [q;k;v] product of one token per sequence
     const float* sx;
     int terms;
     float sq, sk, sv;
@@ -141,8 +142,11 @@ struct LmHeadParams {
     int* adv_pos;
     int* adv_step;
     int adv_max_log;
-    VecStageParams pro;          // fused prologue (pro_rows > 0): builds x from the last block's output
-    int pro_rows;
+    // fused prologue (pro_y != null): x = rmsnorm(pro_h + pro_y, pro_norm), rows of width d
+    const float* pro_y;
+    const float* pro_h;
+    const float* pro_norm;
+    float pro_eps;
 };
 int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st);
 int lmhead_parts();
