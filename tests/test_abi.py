@@ -15,6 +15,7 @@ LIB = os.path.join(ROOT, "rotor-rag_b200", "rotor_b200", "librotor_b200.so")
 def declared_functions():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"^\s*#.*$", "", text, flags=re.M)          # preprocessor lines are not declarations
     return sorted(set(re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{]*\)\s*;", text)))
 
 
