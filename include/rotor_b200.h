@@ -46,7 +46,8 @@ enum {
     ROTOR_B200_ERR_CUDA = 2,       /* a CUDA runtime call or launch failed */
     ROTOR_B200_ERR_SHAPE = 3,      /* shape not supported by the kernels */
     ROTOR_B200_ERR_WORKSPACE = 4,  /* caller-provided workspace too small */
-    ROTOR_B200_ERR_TIMEOUT = 5     /* a bounded device-side wait gave up */
+    ROTOR_B200_ERR_TIMEOUT = 5,    /* a bounded device-side wait gave up */
+    ROTOR_B200_ERR_TOO_LARGE = 6   /* problem does not fit the library's built-in scratch array */
 };
 
 /* GEMV variant selector for rotor_b200_bitlinear_acc */
@@ -132,6 +133,28 @@ int rotor_b200_bitlinear_forward(const void* tiles, size_t out, size_t in, const
                                  size_t m, int terms, float wscale, const float* wscale_vec,
                                  float* y, void* workspace, size_t workspace_bytes,
                                  int variant, void* stream);
+
+/* Allocation-free variant of rotor_b200_bitlinear_forward.  (No counterpart in the reference:
+ * its plug-in call simply has no workspace argument, which is the reason this exists.)
+ * For hosts that cannot allocate device memory when they call in -- a plug-in reached through
+ * ternary_matmul(packed, scales, x, in, out), or a serving loop whose own pool already holds
+ * all free device memory, where cudaMalloc fails or stalls every stream while it runs.  The
+ * scratch (quantised activations, scales, int32 accumulators, a status word) lives in a
+ * fixed ROTOR_B200_STATIC_SCRATCH_BYTES array inside the library, held on every GPU that
+ * loads the library until the process exits.
+ *  - Same arguments and results as rotor_b200_bitlinear_forward, minus the workspace.
+ *  - A problem that needs more scratch than the array returns ROTOR_B200_ERR_TOO_LARGE and
+ *    launches nothing; rotor_b200_bitlinear_static_fits(out, in, m, terms) tells beforehand.
+ *  - The first call on a device looks up the array's device address; make that call before
+ *    any stream capture begins.
+ *  - Calls share the array and it keeps the last call's contents (what must start at zero
+ *    is cleared inside); calls that overlap on the GPU race on it, so keep them ordered.
+ *  - Calls no cudaMalloc / cudaFree or other allocating routine. */
+#define ROTOR_B200_STATIC_SCRATCH_BYTES (4u << 20)
+int rotor_b200_bitlinear_static_fits(size_t out, size_t in, size_t m, int terms);
+int rotor_b200_bitlinear_forward_static(const void* tiles, size_t out, size_t in, const float* x,
+                                        size_t m, int terms, float wscale, const float* wscale_vec,
+                                        float* y, int variant, void* stream);
 
 /* The plug-in seam with HOST buffers: GPUTernaryOps.ternary_matmul
  * (src/rotor/gpu_ternary.py:138-202, called from src/rotor/transformer.py:136-142).

@@ -396,6 +396,107 @@ int rotor_b200_bitlinear_forward(const void* tiles, size_t out, size_t in, const
     return rotor_b200_bitlinear_dequant(acc, sx, m, terms, out, wscale, wscale_vec, y, stream);
 }
 
+/* ---------------------------------------------------------------------------------------
+ * Allocation-free layer forward.
+ *
+ * rotor_b200_bitlinear_forward needs a caller-provided workspace, and the accumulate step
+ * behind it creates a small device status word with cudaMalloc on first use.  Some hosts
+ * cannot do either: a plug-in driven through the reference's backend call
+ * (ternary_matmul(packed, scales, input_vec, in_dim, out_dim) has no workspace argument),
+ * or a serving loop that has already handed every remaining byte of device memory to its
+ * own pool, where cudaMalloc would fail -- and, when it succeeds, stalls all streams of the
+ * device while it runs.  For them the scratch lives in a fixed array inside the library:
+ * ROTOR_B200_STATIC_SCRATCH_BYTES per GPU, resident from library load to process exit on
+ * every GPU that loads the library.
+ *
+ * Rules of use
+ *  - Problems whose scratch need exceeds the array are refused with ROTOR_B200_ERR_TOO_LARGE;
+ *    nothing is launched.  rotor_b200_bitlinear_static_fits() answers the question up front.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress).  Make that first call before starting any stream capture.
+ *  - All calls on one GPU share the array, and it keeps the previous call's contents; the
+ *    entry point clears what has to start at zero.  Two calls that overlap on the GPU
+ *    (different streams, no ordering between them) race on the array: serialise them.
+ *  - No cudaMalloc, cudaFree or other allocating routine is called on this path. */
+static __device__ __align__(256) unsigned char g_static_scratch[ROTOR_B200_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(unsigned char** out) {
+    static unsigned char* addr[64] = {nullptr};
+    int dev = -1;
+    RB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return ROTOR_B200_ERR_ARG;
+    if (!addr[dev]) {
+        // g_static_scratch names the array in device code only; host code must ask for its address
+        void* p = nullptr;
+        RB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        addr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = addr[dev];
+    return ROTOR_B200_OK;
+}
+
+static size_t static_need(size_t out, size_t in, size_t m, int terms) {
+    return 256 + rotor_b200_bitlinear_workspace_bytes(out, in, m, terms);  // status word + stage buffers
+}
+
+int rotor_b200_bitlinear_static_fits(size_t out, size_t in, size_t m, int terms) {
+    if (out == 0 || in == 0 || m == 0 || terms < 1 || terms > 4) return 0;
+    return static_need(out, in, m, terms) <= ROTOR_B200_STATIC_SCRATCH_BYTES;
+}
+
+int rotor_b200_bitlinear_forward_static(const void* tiles, size_t out, size_t in, const float* x, size_t m,
+                                        int terms, float wscale, const float* wscale_vec, float* y, int variant,
+                                        void* stream) {
+    RB_REQUIRE(tiles && x && y && m > 0 && out > 0 && in > 0 && terms >= 1 && terms <= 4);
+    RB_REQUIRE(out < (1u << 30) && in < (1u << 30));
+    RB_REQUIRE(((uintptr_t)tiles & 15) == 0);
+    RB_REQUIRE(variant >= ROTOR_B200_VARIANT_AUTO && variant <= ROTOR_B200_VARIANT_MMA);
+    if (static_need(out, in, m, terms) > ROTOR_B200_STATIC_SCRATCH_BYTES) return ROTOR_B200_ERR_TOO_LARGE;
+    unsigned char* base = nullptr;
+    int rc = static_scratch_address(&base);
+    if (rc) return rc;
+    cudaStream_t st = as_stream(stream);
+    // carve: [status word, 256 B][xq][sx][xsum][acc]
+    unsigned* status = reinterpret_cast<unsigned*>(base);
+    unsigned char* w = base + 256;
+    const size_t nc = m * (size_t)terms, kpad = kpad_of(in);
+    int8_t* xq = (int8_t*)w;
+    w += al256(nc * kpad);
+    float* sx = (float*)w;
+    w += al256(nc * 4);
+    int32_t* xsum = (int32_t*)w;
+    w += al256(nc * 4);
+    int32_t* acc = (int32_t*)w;
+    RB_CUDA(cudaMemsetAsync(status, 0, sizeof(unsigned), st));  // left over from whoever used the array last
+    rc = rotor_b200_quantize_rows(x, m, in, terms, xq, sx, xsum, stream);
+    if (rc) return rc;
+    const int nkt = (int)(kpad / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
+    variant = pick_variant(variant, (int)(nc < 8 ? nc : 8));
+    const size_t chunk = variant == ROTOR_B200_VARIANT_MMA ? 8 : 4;
+    for (size_t c0 = 0; c0 < nc; c0 += chunk) {
+        const int ncols = (int)((nc - c0) < chunk ? (nc - c0) : chunk);
+        const int ksplit = choose_ksplit(nrt, nkt, ncols, 4);
+        AccParams p;
+        p.tiles = (const uint4*)tiles;
+        p.xq = xq + c0 * kpad;
+        p.xsum = xsum + c0;
+        p.acc = acc + c0 * out;
+        p.status = status;
+        p.out = (int)out;
+        p.nkt = nkt;
+        p.kt_per_split = (nkt + ksplit - 1) / ksplit;
+        p.ncols = ncols;
+        const int ksplit_eff = (nkt + p.kt_per_split - 1) / p.kt_per_split;
+        p.atomic = ksplit_eff > 1;
+        p.plane_stride = 0;
+        // split-K partial sums are added into the accumulators: they must start at zero
+        if (p.atomic) RB_CUDA(cudaMemsetAsync(p.acc, 0, (size_t)ncols * out * sizeof(int32_t), st));
+        rc = dispatch_acc(p, nrt, ksplit_eff, variant, st);
+        if (rc) return rc;
+    }
+    return rotor_b200_bitlinear_dequant(acc, sx, m, terms, out, wscale, wscale_vec, y, stream);
+}
+
 int rotor_b200_ternary_matmul_host(const void* tiles, const float* scales_host, const float* x_host, size_t in,
                                    size_t out, int terms, float* y_host) {
     RB_REQUIRE(tiles && scales_host && x_host && y_host && in > 0 && out > 0 && terms >= 1 && terms <= 4);

@@ -173,6 +173,7 @@ const char* rotor_b200_status_string(int status) {
         case ROTOR_B200_ERR_SHAPE: return "unsupported shape";
         case ROTOR_B200_ERR_WORKSPACE: return "workspace too small";
         case ROTOR_B200_ERR_TIMEOUT: return "device-side wait timed out";
+        case ROTOR_B200_ERR_TOO_LARGE: return "problem exceeds the library's built-in scratch array";
         default: return "unknown status";
     }
 }

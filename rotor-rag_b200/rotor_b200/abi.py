@@ -15,6 +15,8 @@ LIB_PATH = os.path.join(_HERE, "librotor_b200.so")
 
 OK = 0
 VARIANT_AUTO, VARIANT_DP4A, VARIANT_MMA = 0, 1, 2
+ERR_TOO_LARGE = 6
+STATIC_SCRATCH_BYTES = 4 << 20
 
 
 class RotorB200Error(RuntimeError):
@@ -58,6 +60,8 @@ _SIGNATURES = {
     "rotor_b200_bitlinear_workspace_bytes": (_sz, [_sz, _sz, _sz, _i]),
     "rotor_b200_bitlinear_forward": (_i, [_p, _sz, _sz, _p, _sz, _i, _f, _p, _p, _p, _sz, _i, _p]),
     "rotor_b200_ternary_matmul_host": (_i, [_p, _p, _p, _sz, _sz, _i, _p]),
+    "rotor_b200_bitlinear_static_fits": (_i, [_sz, _sz, _sz, _i]),
+    "rotor_b200_bitlinear_forward_static": (_i, [_p, _sz, _sz, _p, _sz, _i, _f, _p, _p, _i, _p]),
 }
 
 
