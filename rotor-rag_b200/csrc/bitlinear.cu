@@ -195,6 +195,8 @@ static int ensure_status() {
 
 int g_use_pdl = 0;  // programmatic dependent launch for the kernels that call pdl_wait()
 
+unsigned* library_status_word() { return ensure_status() ? nullptr : g_status; }
+
 template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
 static int launch_acc(const AccParams& p, int nrt, int ksplit, cudaStream_t st) {
     auto kern = bitlinear_acc_kernel<WARPS, UMAX, USE_MMA, NCOL>;

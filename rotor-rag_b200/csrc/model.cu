@@ -15,7 +15,7 @@
 #include <cstring>
 #include <new>
 
-#include "leanstage.cuh"
+#include "product_body.cuh"
 
 namespace rb {
 
@@ -69,6 +69,13 @@ struct Model {
     cudaGraphExec_t graph;
     int graph_batch;
     unsigned long long graph_launches;  // kernels inside the captured step
+    // single-launch generation step: per-block plan on host and device, built per batch size
+    void* mega_host;
+    void* mega_dev;
+    unsigned* mega_bar;
+    LmHeadParams mega_lm;
+    int mega_batch;   // batch the plan is valid for (0 = none)
+    int mega_ok;      // the device can run the step kernel for that plan
 };
 
 struct Carve {
@@ -159,6 +166,8 @@ static void carve(Model& m, unsigned char* base, size_t* total) {
     m.max_log = c.max_seq;
     m.tok_log = cv.take<long long>((size_t)m.max_log * c.max_batch);
     m.d_step = cv.take<int>(1);
+    m.mega_dev = cv.take<unsigned char>(mega_layer_bytes() * (size_t)c.n_layers);
+    m.mega_bar = cv.take<unsigned>(2);
     *total = cv.off;
 }
 
@@ -394,11 +403,19 @@ static bool fused_step_ok(const Model& m, int batch, int seq) {
            fused_gemv_supported(c.d, c.ff, batch, c.terms, 1, 0);
 }
 
+// With record == true nothing is launched: the parameter blocks go to m.mega_host / m.mega_lm.
 static int run_step_fused(Model& m, const long long* ids, int batch, int logits_mode, float* logits,
-                          long long* next_ids, cudaStream_t st, bool advance) {
+                          long long* next_ids, cudaStream_t st, bool advance, bool record = false) {
     Ctx& c = m.c;
     const int d = c.d;
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
+    const int grid = fused_sm_count();
+    FusedGemvParams prod[4];
+    auto product = [&](int i, const void* tiles, size_t out, size_t in, int halves, const LeanStage& stg, float* y,
+                       const float* scale, int seg1, int seg2, int act) {
+        if (record) return make_fused_params(prod[i], tiles, out, in, halves, batch, stg, y, scale, seg1, seg2, act, grid);
+        return launch_fused_gemv(tiles, out, in, halves, batch, stg, y, scale, seg1, seg2, act, st);
+    };
     LeanStage ls;
     auto stage = [&](int mode, int n) {
         ls = {};
@@ -423,7 +440,7 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         ls.h_out = c.h;
         ls.norm1 = L.input_norm;
         const float sqkv[3] = {L.q_scale, L.k_scale, L.v_scale};
-        RB_TRY(launch_fused_gemv(L.qkv_tiles, qkv_out, d, 1, batch, ls, c.fy[0], sqkv, c.dq, c.dq + c.dkv, 0, st));
+        RB_TRY(product(0, L.qkv_tiles, qkv_out, d, 1, ls, c.fy[0], sqkv, c.dq, c.dq + c.dkv, 0));
 
         AttnDecodeParams dp = {};
         dp.qkv_f = c.fy[0];
@@ -439,7 +456,7 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         dp.part_o = c.part_o;
         dp.part_m = c.part_m;
         dp.part_l = c.part_l;
-        RB_TRY(launch_attn_decode(dp, batch, st));  // no counter: the o product merges the partials
+        if (!record) RB_TRY(launch_attn_decode(dp, batch, st));  // no counter: the o product merges the partials
 
         // o <- merged attention
         stage(LM_ATTN, c.dq);
@@ -450,7 +467,7 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         ls.n_heads = c.n_heads;
         ls.head_dim = c.head_dim;
         const float so[3] = {L.o_scale, L.o_scale, L.o_scale};
-        RB_TRY(launch_fused_gemv(L.o_tiles, d, c.dq, 1, batch, ls, c.fy[1], so, d, d, 0, st));
+        RB_TRY(product(1, L.o_tiles, d, c.dq, 1, ls, c.fy[1], so, d, d, 0));
 
         // gate/up <- h + subnorm(o) -> h2, post-attention norm; gating in the epilogue
         stage(LM_SUBNORM_ADD, d);
@@ -460,14 +477,15 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         ls.norm0 = L.attn_sub_norm;
         ls.norm1 = L.post_attn_norm;
         const float sgu[3] = {L.gate_scale, L.up_scale, 0.f};
-        RB_TRY(launch_fused_gemv(L.gate_up_tiles, c.ff, d, 2, batch, ls, c.fy[2], sgu, 0, 0, c.ffn_act, st));
+        RB_TRY(product(2, L.gate_up_tiles, c.ff, d, 2, ls, c.fy[2], sgu, 0, 0, c.ffn_act));
 
         // down <- sub-norm(gated)
         stage(LM_PLAIN, c.ff);
         ls.y = c.fy[2];
         ls.norm1 = L.ffn_sub_norm;
         const float sd[3] = {L.down_scale, L.down_scale, L.down_scale};
-        RB_TRY(launch_fused_gemv(L.down_tiles, d, c.ff, 1, batch, ls, c.fy[3], sd, d, d, 0, st));
+        RB_TRY(product(3, L.down_tiles, d, c.ff, 1, ls, c.fy[3], sd, d, d, 0));
+        if (record) RB_TRY(mega_record_layer(m.mega_host, l, prod, dp));
     }
     // LM head: h2 + last down, final norm in its prologue; greedy pick in its last CTA
     LmHeadParams lp = {};
@@ -490,7 +508,34 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
     lp.pro_h = c.h2;
     lp.pro_norm = m.final_norm;
     lp.pro_eps = c.eps;
+    if (record) {
+        lp.nparts = grid;  // one partial pick per CTA of the step kernel
+        m.mega_lm = lp;
+        return ROTOR_B200_OK;
+    }
     return launch_lmhead(lp, batch, st);
+}
+
+// Builds (once per batch size) the plan of the single-launch generation step and copies it
+// to the device.  Not to be called inside a stream capture.
+static int mega_prepare(Model& m, int batch, cudaStream_t st) {
+    // Measured slower than the five-launch block on B200 (grid barriers of 148 CTAs cost 2.5-5 us
+    // each, more than a kernel boundary), so the single-launch step is opt-in.
+    static const bool off = getenv("ROTOR_B200_MEGA") == nullptr;
+    if (m.mega_batch == batch) return ROTOR_B200_OK;
+    m.mega_batch = batch;
+    m.mega_ok = 0;
+    if (off || !fused_step_ok(m, batch, 1)) return ROTOR_B200_OK;
+    if (!m.mega_host) m.mega_host = calloc((size_t)m.cfg.n_layers, mega_layer_bytes());
+    if (!m.mega_host) return ROTOR_B200_ERR_ARG;
+    RB_TRY(run_step_fused(m, m.cur_ids, batch, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st, true, true));
+    if (!mega_supported(m.mega_host, m.cfg.n_layers, batch, m.c.d, fused_sm_count())) return ROTOR_B200_OK;
+    RB_CUDA(cudaMemcpyAsync(m.mega_dev, m.mega_host, mega_layer_bytes() * (size_t)m.cfg.n_layers,
+                            cudaMemcpyHostToDevice, st));
+    RB_CUDA(cudaMemsetAsync(m.mega_bar, 0, 2 * sizeof(unsigned), st));
+    RB_CUDA(cudaStreamSynchronize(st));  // the host plan may be rebuilt later; the copy must be done
+    m.mega_ok = 1;
+    return ROTOR_B200_OK;
 }
 
 // ids: device [batch*seq]; the position is read from c.d_pos by the kernels.
@@ -611,6 +656,7 @@ void rotor_b200_model_destroy(void* handle) {
     Model* m = (Model*)handle;
     if (!m) return;
     if (m->graph) cudaGraphExecDestroy(m->graph);
+    free(m->mega_host);
     free(m->layers);
     delete m;
 }
@@ -634,6 +680,7 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
     Model* m = (Model*)handle;
     RB_REQUIRE(m && first_ids && batch > 0 && batch <= m->cfg.max_batch && batch <= 1024);
     RB_REQUIRE(past_len >= 0 && past_len < m->cfg.max_seq);
+    RB_TRY(mega_prepare(*m, batch, as_stream(stream)));
     begin_kernel<<<1, 1024, 0, as_stream(stream)>>>(m->cur_ids, (const long long*)first_ids, batch, m->c.d_pos,
                                                     past_len, m->d_step);
     m->pos = past_len;
@@ -643,6 +690,9 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
 }
 
 static int one_step(Model& m, cudaStream_t st) {
+    if (m.mega_ok && m.mega_batch == m.batch)
+        return launch_decode_step_mega(m.mega_dev, m.mega_host, m.cfg.n_layers, m.batch, m.c.head_dim, m.mega_lm,
+                                       m.mega_bar, library_status_word(), fused_sm_count(), st);
     if (m.batch <= 4)  // pick, token log and position advance ride in the LM head's last CTA
         return run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st, true);
     RB_TRY(run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st));
@@ -658,7 +708,7 @@ int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void*
     if (!use_graph) {
         for (int i = 0; i < nsteps; ++i) RB_TRY(one_step(*m, st));
     } else {
-        if (m->graph && m->graph_batch != m->batch) {
+        if (m->graph && (m->graph_batch != m->batch)) {
             cudaGraphExecDestroy(m->graph);
             m->graph = nullptr;
         }

@@ -69,6 +69,8 @@ int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int 
                       const float* scale, int seg1, int seg2, int ffn_act, cudaStream_t st);
 bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int halves, int merge_weights);
 int configure_fused_gemv();
+int fused_sm_count();
+
 extern int g_use_pdl;
 
 struct QkvFinishParams {
@@ -150,5 +152,15 @@ struct LmHeadParams {
 };
 int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st);
 int lmhead_parts();
+
+// Single-launch generation step (megastep.cu).
+struct FusedGemvParams;
+size_t mega_layer_bytes();
+int mega_record_layer(void* host_plan, int l, const FusedGemvParams* prod4, const AttnDecodeParams& attn);
+int launch_decode_step_mega(const void* dev_plan, const void* host_plan, int n_layers, int batch, int head_dim,
+                            const LmHeadParams& lm, unsigned* bar, unsigned* status, int grid, cudaStream_t st);
+int configure_mega();
+bool mega_supported(const void* host_plan, int n_layers, int batch, int d, int grid);
+unsigned* library_status_word();
 
 }  // namespace rb

@@ -1,0 +1,227 @@
+// Device body of the generation-step BitLinear product (see fused.cu), split so that the
+// single-launch generation step can request the next product's first weight tiles before a
+// grid barrier and run the product after it.
+#pragma once
+#include "gemv_core.cuh"
+#include "leanstage.cuh"
+
+namespace rb {
+
+constexpr int FG_THREADS = 1024;
+constexpr int FG_WARPS = FG_THREADS / 32;
+constexpr int FG_U = 4;  // weight tiles in flight per warp
+constexpr int FG_V = 2;  // float4 groups per thread in the prologue: input width <= 8192
+
+struct FusedGemvParams {
+    const uint4* tiles;   // tiles of the (stacked) matrix
+    int nkt;              // K tiles per row tile
+    int units;            // row tiles per half (paired) or in all (plain)
+    int halves;           // 2: rows u and units*16 + u form one output (gate/up); 1 otherwise
+    int out;              // output rows per half
+    int rows, cols;       // token rows, activation columns (= rows * st.terms)
+    int upc;              // units per CTA (ceil)
+    LeanStage st;
+    float* y;             // [rows][out] float32 outputs
+    float scale[3];       // per-tensor weight scales of up to three stacked row segments
+    int seg1, seg2;       // first row of the second / third segment (plain); halves == 2: scale[0]=gate, [1]=up
+    int ffn_act;
+};
+
+// Shared memory one product needs.
+inline size_t fused_smem(const FusedGemvParams& p) {
+    const size_t xs = (size_t)p.cols * (p.nkt * TILE_K + XS_PAD);
+    const size_t aux = p.st.mode == LM_ATTN ? 2 * (size_t)p.st.n_heads * p.st.nsplit : 0;
+    return xs + (size_t)p.upc * p.halves * 512 + (64 + aux) * sizeof(float);
+}
+
+// Fills the parameter block of one product for a grid of `grid` CTAs.  out: output rows per
+// half.  halves == 2: `tiles` holds the gate matrix followed by the up matrix (each `out`
+// rows), y receives the gated product, scale = {gate, up}.  halves == 1: y receives the
+// product scaled per row segment: rows < seg1 by scale[0], < seg2 by scale[1], the rest by
+// scale[2].  Returns a status code.
+inline int make_fused_params(FusedGemvParams& p, const void* tiles, size_t out, size_t in, int halves, int rows,
+                             const LeanStage& stage, float* y, const float* scale, int seg1, int seg2, int ffn_act,
+                             int grid) {
+    p = {};
+    p.tiles = (const uint4*)tiles;
+    p.nkt = (int)(kpad_of(in) / TILE_K);
+    p.units = (int)(opad_of(out) / TILE_ROWS);
+    p.halves = halves;
+    p.out = (int)out;
+    p.rows = rows;
+    p.cols = rows * stage.terms;
+    p.st = stage;
+    p.y = y;
+    p.scale[0] = scale[0];
+    p.scale[1] = scale[1];
+    p.scale[2] = scale[2];
+    p.seg1 = seg1;
+    p.seg2 = seg2;
+    p.ffn_act = ffn_act;
+    if (p.cols < 1 || p.cols > 8 || stage.terms > 3 || halves < 1 || halves > 2) return ROTOR_B200_ERR_ARG;
+    if (halves == 2 && out % TILE_ROWS) return ROTOR_B200_ERR_SHAPE;
+    if (stage.n != (int)in || in % 4 || in > 4 * FG_V * FG_THREADS) return ROTOR_B200_ERR_SHAPE;
+    if (grid > p.units) grid = p.units;
+    p.upc = (p.units + grid - 1) / grid;
+    return ROTOR_B200_OK;
+}
+
+// Tile ranges of the calling CTA / warp and shared-memory carve-up.
+struct ProductCtx {
+    int8_t* xs;
+    int* merge;
+    float* scratch;
+    float* aux;
+    int xs_stride, slots, u0, u1, w0, w1;
+};
+
+__device__ __forceinline__ ProductCtx product_ctx(const FusedGemvParams& p, unsigned char* smem_raw) {
+    ProductCtx c;
+    const int warp = threadIdx.x >> 5;
+    const int kpad = p.nkt * TILE_K;
+    c.xs_stride = kpad + XS_PAD;
+    c.slots = p.upc * p.halves;
+    c.xs = reinterpret_cast<int8_t*>(smem_raw);                                      // [cols][xs_stride]
+    c.merge = reinterpret_cast<int*>(smem_raw + (size_t)p.cols * c.xs_stride);       // [slots][128]
+    c.scratch = reinterpret_cast<float*>(c.merge + c.slots * 128);                   // [64]
+    c.aux = c.scratch + 64;                                                          // attention merge weights
+    // units (row tiles / row-tile pairs) of this CTA, and the warp's share of their tiles
+    // (32-bit arithmetic: units * gridDim.x stays far below 2^31)
+    c.u0 = (int)((unsigned)p.units * blockIdx.x / gridDim.x);
+    c.u1 = (int)((unsigned)p.units * (blockIdx.x + 1) / gridDim.x);
+    const int ntile = (c.u1 - c.u0) * p.halves * p.nkt;  // local tile index = ((u-u0)*halves + half)*nkt + kt
+    const int nw = blockDim.x >> 5;
+    c.w0 = (int)((unsigned)ntile * (unsigned)warp / (unsigned)nw);
+    c.w1 = (int)((unsigned)ntile * (unsigned)(warp + 1) / (unsigned)nw);
+    return c;
+}
+
+__device__ __forceinline__ const uint4* product_tile_ptr(const FusedGemvParams& p, const ProductCtx& c, int lt) {
+    const int lane = threadIdx.x & 31;
+    const int slot = lt / p.nkt, kt = lt - slot * p.nkt;
+    const int u = c.u0 + slot / p.halves, half = slot - (slot / p.halves) * p.halves;
+    const size_t rt = (size_t)half * p.units + u;
+    return p.tiles + (rt * p.nkt + kt) * 32 + lane;
+}
+
+// Requests the warp's first FG_U weight tiles (constants: may run before the activations
+// this product consumes exist).
+__device__ __forceinline__ void product_prefetch(const FusedGemvParams& p, const ProductCtx& c, uint4 (&wv)[FG_U]) {
+#pragma unroll
+    for (int u = 0; u < FG_U; ++u)
+        if (c.w0 + u < c.w1) wv[u] = ld_stream_v4(product_tile_ptr(p, c, c.w0 + u));
+}
+
+// Prologue, tile products and epilogue.  All threads of the CTA must call; `wv` as left by
+// product_prefetch for the same p.  Uses the CTA barrier.
+template <bool USE_MMA, int NCOL>
+__device__ __forceinline__ void product_run(const FusedGemvParams& p, const ProductCtx& c, uint4 (&wv)[FG_U],
+                                            float* s_sx, int* s_xsum) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    int8_t* xs = c.xs;
+    int* merge = c.merge;
+    float* scratch = c.scratch;
+    float* aux = c.aux;
+    const int xs_stride = c.xs_stride, slots = c.slots, u0 = c.u0, u1 = c.u1, w0 = c.w0, w1 = c.w1;
+    for (int e = threadIdx.x; e < slots * 128; e += blockDim.x) merge[e] = 0;
+    auto tile_ptr = [&](int lt) { return product_tile_ptr(p, c, lt); };
+    TraceRec tr;
+    (void)tr;
+
+    // ---- prologue: activation rows -> int8 in shared memory
+    const bool writer = blockIdx.x == 0;
+    for (int m = 0; m < p.rows; ++m) {
+        float4 v[FG_V];
+        lean_row<FG_V>(p.st, m, v, scratch, aux, writer);
+        lean_quantize<FG_V>(p.st, v, scratch, xs + (size_t)m * p.st.terms * xs_stride, (size_t)xs_stride,
+                            s_sx + m * p.st.terms, s_xsum + m * p.st.terms);
+    }
+    __syncthreads();
+
+    // ---- integer tile products over the warp's range
+    int accm[4][4];
+    int accd[2][4][NCOL];
+    auto clear = [&]() {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) accm[j][r] = 0;
+#pragma unroll
+            for (int c = 0; c < NCOL; ++c) accd[0][j][c] = accd[1][j][c] = 0;
+        }
+    };
+    auto flush = [&](int slot) {  // exact rescale of the per-bit-pair sums, then into the slot
+        int* dst = merge + slot * 128;
+        if constexpr (USE_MMA) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int v = accm[0][r] + (accm[1][r] >> 2) + (accm[2][r] >> 4) + (accm[3][r] >> 6);
+                atomicAdd(dst + (g + 8 * (r >> 1)) * 8 + 2 * t + (r & 1), v);
+            }
+        } else {
+#pragma unroll
+            for (int rh = 0; rh < 2; ++rh)
+#pragma unroll
+                for (int c = 0; c < NCOL; ++c) {
+                    int v = accd[rh][0][c] + (accd[rh][1][c] >> 2) + (accd[rh][2][c] >> 4) + (accd[rh][3][c] >> 6);
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    if (t == 0) atomicAdd(dst + (g + 8 * rh) * 8 + c, v);
+                }
+        }
+    };
+    clear();
+    int cur = -1;
+    for (int base = w0; base < w1; base += FG_U) {
+#pragma unroll
+        for (int u = 0; u < FG_U; ++u) {
+            const int lt = base + u;
+            if (lt < w1) {
+                const int slot = lt / p.nkt, kt = lt - slot * p.nkt;
+                if (slot != cur) {  // warp-uniform
+                    if (cur >= 0) flush(cur);
+                    clear();
+                    cur = slot;
+                }
+                const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+                tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, kt * TILE_K + 32 * t, g, p.cols, accm, accd);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < FG_U; ++u)
+            if (base + FG_U + u < w1) wv[u] = ld_stream_v4(tile_ptr(base + FG_U + u));
+    }
+    if (cur >= 0) flush(cur);
+    __syncthreads();
+
+    // ---- epilogue: the CTA's rows are complete: remove the +1 code offset, dequantise, write
+    const int T = p.st.terms;
+    for (int e = threadIdx.x; e < (u1 - u0) * 16 * p.rows; e += blockDim.x) {
+        const int m = e % p.rows, rl = (e / p.rows) & 15, lu = e / (p.rows * 16);
+        const int orow = (u0 + lu) * TILE_ROWS + rl;
+        if (orow >= p.out) continue;
+        float val[2] = {0.f, 0.f};
+        for (int half = 0; half < p.halves; ++half) {
+            const int* src = merge + (lu * p.halves + half) * 128 + rl * 8 + m * T;
+            float f = 0.f;
+            for (int tt = 0; tt < T; ++tt) f += (float)(src[tt] - s_xsum[m * T + tt]) * s_sx[m * T + tt];
+            val[half] = f;
+        }
+        float r;
+        if (p.halves == 2) {
+            const float gt = val[0] * p.scale[0], up = val[1] * p.scale[1];
+            if (p.ffn_act == ROTOR_B200_FFN_RELU2) {
+                const float q = fmaxf(gt, 0.f);
+                r = q * q * up;
+            } else {
+                const float c = fminf(fmaxf(up, -20.f), 20.f);
+                r = gt * (c / (1.f + expf(-c)));
+            }
+        } else {
+            r = val[0] * (orow < p.seg1 ? p.scale[0] : (orow < p.seg2 ? p.scale[1] : p.scale[2]));
+        }
+        p.y[(size_t)m * p.out + orow] = r;
+    }
+}
+
+}  // namespace rb
