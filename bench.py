@@ -162,11 +162,11 @@ def run_reference(args, rank):
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def gemv_roofline(torch, abi, nmat=64, iters=20):
+def gemv_roofline(torch, abi, nmat=64, iters=20, out=6912, inn=2560):
     """Config 1: ternary GEMV 2560 -> 6912, batch 1 (int8 activations), 64 distinct matrices
-    back to back in one CUDA graph so that weights come from HBM, not L2."""
+    back to back in one CUDA graph so that weights come from HBM, not L2.  With other
+    out/inn the same measurement on another shape."""
     lib = abi.lib
-    out, inn = 6912, 2560
     tb = lib.rotor_b200_tiles_bytes(out, inn)
     tiles = torch.randint(0, 256, (nmat, tb), dtype=torch.uint8, device="cuda")
     tiles &= 0xAA  # codes {0, 2}: valid weights -1/+1; timing does not depend on the values
@@ -288,6 +288,7 @@ def run_b200(args, rank, world):
 
     peak, peak_kind = measured_peak_gbs()
     alg, gsec = gemv_roofline(torch, abi)
+    alg_l, gsec_l = gemv_roofline(torch, abi, nmat=8, iters=10, out=28672, inn=8192)
     ctx_mid = PROMPT_LEN + 1 + W + K // 2
     step_bytes = algorithmic_bytes_per_token(CFG_2B, ctx_mid)
     line = {
@@ -305,8 +306,14 @@ def run_b200(args, rank, world):
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "bitlinear_acc_kernel (ternary GEMV 2560->6912, batch 1)",
                      "achieved": alg / gsec / 1e9, "peak": peak, "unit": "GB/s", "frac": alg / gsec / 1e9 / peak,
-                     "peak_kind": f"{peak_kind} HBM copy bandwidth", "traffic": None,
-                     "bytes_per_launch": alg, "us_per_launch": gsec * 1e6},
+                     "peak_kind": f"{peak_kind} HBM copy bandwidth",
+                     "traffic": 4439552,   # dram read + write per launch, ncu capture in profiles/
+                     "bytes_per_launch": alg, "us_per_launch": gsec * 1e6,
+                     "note": "a 4.4 MB matrix is 0.68 us of HBM time: one launch per matrix is launch-latency bound"},
+        "roofline_large_matrix": {"kernel": "bitlinear_acc_kernel (ternary GEMV 8192->28672, batch 1; 8 distinct 58.7 MB matrices)",
+                                  "achieved": alg_l / gsec_l / 1e9, "peak": peak, "unit": "GB/s",
+                                  "frac": alg_l / gsec_l / 1e9 / peak, "bytes_per_launch": alg_l,
+                                  "us_per_launch": gsec_l * 1e6},
         "step_roofline": {"algorithmic_bytes_per_token": step_bytes, "achieved_gbs": step_bytes * K / sec / 1e9,
                           "frac_of_peak": step_bytes * K / sec / 1e9 / peak},
     }

@@ -294,6 +294,10 @@ int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* x
                        int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st) {
     int rc = ensure_status();
     if (rc) return rc;
+    if (ncols >= GEMM_MIN_COLS && variant == ROTOR_B200_VARIANT_AUTO) {
+        // compute-bound regime: the tiled GEMM writes complete sums into plane 0 (callers use one plane)
+        return launch_gemm_mma(tiles, out, in, xq, xsum, ncols, acc, st);
+    }
     const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
     const size_t kpad = kpad_of(in);
     variant = pick_variant(variant, ncols);
@@ -334,6 +338,8 @@ int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int
     cudaStream_t st = as_stream(stream);
     const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
     const size_t kpad = kpad_of(in);
+    if (ncols >= GEMM_MIN_COLS && variant == ROTOR_B200_VARIANT_AUTO)
+        return launch_gemm_mma(tiles, out, in, xq, xsum, (int)ncols, acc, st);
     variant = pick_variant(variant, (int)(ncols < 8 ? ncols : 8));
     const size_t chunk = variant == ROTOR_B200_VARIANT_MMA ? 8 : 4;
     for (size_t c0 = 0; c0 < ncols; c0 += chunk) {

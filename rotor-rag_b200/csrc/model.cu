@@ -222,7 +222,8 @@ static int gemv(Ctx& c, const void* tiles, size_t out, size_t in, int ncols, int
     const size_t plane_stride = (size_t)ncols * out;
     view->acc = acc;
     view->plane_stride = plane_stride;
-    view->planes = plan.ksplit;
+    // many columns go to the tiled GEMM, which leaves complete sums in the first plane
+    view->planes = (ncols >= GEMM_MIN_COLS && c.variant == ROTOR_B200_VARIANT_AUTO) ? 1 : plan.ksplit;
     view->out = (int)out;
     return launch_gemv_planes(tiles, out, in, c.xq, c.xsum[xs], ncols, acc, plane_stride, plan, c.variant, st);
 }

@@ -63,6 +63,11 @@ int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* x
                        int32_t* acc, size_t plane_stride, const GemvPlan& plan, int variant, cudaStream_t st);
 int gemv_cols_per_launch(int variant, int ncols);
 
+// Many-column product (gemm_mma.cu): complete int32 sums into acc[ncols][out].
+constexpr int GEMM_MIN_COLS = 32;
+int launch_gemm_mma(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
+                    int32_t* acc, cudaStream_t st);
+
 // Generation-step product with the consuming vector stage fused in (fused.cu, leanstage.cuh).
 struct LeanStage;
 int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int rows, const LeanStage& stage, float* y,

@@ -76,6 +76,26 @@ def test_integer_accumulators_bit_exact(ops, abi, variant, shape):
     abi.device_status()
 
 
+@pytest.mark.parametrize("shape", [(6912, 2560, 130), (2560, 6912, 257), (48, 1280, 32), (33, 260, 300), (640, 2560, 1024)])
+def test_many_column_product_bit_exact(ops, abi, shape):
+    """Prefill-sized products (>= 32 activation columns) take the tiled tensor-core GEMM."""
+    out, inn, ncols = shape
+    rng = np.random.default_rng(out * 3 + inn + ncols)
+    w = O.synth_ternary(rng, out, inn)
+    tiles = ops.int8_to_tiles(w)
+    kpad = abi.lib.rotor_b200_in_padded(inn)
+    q = np.zeros((ncols, kpad), dtype=np.int8)
+    q[:, :inn] = rng.integers(-128, 128, size=(ncols, inn), dtype=np.int8)
+    xq = ops.to_device(q)
+    xsum = ops.to_device(q.astype(np.int32).sum(axis=1).astype(np.int32))
+    acc = ops.bitlinear_acc(tiles, out, inn, xq, xsum, abi.VARIANT_AUTO).cpu().numpy()
+    want = q[:, :inn].astype(np.int32) @ w.astype(np.int32).T
+    assert np.array_equal(acc, want)
+    # the column-chunked tensor-core GEMV gives the same integers
+    acc2 = ops.bitlinear_acc(tiles, out, inn, xq, xsum, abi.VARIANT_MMA).cpu().numpy()
+    assert np.array_equal(acc2, want)
+
+
 def test_extreme_values_do_not_overflow(ops, abi):
     """All weights +1 and all activations -128 over the longest row the models use."""
     out, inn = 16, 28672
