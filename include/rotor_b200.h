@@ -195,6 +195,10 @@ typedef struct rotor_b200_model_config {
     int32_t max_seq;      /* positions per sequence the KV cache holds */
     int32_t max_rows;     /* most token rows (batch*seq) in one forward call */
     int32_t gemv_variant; /* ROTOR_B200_VARIANT_* */
+    int32_t tp_size;      /* tensor-parallel ranks (0 or 1 = single GPU).  With tp_size > 1 the head and
+                             FFN counts above stay GLOBAL; every rank holds n_heads/tp query heads,
+                             n_kv_heads/tp KV heads and d_ff/tp FFN channels.  Needs act_terms == 1. */
+    int32_t tp_rank;      /* this process's rank, 0 .. tp_size-1 */
 } rotor_b200_model_config;
 
 /* Device pointers of one transformer block.  qkv_tiles holds the tiles of q, k and v one
@@ -242,6 +246,19 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
 int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void* stream);
 int rotor_b200_model_read_tokens(void* handle, int first_step, int count, int64_t* tokens_host, void* stream);
 int rotor_b200_model_position(void* handle);
+
+/* ---------------------------------------------------------------- tensor parallel (new design)
+ * The reference is single-device.  For models large enough to shard, BitLinear is split
+ * Megatron-style over the GPUs of one box, one process per GPU: q/k/v, gate and up by output
+ * rows (their tiles in rotor_b200_layer_weights hold only this rank's rows), o and down by
+ * input columns (this rank's columns, partial sums all-reduced as exact int32), the LM head
+ * by vocabulary.  rotor_b200_tp_unique_id fills a 128-byte NCCL id on one rank (host memory);
+ * the host side broadcasts it; every rank calls rotor_b200_tp_init with it (collective) and
+ * attaches the communicator to its model.  NCCL is bound at run time from libnccl.so.2. */
+int rotor_b200_tp_unique_id(void* out128_host);
+int rotor_b200_tp_init(int rank, int size, const void* unique_id128_host, void** comm);
+void rotor_b200_tp_destroy(void* comm);
+int rotor_b200_model_set_tp(void* handle, void* comm);
 
 /* Programmatic dependent launch for the decode chain: with 1, every kernel of a step may start
  * and prefetch its weight tiles while its predecessor drains (the kernels order themselves with

@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32) lmhead_kernel(const __grid_cons
 }
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int nparts,
-                                    long long* __restrict__ out) {
+                                    long long* __restrict__ out, float* __restrict__ out_val) {
     const int m = blockIdx.x;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
@@ -59,6 +59,7 @@ __global__ void argmax_final_kernel(const float* __restrict__ part_val, const in
                 bi = sidx[w];
             }
         out[m] = bi;
+        if (out_val) out_val[m] = bv;
     }
 }
 
@@ -121,7 +122,7 @@ int launch_lmhead(const LmHeadParams& pin, int rows, cudaStream_t st) {
     }
     if (rc) return rc;
     if (p.argmax_out && !fused) {
-        argmax_final_kernel<<<rows, 256, 0, st>>>(p.part_val, p.part_idx, p.nparts, p.argmax_out);
+        argmax_final_kernel<<<rows, 256, 0, st>>>(p.part_val, p.part_idx, p.nparts, p.argmax_out, p.argmax_val);
         rc = launch_status();
     }
     return rc;

@@ -193,6 +193,7 @@ __device__ __forceinline__ void lmhead_body(const LmHeadParams& p, int row0, flo
                     bi = ti[w];
                 }
             p.argmax_out[row0 + r] = bi;
+            if (p.argmax_val) p.argmax_val[row0 + r] = bv;
             if (p.adv_log) {
                 const int st = *p.adv_step;
                 if (st < p.adv_max_log) p.adv_log[(size_t)st * NROWS + r] = bi;

@@ -46,6 +46,11 @@ struct Ctx {
     int nsplit;
     int max_batch;
     unsigned* counters;  // [8 + max_batch] zeroed words for last-CTA tails
+    // tensor parallel (tp_size > 1): communicator, whole FFN width, exchange buffers
+    void* tp;
+    int tp_size, ff_total;
+    float* stat[2];      // [rows] per-row statistics that cross ranks (sum of squares, absolute maximum)
+    float* gated;        // [rows][ff] this rank's slice of the gated FFN row
     // float32 outputs of the fused generation step's products: q/k/v, o, gated, down
     float* fy[4];
 };
@@ -76,6 +81,11 @@ struct Model {
     LmHeadParams mega_lm;
     int mega_batch;   // batch the plan is valid for (0 = none)
     int mega_ok;      // the device can run the step kernel for that plan
+    // tensor parallel greedy pick: (value, global index) of every rank's best row
+    float* pick_val;      // [rows]
+    long long* pick_idx;  // [rows]
+    unsigned char* pick_send;  // [rows] x 12 bytes
+    unsigned char* pick_recv;  // [tp][rows] x 12 bytes
 };
 
 struct Carve {
@@ -91,17 +101,29 @@ struct Carve {
 
 static int max_planes(size_t out, size_t in) { return plan_gemv(out, in, 8).ksplit; }
 
-static int derive_ctx(Ctx& c, int d_model, int n_heads, int n_kv_heads, int d_ff, int terms) {
+// Dimensions of one rank: with tp > 1 the heads and the FFN width are this rank's share
+// (query / KV heads and d_ff divided by tp), d_model stays whole.
+static int derive_ctx(Ctx& c, int d_model, int n_heads, int n_kv_heads, int d_ff, int terms, int tp = 1) {
     if (d_model <= 0 || n_heads <= 0 || n_kv_heads <= 0 || d_ff <= 0) return ROTOR_B200_ERR_ARG;
     if (terms < 1 || terms > 4) return ROTOR_B200_ERR_ARG;
     if (d_model % n_heads || n_heads % n_kv_heads) return ROTOR_B200_ERR_SHAPE;
+    if (tp < 1) tp = 1;
+    c.head_dim = d_model / n_heads;  // head_dim = d_model // n_heads, src/rotor/transformer.py:192
+    if (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128) return ROTOR_B200_ERR_SHAPE;
+    c.ff_total = d_ff;
+    c.tp_size = tp;
+    if (tp > 1) {
+        // whole heads and whole FFN channels per rank
+        if (n_heads % tp || n_kv_heads % tp || d_ff % tp) return ROTOR_B200_ERR_SHAPE;
+        n_heads /= tp;
+        n_kv_heads /= tp;
+        d_ff /= tp;
+    }
     c.d = d_model;
     c.ff = d_ff;
     c.n_heads = n_heads;
     c.n_kv_heads = n_kv_heads;
     c.terms = terms;
-    c.head_dim = d_model / n_heads;  // head_dim = d_model // n_heads, src/rotor/transformer.py:192
-    if (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128) return ROTOR_B200_ERR_SHAPE;
     c.dq = n_heads * c.head_dim;
     c.dkv = n_kv_heads * c.head_dim;
     if (c.dq % 16 || c.dkv % 16 || d_ff % 16) return ROTOR_B200_ERR_SHAPE;  // stacked products need whole row tiles
@@ -139,6 +161,9 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     c.part_m = cv.take<float>(heads);
     c.part_l = cv.take<float>(heads);
     c.counters = cv.take<unsigned>(8 + (size_t)c.max_batch);
+    c.stat[0] = cv.take<float>(rows);
+    c.stat[1] = cv.take<float>(rows);
+    c.gated = cv.take<float>(c.tp_size > 1 ? rows * ff : 1);
     const size_t outs[4] = {qkv_out, d, ff, d};
     for (int i = 0; i < 4; ++i) c.fy[i] = cv.take<float>(FUSED_MAX_ROWS * outs[i]);
 }
@@ -168,6 +193,11 @@ static void carve(Model& m, unsigned char* base, size_t* total) {
     m.d_step = cv.take<int>(1);
     m.mega_dev = cv.take<unsigned char>(mega_layer_bytes() * (size_t)c.n_layers);
     m.mega_bar = cv.take<unsigned>(2);
+    const size_t tp = c.tp_size > 1 ? c.tp_size : 1;
+    m.pick_val = cv.take<float>(rows);
+    m.pick_idx = cv.take<long long>(rows);
+    m.pick_send = cv.take<unsigned char>(rows * 12);
+    m.pick_recv = cv.take<unsigned char>(tp * rows * 12);
     *total = cv.off;
 }
 
@@ -175,8 +205,12 @@ static int derive(Model& m) {
     const rotor_b200_model_config& c = m.cfg;
     if (c.vocab_size <= 0 || c.n_layers <= 0 || c.max_batch <= 0 || c.max_seq <= 0 || c.max_rows <= 0)
         return ROTOR_B200_ERR_ARG;
-    int rc = derive_ctx(m.c, c.d_model, c.n_heads, c.n_kv_heads, c.d_ff, c.act_terms);
+    int rc = derive_ctx(m.c, c.d_model, c.n_heads, c.n_kv_heads, c.d_ff, c.act_terms, c.tp_size);
     if (rc) return rc;
+    if (c.tp_size > 1) {
+        if (c.act_terms != 1) return ROTOR_B200_ERR_SHAPE;      // sharded rows share one absmax per row: one term only
+        if (c.vocab_size % c.tp_size || c.tp_rank < 0 || c.tp_rank >= c.tp_size) return ROTOR_B200_ERR_SHAPE;
+    }
     m.c.max_batch = c.max_batch;
     if (c.d_model % 256) return ROTOR_B200_ERR_SHAPE;  // LM head reads 256 columns per warp step
     m.c.ffn_act = c.ffn_act;
@@ -396,7 +430,7 @@ static bool fused_step_ok(const Model& m, int batch, int seq) {
     const Ctx& c = m.c;
     static const bool off = getenv("ROTOR_B200_NO_FUSED_STEP") != nullptr;  // measurement aid
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
-    return !off && seq == 1 && batch <= FUSED_MAX_ROWS && batch <= c.max_batch && c.terms <= 3 &&
+    return !off && c.tp_size <= 1 && seq == 1 && batch <= FUSED_MAX_ROWS && batch <= c.max_batch && c.terms <= 3 &&
            batch * c.terms <= 8 && c.ff % 16 == 0 &&
            fused_gemv_supported(qkv_out, c.d, batch, c.terms, 1, 0) &&
            fused_gemv_supported(c.d, c.dq, batch, c.terms, 1, c.n_heads * c.nsplit) &&
@@ -539,10 +573,265 @@ static int mega_prepare(Model& m, int batch, cudaStream_t st) {
     return ROTOR_B200_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// Tensor-parallel forward (one process per GPU).  q/k/v, gate and up are split by output
+// rows (whole heads / FFN channels per rank), o and down by input columns; their int32
+// partial sums are all-reduced (exact: every rank quantises its slice of the input with the
+// row's global absolute maximum, obtained with a one-float-per-row all-reduce, so all ranks
+// share the activation scale).  The FFN sub-norm runs over the sharded row and needs the
+// global sum of squares the same way.  Per block: 3 one-float-per-row all-reduces and
+// 2 all-reduces of rows*d_model int32.  The LM head is split by vocabulary; the greedy pick
+// all-gathers one (value, index) pair per rank and row.
+__global__ void pack_pick_kernel(const float* val, const long long* idx, long long idx_offset, int rows,
+                                 unsigned char* out) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    float v = val[r];
+    long long i = idx[r] + idx_offset;
+    memcpy(out + (size_t)r * 12, &v, 4);
+    memcpy(out + (size_t)r * 12 + 4, &i, 8);
+}
+
+__global__ void final_pick_kernel(const unsigned char* recv, int tp, int rows, long long* out) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    float bv = -INFINITY;
+    long long bi = 0x7fffffffffffffffLL;
+    for (int k = 0; k < tp; ++k) {
+        float v;
+        long long i;
+        memcpy(&v, recv + ((size_t)k * rows + r) * 12, 4);
+        memcpy(&i, recv + ((size_t)k * rows + r) * 12 + 4, 8);
+        if (v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    out[r] = bi;
+}
+
+static int acc1(Ctx& c, const void* tiles, size_t out, size_t in, int ncols, int xs, int32_t* acc, AccView* view,
+                cudaStream_t st) {
+    view->acc = acc;
+    view->plane_stride = 0;
+    view->planes = 1;
+    view->out = (int)out;
+    return rotor_b200_bitlinear_acc(tiles, out, in, c.xq, c.xsum[xs], (size_t)ncols, acc, c.variant, st);
+}
+
+static int run_layers_tp(Model& m, const long long* ids, int batch, int seq, int logits_mode, float* logits,
+                         long long* next_ids, cudaStream_t st, bool advance) {
+    Ctx& c = m.c;
+    const int rows = batch * seq, d = c.d, cols = rows;  // one activation term
+    const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
+    VecStageParams e = {};
+    e.mode = VS_EMBED;
+    e.n = d;
+    e.ids = ids;
+    e.embed = m.embed;
+    e.h = c.h;
+    e.norm1 = m.layers[0].input_norm;
+    e.eps = c.eps;
+    quant_sink(c, e, 0, d);
+    RB_TRY(launch_vec_stage(e, rows, st));
+    for (int l = 0; l < m.cfg.n_layers; ++l) {
+        const rotor_b200_layer_weights& L = m.layers[l];
+        AccView va, vb;
+        // ---- attention on this rank's heads
+        RB_TRY(acc1(c, L.qkv_tiles, qkv_out, d, cols, 0, c.accA, &va, st));
+        if (seq == 1 && batch <= c.max_batch) {
+            AttnDecodeParams dp = {};
+            dp.acc = va;
+            dp.sx = c.sx[0];
+            dp.terms = 1;
+            dp.sq = L.q_scale;
+            dp.sk = L.k_scale;
+            dp.sv = L.v_scale;
+            dp.n_heads = c.n_heads;
+            dp.n_kv_heads = c.n_kv_heads;
+            dp.head_dim = c.head_dim;
+            dp.max_seq = c.max_seq;
+            dp.nsplit = c.nsplit;
+            dp.past_len = c.d_pos;
+            dp.rope = c.rope;
+            dp.k_cache = L.k_cache;
+            dp.v_cache = L.v_cache;
+            dp.part_o = c.part_o;
+            dp.part_m = c.part_m;
+            dp.part_l = c.part_l;
+            dp.counter = c.counters + 8;
+            dp.attn_out = c.attn;  // merged rows as float; quantised below with the global maximum
+            RB_TRY(launch_attn_decode(dp, batch, st));
+        } else {
+            QkvFinishParams qf = {};
+            qf.acc = va;
+            qf.sx = c.sx[0];
+            qf.terms = 1;
+            qf.sq = L.q_scale;
+            qf.sk = L.k_scale;
+            qf.sv = L.v_scale;
+            qf.n_heads = c.n_heads;
+            qf.n_kv_heads = c.n_kv_heads;
+            qf.head_dim = c.head_dim;
+            qf.seq = seq;
+            qf.past_len = c.d_pos;
+            qf.max_seq = c.max_seq;
+            qf.rope = c.rope;
+            qf.q = c.qbuf;
+            qf.k_cache = L.k_cache;
+            qf.v_cache = L.v_cache;
+            RB_TRY(launch_qkv_finish(qf, rows, st));
+            AttnParams ap = {};
+            ap.q = c.qbuf;
+            ap.k_cache = L.k_cache;
+            ap.v_cache = L.v_cache;
+            ap.out = c.attn;
+            ap.n_heads = c.n_heads;
+            ap.n_kv_heads = c.n_kv_heads;
+            ap.head_dim = c.head_dim;
+            ap.seq = seq;
+            ap.past_len = c.d_pos;
+            ap.max_seq = c.max_seq;
+            ap.causal = c.causal;
+            RB_TRY(launch_attention(ap, rows, st));
+        }
+        // o projection input: global absolute maximum, then quantise the local slice
+        VecStageParams sa = {};
+        sa.mode = VS_PLAIN;
+        sa.n = c.dq;
+        sa.src = c.attn;
+        sa.eps = c.eps;
+        sa.out_absmax = c.stat[0];
+        RB_TRY(launch_vec_stage(sa, rows, st));
+        RB_TRY(tp_allreduce_f32(c.tp, c.stat[0], rows, true, st));
+        VecStageParams qa = {};
+        qa.mode = VS_PLAIN;
+        qa.n = c.dq;
+        qa.src = c.attn;
+        qa.eps = c.eps;
+        qa.ext_absmax = c.stat[0];
+        quant_sink(c, qa, 1, c.dq);
+        RB_TRY(launch_vec_stage(qa, rows, st));
+        RB_TRY(acc1(c, L.o_tiles, d, c.dq, cols, 1, c.accB, &vb, st));
+        RB_TRY(tp_allreduce_sum_i32(c.tp, c.accB, (size_t)cols * d, st));
+        VecStageParams op = {};
+        op.mode = VS_OPROJ;
+        op.n = d;
+        op.acc = vb;
+        op.sx_in = c.sx[1];
+        op.terms = 1;
+        op.wscale0 = L.o_scale;
+        op.norm0 = L.attn_sub_norm;
+        op.h = c.h;
+        op.norm1 = L.post_attn_norm;
+        op.eps = c.eps;
+        quant_sink(c, op, 0, d);
+        RB_TRY(launch_vec_stage(op, rows, st));
+        // ---- FFN on this rank's channels
+        RB_TRY(acc1(c, L.gate_up_tiles, 2 * (size_t)c.ff, d, cols, 0, c.accA, &va, st));
+        VecStageParams fp = {};
+        fp.mode = VS_FFN;
+        fp.n = c.ff;
+        fp.acc = va;
+        fp.sx_in = c.sx[0];
+        fp.terms = 1;
+        fp.wscale0 = L.gate_scale;
+        fp.wscale1 = L.up_scale;
+        fp.ffn_act = c.ffn_act;
+        fp.eps = c.eps;
+        fp.y_out = c.gated;
+        fp.out_sumsq = c.stat[0];
+        RB_TRY(launch_vec_stage(fp, rows, st));
+        RB_TRY(tp_allreduce_f32(c.tp, c.stat[0], rows, false, st));
+        VecStageParams fn = {};
+        fn.mode = VS_PLAIN;
+        fn.n = c.ff;
+        fn.src = c.gated;
+        fn.norm1 = L.ffn_sub_norm;  // this rank's slice of the sub-norm weight
+        fn.ext_sumsq = c.stat[0];
+        fn.norm_n = c.ff_total;
+        fn.eps = c.eps;
+        fn.y_out = c.gated;
+        fn.out_absmax = c.stat[1];
+        RB_TRY(launch_vec_stage(fn, rows, st));
+        RB_TRY(tp_allreduce_f32(c.tp, c.stat[1], rows, true, st));
+        VecStageParams fq = {};
+        fq.mode = VS_PLAIN;
+        fq.n = c.ff;
+        fq.src = c.gated;
+        fq.eps = c.eps;
+        fq.ext_absmax = c.stat[1];
+        quant_sink(c, fq, 1, c.ff);
+        RB_TRY(launch_vec_stage(fq, rows, st));
+        RB_TRY(acc1(c, L.down_tiles, d, c.ff, cols, 1, c.accB, &vb, st));
+        RB_TRY(tp_allreduce_sum_i32(c.tp, c.accB, (size_t)cols * d, st));
+        VecStageParams dn = {};
+        dn.mode = VS_DOWN;
+        dn.n = d;
+        dn.acc = vb;
+        dn.sx_in = c.sx[1];
+        dn.terms = 1;
+        dn.wscale0 = L.down_scale;
+        dn.h = c.h;
+        dn.eps = c.eps;
+        const bool last = l + 1 == m.cfg.n_layers;
+        dn.norm1 = last ? m.final_norm : m.layers[l + 1].input_norm;
+        if (last)
+            dn.y_out = c.hn;
+        else
+            quant_sink(c, dn, 0, d);
+        RB_TRY(launch_vec_stage(dn, rows, st));
+    }
+    if (logits_mode == ROTOR_B200_LOGITS_NONE && !next_ids) return ROTOR_B200_OK;
+
+    // ---- LM head over this rank's vocabulary slice; logits (if asked for) are the local slice
+    const bool all = logits_mode == ROTOR_B200_LOGITS_ALL;
+    const int vl = m.cfg.vocab_size / c.tp_size, rank = tp_rank(c.tp);
+    const float* x = c.hn;
+    int lm_rows = rows;
+    if (!all && seq > 1) {
+        for (int b = 0; b < batch; ++b)
+            RB_CUDA(cudaMemcpyAsync(c.qbuf + (size_t)b * d, c.hn + ((size_t)b * seq + seq - 1) * d, d * sizeof(float),
+                                    cudaMemcpyDeviceToDevice, st));
+        x = c.qbuf;
+        lm_rows = batch;
+    }
+    LmHeadParams lp = {};
+    lp.embed = m.embed + (size_t)rank * vl * d;
+    lp.x = x;
+    lp.vocab = vl;
+    lp.d = d;
+    lp.logits = logits_mode == ROTOR_B200_LOGITS_NONE ? nullptr : logits;
+    lp.part_val = m.part_val;
+    lp.part_idx = m.part_idx;
+    const bool pick = next_ids && !(all && seq > 1);
+    lp.argmax_out = pick ? m.pick_idx : nullptr;
+    lp.argmax_val = pick ? m.pick_val : nullptr;
+    lp.nparts = lmhead_parts();
+    RB_TRY(launch_lmhead(lp, lm_rows, st));
+    if (pick) {
+        pack_pick_kernel<<<(lm_rows + 127) / 128, 128, 0, st>>>(m.pick_val, m.pick_idx, (long long)rank * vl, lm_rows,
+                                                                m.pick_send);
+        RB_TRY(launch_status());
+        RB_TRY(tp_allgather_bytes(c.tp, m.pick_send, m.pick_recv, (size_t)lm_rows * 12, st));
+        final_pick_kernel<<<(lm_rows + 127) / 128, 128, 0, st>>>(m.pick_recv, c.tp_size, lm_rows, next_ids);
+        RB_TRY(launch_status());
+    }
+    if (advance) {
+        advance_kernel<<<1, 1024, 0, st>>>(next_ids, m.tok_log, batch, m.max_log, c.d_pos, m.d_step);
+        RB_TRY(launch_status());
+    }
+    return ROTOR_B200_OK;
+}
+
 // ids: device [batch*seq]; the position is read from c.d_pos by the kernels.
 static int run_layers(Model& m, const long long* ids, int batch, int seq, int logits_mode, float* logits,
                       long long* next_ids, cudaStream_t st, bool advance = false) {
     Ctx& c = m.c;
+    if (c.tp_size > 1) {
+        if (!c.tp) return ROTOR_B200_ERR_ARG;  // rotor_b200_model_set_tp has not been called
+        return run_layers_tp(m, ids, batch, seq, logits_mode, logits, next_ids, st, advance);
+    }
     if (fused_step_ok(m, batch, seq) && (logits_mode != ROTOR_B200_LOGITS_NONE || next_ids))
         return run_step_fused(m, ids, batch, logits_mode, logits, next_ids, st, advance);
     const int rows = batch * seq, d = c.d;
@@ -691,6 +980,8 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
 }
 
 static int one_step(Model& m, cudaStream_t st) {
+    if (m.c.tp_size > 1)
+        return run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st, true);
     if (m.mega_ok && m.mega_batch == m.batch)
         return launch_decode_step_mega(m.mega_dev, m.mega_host, m.cfg.n_layers, m.batch, m.c.head_dim, m.mega_lm,
                                        m.mega_bar, library_status_word(), fused_sm_count(), st);
@@ -746,6 +1037,16 @@ int rotor_b200_model_read_tokens(void* handle, int first_step, int count, int64_
     RB_CUDA(cudaMemcpyAsync(tokens_host, m->tok_log + (size_t)first_step * m->batch,
                             (size_t)count * m->batch * sizeof(int64_t), cudaMemcpyDeviceToHost, st));
     RB_CUDA(cudaStreamSynchronize(st));
+    return ROTOR_B200_OK;
+}
+
+/* Attaches the tensor-parallel communicator (made by rotor_b200_tp_init) to a model created with
+ * tp_size > 1.  The handle's rank must match the configuration's tp_rank. */
+int rotor_b200_model_set_tp(void* handle, void* comm) {
+    Model* m = (Model*)handle;
+    RB_REQUIRE(m && comm && m->cfg.tp_size > 1);
+    RB_REQUIRE(tp_size(comm) == m->cfg.tp_size && tp_rank(comm) == m->cfg.tp_rank);
+    m->c.tp = comm;
     return ROTOR_B200_OK;
 }
 

@@ -46,6 +46,12 @@ struct VecStageParams {
     int32_t* xsum_out;
     int terms_out;
     int kpad;
+    // Sharded rows (tensor parallel): the row is one rank's slice of a longer row.
+    const float* ext_sumsq;      // [rows] sum of squares of the whole row, used by norm1 instead of the local one
+    int norm_n;                  // width of the whole row for norm1's mean (0 = n)
+    const float* ext_absmax;     // [rows] max|.| of the whole row, used by the quantiser
+    float* out_sumsq;            // [rows] optional: local sum of squares of the built row (before norm1)
+    float* out_absmax;           // [rows] optional: local max|.| of the row after norm1
 };
 
 int launch_vec_stage(const VecStageParams& p, int rows, cudaStream_t st);
@@ -143,6 +149,7 @@ struct LmHeadParams {
     float* part_val;             // [rows][nparts]
     int* part_idx;
     long long* argmax_out;       // [rows]
+    float* argmax_val;           // optional [rows]: the picked logit (vocabulary-sharded picks compare them)
     int nparts;
     unsigned* tail_counter;      // zeroed word: enables the fused pick when rows fit one launch
     long long* adv_log;          // optional: token log [max_log][rows]; also advances *adv_pos, *adv_step
@@ -167,5 +174,12 @@ int launch_decode_step_mega(const void* dev_plan, const void* host_plan, int n_l
 int configure_mega();
 bool mega_supported(const void* host_plan, int n_layers, int batch, int d, int grid);
 unsigned* library_status_word();
+
+// Tensor-parallel collectives (tp.cu); `comm` is the handle made by rotor_b200_tp_init.
+int tp_rank(void* comm);
+int tp_size(void* comm);
+int tp_allreduce_sum_i32(void* comm, int32_t* buf, size_t n, cudaStream_t st);
+int tp_allreduce_f32(void* comm, float* buf, size_t n, bool max_op, cudaStream_t st);
+int tp_allgather_bytes(void* comm, const void* send, void* recv, size_t bytes_per_rank, cudaStream_t st);
 
 }  // namespace rb

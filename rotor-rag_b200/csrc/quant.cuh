@@ -23,15 +23,22 @@ __device__ __forceinline__ float exact_quant(float v, float s, float rs) {
 // scratch  : shared memory, 33 floats
 // All threads of the block must call; blockDim.x is a multiple of 32.
 // tstride   : bytes between consecutive terms in xq (>= kpad; xq may be shared memory)
+// given_absmax : optional max|row| of term 0 supplied by the caller (sharded rows)
 __device__ __forceinline__ void quantize_row_from_smem(float* row, int k, int kpad, int terms,
                                                        int8_t* __restrict__ xq, float* __restrict__ sx,
                                                        int32_t* __restrict__ xsum, float* scratch,
-                                                       size_t tstride = 0) {
+                                                       size_t tstride = 0, const float* given_absmax = nullptr) {
     if (tstride == 0) tstride = (size_t)kpad;
     for (int t = 0; t < terms; ++t) {
         float mx = 0.f;
-        for (int i = threadIdx.x; i < k; i += blockDim.x) mx = fmaxf(mx, fabsf(row[i]));
-        mx = block_max(mx, scratch);
+        if (t == 0 && given_absmax) {
+            // the row is a slice of a longer one: the absolute maximum of the whole row comes from outside
+            mx = *given_absmax;
+            __syncthreads();
+        } else {
+            for (int i = threadIdx.x; i < k; i += blockDim.x) mx = fmaxf(mx, fabsf(row[i]));
+            mx = block_max(mx, scratch);
+        }
         const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
         const float rs = __fdiv_rn(1.0f, s);
         int lsum = 0;

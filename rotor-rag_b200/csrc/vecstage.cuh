@@ -10,8 +10,10 @@ constexpr int VS_U = 8;  // elements per thread whose global loads are in flight
 
 // y[i] = row[i] / sqrt(mean(row^2) + eps) * w[i], in place.  The first batch of norm
 // weights is requested before the reduction so that its latency hides behind it.
+// ext_ss / n_total: when the row is a slice of a longer one, the sum of squares and width of
+// the whole row (nullptr / 0 = this row alone).
 __device__ __forceinline__ void rmsnorm_inplace(float* row, int n, const float* __restrict__ w, float eps,
-                                                float* scratch) {
+                                                float* scratch, const float* ext_ss = nullptr, int n_total = 0) {
     const int bd = blockDim.x;
     float wv[VS_U];
 #pragma unroll
@@ -22,7 +24,8 @@ __device__ __forceinline__ void rmsnorm_inplace(float* row, int n, const float* 
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += bd) ss += row[i] * row[i];
     ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    if (ext_ss) ss = *ext_ss;
+    const float inv = 1.0f / sqrtf(ss / (float)(n_total ? n_total : n) + eps);
     for (int i0 = threadIdx.x; i0 < n; i0 += VS_U * bd) {
         float wn[VS_U];
 #pragma unroll
@@ -257,8 +260,22 @@ __device__ __forceinline__ void vec_stage_row(const VecStageParams& p, int m, fl
     }
     __syncthreads();
 
-    // ---- pre-norm of the consumer, then its quantiser (or a float copy for the LM head)
-    if (p.norm1) rmsnorm_inplace(row, n, p.norm1, p.eps, scratch);
+    // ---- statistics for sharded rows, pre-norm of the consumer, then its quantiser (or a float copy)
+    if (p.out_sumsq) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) ss += row[i] * row[i];
+        ss = block_sum(ss, scratch);
+        if (threadIdx.x == 0 && writer) p.out_sumsq[m] = ss;
+        __syncthreads();
+    }
+    if (p.norm1) rmsnorm_inplace(row, n, p.norm1, p.eps, scratch, p.ext_sumsq ? p.ext_sumsq + m : nullptr, p.norm_n);
+    if (p.out_absmax) {
+        float mx = 0.f;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) mx = fmaxf(mx, fabsf(row[i]));
+        mx = block_max(mx, scratch);
+        if (threadIdx.x == 0 && writer) p.out_absmax[m] = mx;
+        __syncthreads();
+    }
     if (p.y_out && writer)
         for (int i = threadIdx.x; i < n; i += blockDim.x) p.y_out[(size_t)m * n + i] = row[i];
     if (sink) {
@@ -267,7 +284,8 @@ __device__ __forceinline__ void vec_stage_row(const VecStageParams& p, int m, fl
     } else if (p.xq && writer) {
         __syncthreads();
         quantize_row_from_smem(row, n, p.kpad, p.terms_out, p.xq + (size_t)m * p.terms_out * p.kpad,
-                               p.sx_out + (size_t)m * p.terms_out, p.xsum_out + (size_t)m * p.terms_out, scratch);
+                               p.sx_out + (size_t)m * p.terms_out, p.xsum_out + (size_t)m * p.terms_out, scratch, 0,
+                               p.ext_absmax ? p.ext_absmax + m : nullptr);
     }
 }
 

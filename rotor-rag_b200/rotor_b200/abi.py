@@ -72,7 +72,7 @@ class ModelConfig(C.Structure):
                 ("act_terms", C.c_int32), ("ffn_act", C.c_int32), ("causal", C.c_int32),
                 ("rope_theta", C.c_float), ("eps", C.c_float),
                 ("max_batch", C.c_int32), ("max_seq", C.c_int32), ("max_rows", C.c_int32),
-                ("gemv_variant", C.c_int32)]
+                ("gemv_variant", C.c_int32), ("tp_size", C.c_int32), ("tp_rank", C.c_int32)]
 
 
 class LayerWeights(C.Structure):
@@ -101,6 +101,10 @@ _SIGNATURES.update({
     "rotor_b200_model_position": (_i, [_p]),
     "rotor_b200_block_workspace_bytes": (_sz, [_cfgp, _i]),
     "rotor_b200_set_pdl": (_i, [_i]),
+    "rotor_b200_tp_unique_id": (_i, [_p]),
+    "rotor_b200_tp_init": (_i, [_i, _i, _p, C.POINTER(_p)]),
+    "rotor_b200_tp_destroy": (None, [_p]),
+    "rotor_b200_model_set_tp": (_i, [_p, _p]),
     "rotor_b200_ffn_forward": (_i, [_cfgp, _lwp, _p, _p, _i, _p, _p, _sz, _p]),
     "rotor_b200_attention_forward": (_i, [_cfgp, _lwp, _p, _i, _i, _i, _p, _p, _sz, _p]),
 })

@@ -260,3 +260,23 @@ def test_batched_forward_and_cache_growth(rb):
     want2, _ = O.model_forward(om, long_ids, O.REFERENCE)
     got2, _ = model.forward(long_ids)
     assert rel_err(got2, want2) < TOL
+
+
+def test_prefill_and_stepwise_decode_agree(rb):
+    """Size-independent property of the cached path (causal semantics): the last-position logits
+    of one forward over n+1 tokens equal those of a forward over n tokens followed by a one-token
+    step.  The prefill side runs the tiled tensor-core GEMM (>= 32 columns), the step the fused
+    generation kernels."""
+    om, prompt, model = _tiny(rb, "hd128", rb.sem.BASELINE, max_rows=64)
+    rng = np.random.default_rng(17)
+    ids = rng.integers(0, om["cfg"]["vocab_size"], size=(1, 41))
+    full, _ = model.forward(ids, logits_positions="last")
+    _, cache = model.forward(ids[:, :40], use_cache=True, logits_positions="last")
+    step, _ = model.forward(ids[:, 40:], past_kv_cache=cache, use_cache=True, logits_positions="last")
+    # int8 rounding decisions can differ between the two routes only through float32 summation order
+    assert rel_err(step[0, -1], full[0, -1]) < 2e-2
+    ref = rb.synth.model_from_oracle_params(om, semantics=rb.sem.REFERENCE.with_(causal=True), max_seq=64)
+    full_r, _ = ref.forward(ids, logits_positions="last")
+    _, cache_r = ref.forward(ids[:, :40], use_cache=True, logits_positions="last")
+    step_r, _ = ref.forward(ids[:, 40:], past_kv_cache=cache_r, use_cache=True, logits_positions="last")
+    assert rel_err(step_r[0, -1], full_r[0, -1]) < TOL
