@@ -21,6 +21,10 @@ One JSON line is printed by rank 0:
   cpu_baseline  the NumPy oracle port of the reference's path on this box's host cores,
              bounded sample (N = 1 only)
 --impl reference times that same CPU port as the reference arm.
+
+--workload xl_tp is a second, separate measurement (not the headline line): the 80-layer
+d 8192 / FFN 28672 shape sharded tensor-parallel over the N GPUs of the launch (strong
+scaling: one sequence, every rank works on every token), batch-1 greedy decode.
 """
 import argparse
 import json
@@ -327,6 +331,96 @@ def run_b200(args, rank, world):
         dist.destroy_process_group()
 
 
+def run_xl_tp(args, rank, world):
+    """Batch-1 greedy decode of the XL shape, sharded over `world` GPUs (1 = unsharded)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from rotor_b200 import abi, semantics
+    from rotor_b200.synth import XL_TP, random_model_on_device
+    from rotor_b200.tensor_parallel import ShardedBitNetModel, TPGroup
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    cfg = dict(XL_TP)
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    K, W = args.steps, max(args.warmup, 3)
+    max_seq = PROMPT_LEN + 1 + W + K + 8
+    sem = semantics.BASELINE
+    group = None
+    if world > 1:
+        dist.init_process_group("gloo")   # carries the communicator id only; the data path is the library's NCCL
+        group = TPGroup()
+        model = ShardedBitNetModel(cfg, group, semantics=sem, max_seq=max_seq, max_rows=PROMPT_LEN)
+        model.load_random(seed=4321)
+        handle = model._ensure_handle(1, PROMPT_LEN, max_seq)
+    else:
+        model = random_model_on_device(cfg, seed=4321, semantics=sem, max_seq=max_seq, max_rows=PROMPT_LEN)
+        handle = model._ensure_handle(1, PROMPT_LEN, max_seq).h
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    prompt = np.random.default_rng(7).integers(0, cfg["vocab_size"], size=PROMPT_LEN).astype(np.int64)
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        s = st.cuda_stream
+        ids_d = torch.from_numpy(prompt.reshape(1, -1)).cuda()
+        first = torch.empty(1, dtype=torch.int64, device="cuda")
+        abi.check(abi.lib.rotor_b200_model_forward(handle, ids_d.data_ptr(), 1, PROMPT_LEN, 0, abi.LOGITS_NONE, None,
+                                                   first.data_ptr(), s), "prefill")
+        abi.check(abi.lib.rotor_b200_model_decode_begin(handle, first.data_ptr(), 1, PROMPT_LEN, s), "begin")
+        abi.check(abi.lib.rotor_b200_model_decode_steps(handle, W, int(args.graph), s), "warmup")
+        barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
+        time.sleep(0.25)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        before = abi.lib.rotor_b200_launch_count()
+        t0 = time.time()
+        e0.record(st)
+        abi.check(abi.lib.rotor_b200_model_decode_steps(handle, K, int(args.graph), s), "timed steps")
+        e1.record(st)
+        st.synchronize()
+        barrier()
+        t1 = time.time()
+        clocks = sampler.stop(t0, t1)
+        launches = abi.lib.rotor_b200_launch_count() - before
+        sec = e0.elapsed_time(e1) * 1e-3
+        toks = np.empty(W + K, dtype=np.int64)
+        abi.check(abi.lib.rotor_b200_model_read_tokens(handle, 0, W + K, toks.ctypes.data, s), "read_tokens")
+    abi.device_status()
+    if world > 1:
+        t = torch.tensor([sec], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t[0])
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        step_bytes = algorithmic_bytes_per_token(cfg, PROMPT_LEN + 1 + W + K // 2)
+        print(json.dumps({
+            "metric": "XL-shape greedy decode tokens/s (batch 1, tensor parallel)", "value": K / sec, "unit": UNIT,
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": sec * 1e3 / K, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "data": "synthetic",
+            "dtype": "int8 activations x ternary weights -> int32 (float32 glue, bf16 LM head)",
+            "config": {"workload": f"random-init {cfg['n_layers']}-layer d {cfg['d_model']} ffn {cfg['d_ff']} "
+                                   f"{cfg['n_heads']}q/{cfg['n_kv_heads']}kv model, greedy decode batch 1 after a "
+                                   f"{PROMPT_LEN}-token prompt", "parallelism": f"tp{world}",
+                       "cuda_graph": bool(args.graph), "l2": "inputs larger than L2"},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "step_roofline": {"algorithmic_bytes_per_token_all_ranks": step_bytes,
+                              "achieved_gbs_per_gpu": step_bytes / world * K / sec / 1e9,
+                              "frac_of_peak": step_bytes / world * K / sec / 1e9 / peak, "peak_kind": peak_kind},
+            "token_checksum": int(toks.sum() % 1000003)}), flush=True)
+    del model
+    if group is not None:
+        group.close()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -336,6 +430,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "gemv"],
                     help="profiling aid: run only the device-resident decode section or only the GEMV section")
+    ap.add_argument("--workload", default="decode_2b", choices=["decode_2b", "xl_tp"],
+                    help="decode_2b: the headline line; xl_tp: the tensor-parallel XL shape (separate line)")
+    ap.add_argument("--layers", type=int, default=0, help="xl_tp: override the layer count (0 = 80)")
+    ap.add_argument("--graph", type=int, default=1, help="xl_tp: replay the step as a CUDA graph (1) or launch it (0)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -349,6 +447,8 @@ def main():
         return
     if args.impl == "reference":
         run_reference(args, rank)
+    elif args.workload == "xl_tp":
+        run_xl_tp(args, rank, world)
     else:
         run_b200(args, rank, world)
 

@@ -619,22 +619,12 @@ static int acc1(Ctx& c, const void* tiles, size_t out, size_t in, int ncols, int
     return rotor_b200_bitlinear_acc(tiles, out, in, c.xq, c.xsum[xs], (size_t)ncols, acc, c.variant, st);
 }
 
-static int run_layers_tp(Model& m, const long long* ids, int batch, int seq, int logits_mode, float* logits,
-                         long long* next_ids, cudaStream_t st, bool advance) {
+static int run_blocks_tp(Model& m, int l0, int l1, const float* next_norm, bool to_float, int batch, int seq,
+                         cudaStream_t st) {
     Ctx& c = m.c;
     const int rows = batch * seq, d = c.d, cols = rows;  // one activation term
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
-    VecStageParams e = {};
-    e.mode = VS_EMBED;
-    e.n = d;
-    e.ids = ids;
-    e.embed = m.embed;
-    e.h = c.h;
-    e.norm1 = m.layers[0].input_norm;
-    e.eps = c.eps;
-    quant_sink(c, e, 0, d);
-    RB_TRY(launch_vec_stage(e, rows, st));
-    for (int l = 0; l < m.cfg.n_layers; ++l) {
+    for (int l = l0; l < l1; ++l) {
         const rotor_b200_layer_weights& L = m.layers[l];
         AccView va, vb;
         // ---- attention on this rank's heads
@@ -774,14 +764,32 @@ static int run_layers_tp(Model& m, const long long* ids, int batch, int seq, int
         dn.wscale0 = L.down_scale;
         dn.h = c.h;
         dn.eps = c.eps;
-        const bool last = l + 1 == m.cfg.n_layers;
-        dn.norm1 = last ? m.final_norm : m.layers[l + 1].input_norm;
-        if (last)
+        const bool last = l + 1 == l1;
+        dn.norm1 = last ? next_norm : m.layers[l + 1].input_norm;
+        if (last && to_float)
             dn.y_out = c.hn;
         else
             quant_sink(c, dn, 0, d);
         RB_TRY(launch_vec_stage(dn, rows, st));
     }
+    return ROTOR_B200_OK;
+}
+
+static int run_layers_tp(Model& m, const long long* ids, int batch, int seq, int logits_mode, float* logits,
+                         long long* next_ids, cudaStream_t st, bool advance) {
+    Ctx& c = m.c;
+    const int rows = batch * seq, d = c.d;
+    VecStageParams e = {};
+    e.mode = VS_EMBED;
+    e.n = d;
+    e.ids = ids;
+    e.embed = m.embed;
+    e.h = c.h;
+    e.norm1 = m.layers[0].input_norm;
+    e.eps = c.eps;
+    quant_sink(c, e, 0, d);
+    RB_TRY(launch_vec_stage(e, rows, st));
+    RB_TRY(run_blocks_tp(m, 0, m.cfg.n_layers, m.final_norm, true, batch, seq, st));
     if (logits_mode == ROTOR_B200_LOGITS_NONE && !next_ids) return ROTOR_B200_OK;
 
     // ---- LM head over this rank's vocabulary slice; logits (if asked for) are the local slice
@@ -1090,7 +1098,12 @@ int rotor_b200_model_forward_hidden(void* handle, const float* hidden_in, int ba
     quant_sink(c, e, 0, c.d);
     RB_TRY(launch_vec_stage(e, rows, st));
     const float* next_norm = layer_end < m->cfg.n_layers ? m->layers[layer_end].input_norm : m->final_norm;
-    RB_TRY(run_blocks(c, m->layers, layer_begin, layer_end, next_norm, true, batch, seq, st));
+    if (c.tp_size > 1) {
+        RB_REQUIRE(c.tp);
+        RB_TRY(run_blocks_tp(*m, layer_begin, layer_end, next_norm, true, batch, seq, st));
+    } else {
+        RB_TRY(run_blocks(c, m->layers, layer_begin, layer_end, next_norm, true, batch, seq, st));
+    }
     RB_CUDA(cudaMemcpyAsync(hidden_out, apply_final_norm ? c.hn : c.h, (size_t)rows * c.d * sizeof(float),
                             cudaMemcpyDeviceToDevice, st));
     m->pos = past_len + seq;

@@ -1,12 +1,24 @@
-// Tensor-parallel plumbing: one process per GPU, NCCL over NVLink for the exchange steps
-// of column/row-parallel BitLinear (new design: the reference has no multi-device code).
+// Tensor-parallel plumbing: one process per GPU, exchange steps of column/row-parallel
+// BitLinear over NVLink (new design: the reference has no multi-device code).
 //
-// NCCL is bound at run time (dlopen of libnccl.so.2) so that the library has no link-time
-// dependency on a particular NCCL build and shares the copy the host process already
-// loaded.  Collectives are enqueued on the caller's stream between this library's kernels.
+// Two transports:
+//  * One-shot all-reduce over peer memory (default for the payloads of generation steps, up
+//    to XCH_CAP 32-bit elements).  Every rank owns an exchange buffer that its peers map
+//    with CUDA IPC.  A rank pushes each element to every peer as one 64-bit store
+//    {value, generation}; the same thread then polls its own buffer until the word of every
+//    source carries the current generation and reduces in rank order (so all ranks hold
+//    identical bits).  One NVLink crossing, no fence, no second kernel.  Two slots alternate
+//    with the generation; a slot is rewritten two collectives later, which a peer can only
+//    reach after this rank has finished reading it.  Polls are bounded by a cycle count and
+//    report through the library status word.
+//  * NCCL for everything else (large prefill payloads, the pick all-gather, set-up).  NCCL is
+//    bound at run time (dlopen of libnccl.so.2) so that the library has no link-time
+//    dependency on a particular NCCL build and shares the copy the host process loaded.
+// Collectives are enqueued on the caller's stream between this library's kernels.
 #include <dlfcn.h>
 #include <nccl.h>  // types and enums only; every function is resolved with dlsym
 
+#include <cstdlib>
 #include <cstring>
 
 #include "model.cuh"
@@ -40,21 +52,159 @@ static int load_nccl() {
     return ROTOR_B200_OK;
 }
 
+constexpr int XCH_MAX_RANKS = 8;
+constexpr int XCH_CAP = 1 << 16;  // 32-bit elements per one-shot collective
+constexpr long long XCH_SPIN_CYCLES = 2000000000LL;  // about one second
+
+// Device view of the exchange: rank r's buffer is uint2 [2 slots][size][XCH_CAP].
+struct XchDev {
+    uint2* buf[XCH_MAX_RANKS];  // this process's mapping of every rank's buffer (own included)
+    unsigned* seq;              // collectives completed so far (device memory: graph replays advance it)
+    unsigned* done;             // CTAs of the running collective that have finished
+    unsigned* status;           // library status word
+    int rank, size;
+};
+
 struct TpComm {
     ncclComm_t comm;
     int rank, size;
+    bool oneshot;               // peer-memory exchange is set up
+    XchDev x;
+    void* own;                  // this rank's exchange buffer (cudaMalloc)
+    void* peer[XCH_MAX_RANKS];  // IPC mappings to close
+    unsigned* ctr;              // seq, done
 };
+
+__device__ __forceinline__ void st_pair(uint2* p, unsigned v, unsigned g) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v), "r"(g) : "memory");
+}
+__device__ __forceinline__ uint2 ld_pair(const uint2* p) {
+    uint2 r;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+    return r;
+}
+
+enum { XOP_SUM_I32 = 0, XOP_SUM_F32 = 1, XOP_MAX_F32 = 2 };
+
+template <int OP>
+__device__ __forceinline__ unsigned xch_reduce(unsigned a, unsigned b) {
+    if (OP == XOP_SUM_I32) return (unsigned)((int)a + (int)b);
+    if (OP == XOP_SUM_F32) return __float_as_uint(__fadd_rn(__uint_as_float(a), __uint_as_float(b)));
+    return __float_as_uint(fmaxf(__uint_as_float(a), __uint_as_float(b)));
+}
+
+template <int OP>
+__global__ void __launch_bounds__(256) oneshot_allreduce_kernel(const __grid_constant__ XchDev t,
+                                                                const unsigned* in, unsigned* out, int n) {
+    const unsigned seq = *reinterpret_cast<volatile unsigned*>(t.seq);
+    const unsigned gen = seq + 1u;  // never matches what a slot held two collectives ago, nor the zero fill
+    const size_t slot = (size_t)(gen & 1u) * t.size;
+    // a wait that ran out earlier (status word set) is not repeated: later collectives finish at once
+    bool failed = *reinterpret_cast<volatile unsigned*>(t.status) != 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const unsigned v = in[i];
+        for (int p = 0; p < t.size; ++p)
+            if (p != t.rank) st_pair(t.buf[p] + (slot + t.rank) * XCH_CAP + i, v, gen);
+        unsigned acc = 0;
+        for (int src = 0; src < t.size; ++src) {
+            unsigned x = v;
+            if (src != t.rank) {
+                const uint2* w = t.buf[t.rank] + (slot + src) * XCH_CAP + i;
+                uint2 got = ld_pair(w);
+                if (got.y != gen && !failed) {
+                    const long long t0 = clock64();
+                    while ((got = ld_pair(w)).y != gen) {
+                        if (clock64() - t0 > XCH_SPIN_CYCLES) {
+                            failed = true;
+                            atomicExch(t.status, 0x7e000000u | (unsigned)src);
+                            break;
+                        }
+                    }
+                }
+                x = got.x;
+            }
+            acc = src == 0 ? x : xch_reduce<OP>(acc, x);
+        }
+        out[i] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(t.done, 1u) == gridDim.x - 1) {  // every CTA has read seq by now
+            *t.done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned*>(t.seq) = seq + 1u;
+        }
+    }
+}
+
+template <int OP>
+static int launch_oneshot(TpComm* t, const void* in, void* out, size_t n, cudaStream_t st) {
+    int grid = (int)((n + 255) / 256);
+    if (grid > 64) grid = 64;
+    oneshot_allreduce_kernel<OP><<<grid, 256, 0, st>>>(t->x, (const unsigned*)in, (unsigned*)out, (int)n);
+    return launch_status();
+}
+
+// Peer-memory set-up: allocate and zero the exchange buffer, swap IPC handles through the
+// NCCL communicator, map every peer.  Failure leaves the communicator on NCCL alone.
+static int setup_oneshot(TpComm* t) {
+    if (t->size > XCH_MAX_RANKS || t->size < 2) return ROTOR_B200_ERR_ARG;
+    const size_t bytes = 2 * (size_t)t->size * XCH_CAP * sizeof(uint2);
+    unsigned char* scratch = nullptr;
+    RB_CUDA(cudaMalloc(&t->own, bytes));
+    RB_CUDA(cudaMalloc(&t->ctr, 2 * sizeof(unsigned)));
+    RB_CUDA(cudaMalloc(&scratch, (size_t)(t->size + 1) * sizeof(cudaIpcMemHandle_t)));
+    RB_CUDA(cudaMemset(t->own, 0, bytes));
+    RB_CUDA(cudaMemset(t->ctr, 0, 2 * sizeof(unsigned)));
+    cudaIpcMemHandle_t mine, all[XCH_MAX_RANKS];
+    RB_CUDA(cudaIpcGetMemHandle(&mine, t->own));
+    RB_CUDA(cudaMemcpy(scratch, &mine, sizeof(mine), cudaMemcpyHostToDevice));
+    RB_CUDA(cudaDeviceSynchronize());  // the zero fill is done before any peer can learn the handle
+    if (g_nccl.AllGather(scratch, scratch + sizeof(mine), sizeof(mine), ncclInt8, t->comm, nullptr) != ncclSuccess)
+        return ROTOR_B200_ERR_CUDA;
+    RB_CUDA(cudaDeviceSynchronize());
+    RB_CUDA(cudaMemcpy(all, scratch + sizeof(mine), (size_t)t->size * sizeof(mine), cudaMemcpyDeviceToHost));
+    cudaFree(scratch);
+    for (int p = 0; p < t->size; ++p) {
+        if (p == t->rank) {
+            t->x.buf[p] = (uint2*)t->own;
+            continue;
+        }
+        RB_CUDA(cudaIpcOpenMemHandle(&t->peer[p], all[p], cudaIpcMemLazyEnablePeerAccess));
+        t->x.buf[p] = (uint2*)t->peer[p];
+    }
+    t->x.seq = t->ctr;
+    t->x.done = t->ctr + 1;
+    t->x.status = library_status_word();
+    t->x.rank = t->rank;
+    t->x.size = t->size;
+    if (!t->x.status) return ROTOR_B200_ERR_CUDA;
+    t->oneshot = true;
+    return ROTOR_B200_OK;
+}
+
+static void teardown_oneshot(TpComm* t) {
+    cudaDeviceSynchronize();  // everything pushed to this rank belongs to collectives it has finished
+    for (int p = 0; p < XCH_MAX_RANKS; ++p)
+        if (t->peer[p]) cudaIpcCloseMemHandle(t->peer[p]);
+    if (t->own) cudaFree(t->own);
+    if (t->ctr) cudaFree(t->ctr);
+}
 
 int tp_rank(void* c) { return c ? static_cast<TpComm*>(c)->rank : 0; }
 int tp_size(void* c) { return c ? static_cast<TpComm*>(c)->size : 1; }
 
 int tp_allreduce_sum_i32(void* c, int32_t* buf, size_t n, cudaStream_t st) {
     TpComm* t = static_cast<TpComm*>(c);
+    if (t->oneshot && n <= (size_t)XCH_CAP) return launch_oneshot<XOP_SUM_I32>(t, buf, buf, n, st);
     return g_nccl.AllReduce(buf, buf, n, ncclInt32, ncclSum, t->comm, st) == ncclSuccess ? ROTOR_B200_OK
                                                                                            : ROTOR_B200_ERR_CUDA;
 }
 int tp_allreduce_f32(void* c, float* buf, size_t n, bool max_op, cudaStream_t st) {
     TpComm* t = static_cast<TpComm*>(c);
+    if (t->oneshot && n <= (size_t)XCH_CAP)
+        return max_op ? launch_oneshot<XOP_MAX_F32>(t, buf, buf, n, st) : launch_oneshot<XOP_SUM_F32>(t, buf, buf, n, st);
     return g_nccl.AllReduce(buf, buf, n, ncclFloat32, max_op ? ncclMax : ncclSum, t->comm, st) == ncclSuccess
                ? ROTOR_B200_OK
                : ROTOR_B200_ERR_CUDA;
@@ -88,12 +238,23 @@ int rotor_b200_tp_init(int rank, int size, const void* unique_id128, void** comm
     if (rc) return rc;
     ncclUniqueId id;
     memcpy(&id, unique_id128, sizeof(id));
-    TpComm* t = new TpComm;
+    TpComm* t = new TpComm();
     t->rank = rank;
     t->size = size;
     if (g_nccl.CommInitRank(&t->comm, size, id, rank) != ncclSuccess) {
         delete t;
         return ROTOR_B200_ERR_CUDA;
+    }
+    // ROTOR_B200_TP_NCCL=1 keeps every collective on NCCL (the comparison baseline)
+    const char* only_nccl = getenv("ROTOR_B200_TP_NCCL");
+    if (size > 1 && !(only_nccl && only_nccl[0] == '1')) {
+        rc = setup_oneshot(t);
+        if (rc) {  // all ranks must agree on the transport: a rank that cannot map its peers fails the init
+            teardown_oneshot(t);
+            g_nccl.CommDestroy(t->comm);
+            delete t;
+            return rc;
+        }
     }
     *comm = t;
     return ROTOR_B200_OK;
@@ -102,6 +263,7 @@ int rotor_b200_tp_init(int rank, int size, const void* unique_id128, void** comm
 void rotor_b200_tp_destroy(void* comm) {
     TpComm* t = static_cast<TpComm*>(comm);
     if (!t) return;
+    teardown_oneshot(t);
     if (g_nccl.CommDestroy) g_nccl.CommDestroy(t->comm);
     delete t;
 }

@@ -262,6 +262,22 @@ class ShardedBitNetModel:
         abi.device_status()
         return out.cpu().numpy()
 
+    def forward_hidden(self, hidden, past: int = 0, layer_begin: int = 0, layer_end: Optional[int] = None,
+                       final_norm: bool = False):
+        """Blocks [layer_begin, layer_end) applied to replicated hidden rows [batch, seq, d_model];
+        returns the (replicated) residual stream, or its normed form.  Collective."""
+        torch = abi.require_cuda()
+        x = np.asarray(hidden, dtype=np.float32)
+        batch, seq, d = x.shape
+        h = self._ensure_handle(batch, seq, past + seq)
+        xd = ops.to_device(x.reshape(batch * seq, d), torch.float32)
+        y = torch.empty_like(xd)
+        check(lib.rotor_b200_model_forward_hidden(h, ptr(xd), batch, seq, past, layer_begin,
+                                                  self.n_layers if layer_end is None else layer_end,
+                                                  int(final_norm), ptr(y), abi.stream()), "model_forward_hidden")
+        abi.device_status()
+        return y.cpu().numpy().reshape(batch, seq, d)
+
     def generate_greedy(self, prompt_ids, max_new_tokens: int, use_graph: bool = False):
         """Device-resident greedy generation; returns the new global token ids (the same list
         on every rank).  Collective."""
