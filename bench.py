@@ -331,6 +331,62 @@ def run_b200(args, rank, world):
         dist.destroy_process_group()
 
 
+def run_prefill(args, rank, world):
+    """Prompt prefill of the 2B shape: batch 8 x 2048 positions through the whole model
+    (tiled tensor-core BitLinear products, tiled attention, LM head on the last position)."""
+    import numpy as np
+    import torch
+    from rotor_b200 import abi, semantics
+    from rotor_b200.synth import random_model_on_device
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    B, S = args.batch or 8, args.seq or 2048
+    cfg = dict(CFG_2B)
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    model = random_model_on_device(cfg, seed=77, semantics=semantics.BASELINE, max_seq=S, max_batch=B,
+                                   max_rows=B * S)
+    h = model._ensure_handle(B, S, S).h
+    ids = torch.from_numpy(np.random.default_rng(5).integers(0, cfg["vocab_size"], size=(B, S))).cuda()
+    nxt = torch.empty(B, dtype=torch.int64, device="cuda")
+    st = torch.cuda.Stream()
+    K, W = args.steps, max(args.warmup, 1)
+    with torch.cuda.stream(st):
+        s = st.cuda_stream
+        run = lambda: abi.check(abi.lib.rotor_b200_model_forward(h, ids.data_ptr(), B, S, 0, abi.LOGITS_NONE, None,
+                                                                 nxt.data_ptr(), s), "prefill")
+        for _ in range(W):
+            run()
+        st.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        time.sleep(0.25)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = abi.lib.rotor_b200_launch_count()
+        t0 = time.time()
+        e0.record(st)
+        for _ in range(K):
+            run()
+        e1.record(st)
+        st.synchronize()
+        t1 = time.time()
+        clocks = sampler.stop(t0, t1)
+        launches = abi.lib.rotor_b200_launch_count() - before
+    abi.device_status()
+    sec = e0.elapsed_time(e1) * 1e-3 / K
+    d, ff, L = cfg["d_model"], cfg["d_ff"], cfg["n_layers"]
+    hd = d // cfg["n_heads"]
+    macs = (cfg["n_heads"] * hd + 2 * cfg["n_kv_heads"] * hd) * d + d * cfg["n_heads"] * hd + 3 * ff * d
+    int8_ops = 2.0 * B * S * macs * L
+    attn_flops = 4.0 * B * cfg["n_heads"] * S * S * hd * L / 2   # causal: half of the score matrix
+    print(json.dumps({
+        "metric": "2B-shape prompt prefill tokens/s", "value": B * S / sec, "unit": UNIT, "n_gpus": 1, "steps": K,
+        "warmup": W, "ms_per_step": sec * 1e3, "higher_is_better": True, "data": "synthetic",
+        "config": {"workload": f"{L}-layer 2B-shape model, batch {B} x {S} positions, causal, last-position pick"},
+        "bitlinear_int8_ops": int8_ops, "attention_flops": attn_flops,
+        "if_all_time_were_bitlinear_TOPS": int8_ops / sec / 1e12,
+        "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+
+
 def run_xl_tp(args, rank, world):
     """Batch-1 greedy decode of the XL shape, sharded over `world` GPUs (1 = unsharded)."""
     import numpy as np
@@ -430,8 +486,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "gemv"],
                     help="profiling aid: run only the device-resident decode section or only the GEMV section")
-    ap.add_argument("--workload", default="decode_2b", choices=["decode_2b", "xl_tp"],
+    ap.add_argument("--workload", default="decode_2b", choices=["decode_2b", "xl_tp", "prefill_2b"],
                     help="decode_2b: the headline line; xl_tp: the tensor-parallel XL shape (separate line)")
+    ap.add_argument("--batch", type=int, default=0, help="prefill_2b: sequences (0 = 8)")
+    ap.add_argument("--seq", type=int, default=0, help="prefill_2b: positions per sequence (0 = 2048)")
     ap.add_argument("--layers", type=int, default=0, help="xl_tp: override the layer count (0 = 80)")
     ap.add_argument("--graph", type=int, default=1, help="xl_tp: replay the step as a CUDA graph (1) or launch it (0)")
     args = ap.parse_args()
@@ -449,6 +507,9 @@ def main():
         run_reference(args, rank)
     elif args.workload == "xl_tp":
         run_xl_tp(args, rank, world)
+    elif args.workload == "prefill_2b":
+        if rank == 0:
+            run_prefill(args, rank, world)
     else:
         run_b200(args, rank, world)
 

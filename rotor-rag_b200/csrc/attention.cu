@@ -157,6 +157,7 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnParams p) {
 }
 
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st) {
+    if (attn_prefill_supported(p)) return launch_attn_prefill(p, rows, st);
     dim3 grid(p.n_heads, rows);
     switch (p.head_dim) {
         case 32: attention_kernel<1><<<grid, 128, 0, st>>>(p); break;
@@ -307,7 +308,7 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    return ROTOR_B200_OK;
+    return configure_attn_prefill();
 }
 
 }  // namespace rb

@@ -1,0 +1,316 @@
+// Ternary BitLinear integer core for prompt prefill on the fifth-generation tensor cores:
+// acc[c][o] = sum_k xq[c][k] * w[o][k], exact int32, for hundreds to thousands of
+// activation columns c (tokens).
+//
+// CTA tile: 256 tokens x 256 weight rows, K walked 128 at a time through a 3-stage ring of
+// shared-memory operand tiles.  tcgen05.mma.kind::i8 (M = 128 tokens, N = 256 weight rows,
+// K = 32 per instruction) accumulates into tensor memory: two 128-lane x 256-column int32
+// accumulators, all 512 TMEM columns of the SM.  Per stage:
+//   * the token operand (2 x 128 rows of 128 int8) arrives by TMA
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past the last token zero filled),
+//   * four decoder warps turn 16 packed weight tiles (2 bits per weight, 8 KB) into 32 KB of
+//     signed int8 in the same swizzled K-major layout: a lane's 128-bit tile word holds, per
+//     row, 32 consecutive K positions, i.e. two 16-byte chunks of the operand row,
+//   * one thread issues the eight MMAs and commits them to the stage's "empty" barrier.
+// The weights are signed int8 (-1, 0, +1) in shared memory, so no code-offset correction is
+// needed.  After the last stage the decoder warps read the accumulators back
+// (tcgen05.ld 32 lanes x 32 columns) and store acc[token][row], 128 contiguous bytes per
+// thread.  Every wait is bounded by a cycle count; a wait that runs out records a code in
+// the library status word, the CTA stops issuing work, lets its copies land, frees its
+// tensor memory and returns.
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "gemv_core.cuh"
+#include "model.cuh"
+
+namespace rb {
+
+constexpr int T5_TOK = 256;                        // tokens per CTA (two MMA M halves)
+constexpr int T5_ROWS = 256;                       // weight rows per CTA (MMA N)
+constexpr int T5_STAGES = 3;
+constexpr int T5_A_BYTES = T5_TOK * TILE_K;        // token operand per stage
+constexpr int T5_B_BYTES = T5_ROWS * TILE_K;       // weight operand per stage
+constexpr int T5_STAGE_BYTES = T5_A_BYTES + T5_B_BYTES;
+constexpr int T5_THREADS = 192;                    // warps 0-3 decode + epilogue, 4 TMA + TMEM, 5 MMA
+constexpr int T5_SMEM = T5_STAGES * T5_STAGE_BYTES + 1024;  // + slack to align the ring to 1024 bytes
+constexpr long long T5_SPIN_CYCLES = 400000000LL;  // about 0.2 s
+
+struct Tc5Params {
+    const uint4* tiles;
+    int32_t* acc;       // [ncols][out]
+    unsigned* status;
+    int out, nrt, nkt, ncols;
+};
+
+__device__ __forceinline__ bool t5_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned* status,
+                                        unsigned code) {
+    long long t0 = 0;
+    for (int it = 0;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if (it == 0) t0 = clock64();
+        if (clock64() - t0 > T5_SPIN_CYCLES) {
+            *abort_flag = 1;
+            atomicExch(status, code);
+            return false;
+        }
+    }
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t t5_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+
+// codes {0,1,2} in four bytes -> signed bytes {-1,0,+1}
+__device__ __forceinline__ uint32_t t5_s8(uint32_t codes) { return (codes + 0x7f7f7f7fu) ^ 0x80808080u; }
+
+__global__ void __launch_bounds__(T5_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Tc5Params p) {
+    extern __shared__ unsigned char t5_raw[];
+    __shared__ __align__(8) unsigned long long s_full[T5_STAGES], s_empty[T5_STAGES], s_accf;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const uint32_t ring = (smem_u32(t5_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok0 = blockIdx.x * T5_TOK, rt0 = blockIdx.y * (T5_ROWS / TILE_ROWS);
+    volatile int* abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < T5_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_full[s])), "r"(128 + 1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_empty[s])), "r"(1));
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_accf)), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {  // the whole warp allocates all 512 tensor-memory columns (one CTA per SM)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)),
+                     "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp < 4) {
+        // ---------------- weight decoders: warp w owns row tiles 4w .. 4w+3 of the CTA's 16
+        const int g = lane >> 2, t = lane & 3;
+        uint4 wv[4];
+        auto fetch = [&](int kt) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int rt = rt0 + warp * 4 + u;
+                wv[u] = rt < p.nrt ? ld_stream_v4(p.tiles + ((size_t)rt * p.nkt + kt) * 32 + lane)
+                                   : make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+            }
+        };
+        fetch(0);
+        for (int kt = 0; kt < p.nkt; ++kt) {
+            const int s = kt % T5_STAGES;
+            if (!t5_wait(smem_u32(&s_empty[s]), ((kt / T5_STAGES) & 1) ^ 1, abort_flag, p.status, 0x7c000001u)) break;
+            const uint32_t bbase = ring + s * T5_STAGE_BYTES + T5_A_BYTES;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+#pragma unroll
+                for (int rh = 0; rh < 2; ++rh) {
+                    // operand row R = 16 (4 warp + u) + g + 8 rh; R % 8 == g; K bytes [32 t, 32 t + 32)
+                    const uint32_t row = bbase + (uint32_t)((warp * 4 + u) * 2 + rh) * 1024u + (uint32_t)g * 128u;
+                    const uint32_t lo = pw[rh], hi = pw[rh + 2];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {  // 16-byte chunk 2 t + c holds bit pairs 2 c and 2 c + 1
+                        const uint32_t a0 = t5_s8((lo >> (4 * c)) & 0x03030303u);
+                        const uint32_t a1 = t5_s8((hi >> (4 * c)) & 0x03030303u);
+                        const uint32_t a2 = t5_s8((lo >> (4 * c + 2)) & 0x03030303u);
+                        const uint32_t a3 = t5_s8((hi >> (4 * c + 2)) & 0x03030303u);
+                        const uint32_t dst = row + (uint32_t)(((2 * t + c) ^ g) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(a0), "r"(a1), "r"(a2),
+                                     "r"(a3)
+                                     : "memory");
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s_full[s])) : "memory");
+            if (kt + 1 < p.nkt) fetch(kt + 1);
+        }
+        // ---------------- epilogue: lane = token, 32 columns (weight rows) per load
+        // (warp-uniform decision: the tensor-memory loads below are warp-wide instructions)
+        const bool acc_ok = !*abort_flag && t5_wait(smem_u32(&s_accf), 0, abort_flag, p.status, 0x7c000002u);
+        if (__all_sync(0xffffffffu, acc_ok)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row0 = rt0 * TILE_ROWS;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                const int token = tok0 + half * 128 + warp * 32 + lane;
+#pragma unroll 1
+                for (int ch = 0; ch < T5_ROWS / 32; ++ch) {
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(half * 256 + ch * 32);
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+                          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int rbase = row0 + ch * 32;
+                    if (token < p.ncols && rbase < p.out) {
+                        int32_t* dst = p.acc + (size_t)token * p.out + rbase;
+                        if (rbase + 32 <= p.out && (p.out & 3) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                *reinterpret_cast<uint4*>(dst + 4 * q) =
+                                    make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 32; ++q)
+                                if (rbase + q < p.out) dst[q] = (int32_t)v[q];
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ---------------- token operand by TMA
+        if (lane == 0) {
+            for (int kt = 0; kt < p.nkt; ++kt) {
+                const int s = kt % T5_STAGES;
+                if (!t5_wait(smem_u32(&s_empty[s]), ((kt / T5_STAGES) & 1) ^ 1, abort_flag, p.status, 0x7c000003u)) break;
+                const uint32_t bar = smem_u32(&s_full[s]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(T5_A_BYTES)
+                             : "memory");
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t dst = ring + s * T5_STAGE_BYTES + half * (T5_A_BYTES / 2);
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                        "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                        "l"(&tmap), "r"(kt * TILE_K), "r"(tok0 + half * 128), "r"(bar)
+                        : "memory");
+                }
+            }
+        }
+    } else {
+        // ---------------- MMA issue
+        if (lane == 0) {
+            // kind::i8, S32 accumulate, signed x signed, both operands K-major, N = 256, M = 128
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(T5_ROWS >> 3) << 17) | ((128u >> 4) << 24);
+            bool ok = true;
+            for (int kt = 0; kt < p.nkt && ok; ++kt) {
+                const int s = kt % T5_STAGES;
+                ok = t5_wait(smem_u32(&s_full[s]), (kt / T5_STAGES) & 1, abort_flag, p.status, 0x7c000004u);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t abase = ring + s * T5_STAGE_BYTES, bbase = abase + T5_A_BYTES;
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+#pragma unroll
+                    for (int k4 = 0; k4 < TILE_K / 32; ++k4) {
+                        const uint64_t da = t5_desc(abase + half * (T5_A_BYTES / 2) + k4 * 32);
+                        const uint64_t db = t5_desc(bbase + k4 * 32);
+                        const uint32_t accumulate = (kt > 0 || k4 > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t"
+                            ".reg .pred p;\n\t"
+                            "setp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+                            "}\n" ::"r"(tmem + (uint32_t)(half * 256)),
+                            "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+                            : "memory");
+                    }
+                // arrives on the stage's "empty" barrier once these MMAs have read their operands
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                 smem_u32(&s_empty[s]))
+                             : "memory");
+            }
+            if (ok)
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                 smem_u32(&s_accf))
+                             : "memory");
+        }
+    }
+
+    // ---------------- common exit: nothing of this CTA may still be in flight when it returns
+    if (*abort_flag && threadIdx.x == 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {
+        }  // about a millisecond for copies already issued to land
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static bool g_tc5_ready = false;
+
+// Shapes this kernel takes: enough tokens to fill its tile, 16-byte aligned operands.
+bool gemm_tcgen05_supported(size_t out, size_t in, int ncols, const void* xq) {
+    static const bool off = getenv("ROTOR_B200_NO_TCGEN05") != nullptr;  // measurement aid: legacy mma.sync path
+    return !off && ncols >= T5_TOK && out >= 16 && in >= 4 && ((uintptr_t)xq & 15) == 0;
+}
+
+int configure_gemm_tcgen05() {
+    if (g_tc5_ready) return ROTOR_B200_OK;
+    cudaDriverEntryPointQueryResult q;
+    void* fn = nullptr;
+    RB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (!fn || q != cudaDriverEntryPointSuccess) return ROTOR_B200_ERR_CUDA;
+    g_encode = (EncodeTiledFn)fn;
+    RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T5_SMEM));
+    g_tc5_ready = true;
+    return ROTOR_B200_OK;
+}
+
+int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* xq, int ncols, int32_t* acc,
+                        cudaStream_t st) {
+    int rc = configure_gemm_tcgen05();
+    if (rc) return rc;
+    Tc5Params p;
+    p.tiles = (const uint4*)tiles;
+    p.acc = acc;
+    p.status = library_status_word();
+    p.out = (int)out;
+    p.nrt = (int)(opad_of(out) / TILE_ROWS);
+    p.nkt = (int)(kpad_of(in) / TILE_K);
+    p.ncols = ncols;
+    if (!p.status) return ROTOR_B200_ERR_CUDA;
+    const size_t kpad = kpad_of(in);
+    CUtensorMap tmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t)kpad, (cuuint64_t)ncols};
+    const cuuint64_t gstride[1] = {(cuuint64_t)kpad};  // bytes between token rows
+    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, 128u};
+    const cuuint32_t estride[2] = {1u, 1u};
+    if (g_encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)xq, gdim, gstride, box, estride,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return ROTOR_B200_ERR_CUDA;
+    dim3 grid((ncols + T5_TOK - 1) / T5_TOK, (p.nrt * TILE_ROWS + T5_ROWS - 1) / T5_ROWS);
+    gemm_tcgen05_kernel<<<grid, T5_THREADS, T5_SMEM, st>>>(tmap, p);
+    return launch_status();
+}
+
+}  // namespace rb

@@ -71,6 +71,10 @@ int gemv_cols_per_launch(int variant, int ncols);
 
 // Many-column product (gemm_mma.cu): complete int32 sums into acc[ncols][out].
 constexpr int GEMM_MIN_COLS = 32;
+bool gemm_tcgen05_supported(size_t out, size_t in, int ncols, const void* xq);
+int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* xq, int ncols, int32_t* acc,
+                        cudaStream_t st);
+int configure_gemm_tcgen05();
 int launch_gemm_mma(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
                     int32_t* acc, cudaStream_t st);
 
@@ -140,6 +144,9 @@ struct AttnParams {
     int causal;
 };
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st);
+bool attn_prefill_supported(const AttnParams& p);
+int launch_attn_prefill(const AttnParams& p, int rows, cudaStream_t st);
+int configure_attn_prefill();
 
 struct LmHeadParams {
     const __nv_bfloat16* embed;  // [vocab][d]

@@ -76,9 +76,13 @@ def test_integer_accumulators_bit_exact(ops, abi, variant, shape):
     abi.device_status()
 
 
-@pytest.mark.parametrize("shape", [(6912, 2560, 130), (2560, 6912, 257), (48, 1280, 32), (33, 260, 300), (640, 2560, 1024)])
+@pytest.mark.parametrize("shape", [(6912, 2560, 130), (2560, 6912, 257), (48, 1280, 32), (33, 260, 300), (640, 2560, 1024),
+                                   (400, 2560, 517), (3840, 384, 256), (272, 128, 700)])
 def test_many_column_product_bit_exact(ops, abi, shape):
-    """Prefill-sized products (>= 32 activation columns) take the tiled tensor-core GEMM."""
+    """Prefill-sized products: 32 to 255 activation columns take the mma.sync tiled GEMM, 256 and
+    more the tcgen05 kernel (TMA-fed token operand, weights decoded into shared memory, int32
+    accumulators in tensor memory).  Ragged token counts, row counts that do not fill the
+    256-row tile, and K that is not a multiple of the 128-wide weight tile."""
     out, inn, ncols = shape
     rng = np.random.default_rng(out * 3 + inn + ncols)
     w = O.synth_ternary(rng, out, inn)
@@ -94,6 +98,20 @@ def test_many_column_product_bit_exact(ops, abi, shape):
     # the column-chunked tensor-core GEMV gives the same integers
     acc2 = ops.bitlinear_acc(tiles, out, inn, xq, xsum, abi.VARIANT_MMA).cpu().numpy()
     assert np.array_equal(acc2, want)
+
+
+def test_tcgen05_extreme_values(ops, abi):
+    """-128 x -1 and 127 x +1 over K = 6912 on the tcgen05 path: sums stay exact in int32."""
+    out, inn, ncols = 256, 6912, 256
+    w = np.ones((out, inn), dtype=np.int8)
+    w[::2] = -1
+    tiles = ops.int8_to_tiles(w)
+    q = np.full((ncols, inn), -128, dtype=np.int8)
+    q[1::2] = 127
+    xq, xsum = ops.to_device(q), ops.to_device(q.astype(np.int32).sum(axis=1).astype(np.int32))
+    acc = ops.bitlinear_acc(tiles, out, inn, xq, xsum, abi.VARIANT_AUTO).cpu().numpy()
+    assert np.array_equal(acc, q.astype(np.int32) @ w.astype(np.int32).T)
+    abi.device_status()
 
 
 def test_extreme_values_do_not_overflow(ops, abi):

@@ -91,7 +91,8 @@ def test_ffn_block_config2(rb, golden_dir, mode):
 
 def _tiny(rb, name, sem, **kw):
     om, prompt = G.tiny_model(name)
-    return om, prompt, rb.synth.model_from_oracle_params(om, semantics=sem, max_seq=64, **kw)
+    kw.setdefault("max_seq", 64)
+    return om, prompt, rb.synth.model_from_oracle_params(om, semantics=sem, **kw)
 
 
 @pytest.mark.parametrize("name", list(G.TINY_MODELS))
@@ -280,3 +281,27 @@ def test_prefill_and_stepwise_decode_agree(rb):
     _, cache_r = ref.forward(ids[:, :40], use_cache=True, logits_positions="last")
     step_r, _ = ref.forward(ids[:, 40:], past_kv_cache=cache_r, use_cache=True, logits_positions="last")
     assert rel_err(step_r[0, -1], full_r[0, -1]) < TOL
+
+
+@pytest.mark.parametrize("name", list(G.TINY_MODELS))
+@pytest.mark.parametrize("causal", [False, True])
+def test_tiled_prefill_attention(rb, name, causal):
+    """Prompts of 16 positions and more take the tiled attention kernel: ragged lengths (not a
+    multiple of the 64-key tile or of the query tile), batch 2, then a second chunk attending
+    over the cached keys of the first."""
+    sem = rb.sem.REFERENCE.with_(causal=causal)
+    osem = O.with_semantics(O.REFERENCE, causal=causal)
+    om, prompt, model = _tiny(rb, name, sem, max_seq=256, max_batch=2)
+    cfg, lw = om["cfg"], om["layers"][0]
+    rng = np.random.default_rng(23)
+    att = model.layers[0].attention
+    x = rng.standard_normal((2, 150, cfg["d_model"])).astype(np.float32)
+    mask = O.causal_mask(150, 150) if causal else None
+    want, wc = O.attention(x, lw, cfg, osem, None, True)
+    got, cache = att.forward(x, mask=mask, use_cache=True)
+    assert rel_err(got, want) < TOL
+    x2 = rng.standard_normal((2, 37, cfg["d_model"])).astype(np.float32)
+    mask2 = O.causal_mask(37, 187) if causal else None
+    want2, _ = O.attention(x2, lw, cfg, osem, wc, True)
+    got2, cache2 = att.forward(x2, mask=mask2, kv_cache=cache, use_cache=True)
+    assert rel_err(got2, want2) < TOL and cache2.length == 187
