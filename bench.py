@@ -205,6 +205,33 @@ def gemv_roofline(torch, abi, nmat=64, iters=20, out=6912, inn=2560):
     return alg, sec
 
 
+def gemm_throughput(torch, abi, out=13824, inn=2560, m=16384, iters=5):
+    """Config 4's dominant product: the stacked gate/up BitLinear of the 2B shape as an
+    [m x inn] x [inn x out] ternary x int8 GEMM.  Returns (int8 ops per launch, seconds per launch)."""
+    lib = abi.lib
+    tiles = torch.randint(0, 256, (lib.rotor_b200_tiles_bytes(out, inn),), dtype=torch.uint8, device="cuda") & 0xAA
+    kpad = lib.rotor_b200_in_padded(inn)
+    xq = torch.randint(-127, 128, (m, kpad), dtype=torch.int8, device="cuda")
+    xsum = xq.to(torch.int32).sum(1).to(torch.int32)
+    acc = torch.empty((m, out), dtype=torch.int32, device="cuda")
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        s = st.cuda_stream
+        run = lambda: abi.check(lib.rotor_b200_bitlinear_acc(tiles.data_ptr(), out, inn, xq.data_ptr(), xsum.data_ptr(),
+                                                             m, acc.data_ptr(), abi.VARIANT_AUTO, s), "gemm")
+        for _ in range(3):
+            run()
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(iters):
+            run()
+        e1.record(st)
+        st.synchronize()
+    abi.device_status()
+    return 2.0 * out * inn * m, e0.elapsed_time(e1) * 1e-3 / iters
+
+
 def run_b200(args, rank, world):
     import numpy as np
     import torch
@@ -484,8 +511,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "gemv"],
-                    help="profiling aid: run only the device-resident decode section or only the GEMV section")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "gemv", "gemm"],
+                    help="profiling aid: run only the device-resident decode section, the GEMV section, or one "
+                         "prefill GEMM (--m tokens)")
+    ap.add_argument("--m", type=int, default=16384, help="--only gemm: activation columns (tokens)")
     ap.add_argument("--workload", default="decode_2b", choices=["decode_2b", "xl_tp", "prefill_2b"],
                     help="decode_2b: the headline line; xl_tp: the tensor-parallel XL shape (separate line)")
     ap.add_argument("--batch", type=int, default=0, help="prefill_2b: sequences (0 = 8)")
@@ -502,6 +531,14 @@ def main():
         alg, gsec = gemv_roofline(torch, abi)
         print(json.dumps({"only": "gemv", "bytes_per_launch": alg, "us_per_launch": gsec * 1e6,
                           "gbs": alg / gsec / 1e9}), flush=True)
+        return
+    if args.only == "gemm":
+        import torch
+        from rotor_b200 import abi
+        torch.cuda.set_device(0)
+        ops, sec = gemm_throughput(torch, abi, m=args.m)
+        print(json.dumps({"only": "gemm", "shape": [13824, 2560, args.m], "ms_per_launch": sec * 1e3,
+                          "int8_tops": ops / sec / 1e12}), flush=True)
         return
     if args.impl == "reference":
         run_reference(args, rank)

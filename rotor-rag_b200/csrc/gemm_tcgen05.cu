@@ -107,23 +107,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     if (warp < 4) {
         // ---------------- weight decoders: warp w owns row tiles 4w .. 4w+3 of the CTA's 16
         const int g = lane >> 2, t = lane & 3;
-        uint4 wv[4];
-        auto fetch = [&](int kt) {
+        // weight tiles are requested two K steps ahead of their decode, so that the L2 / HBM latency
+        // hides behind the decode of the step in between and the wait for a free stage
+        uint4 wv[2][4];
+        auto fetch = [&](int kt, uint4 (&dst)[4]) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int rt = rt0 + warp * 4 + u;
-                wv[u] = rt < p.nrt ? ld_stream_v4(p.tiles + ((size_t)rt * p.nkt + kt) * 32 + lane)
-                                   : make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
+                dst[u] = (rt < p.nrt && kt < p.nkt)
+                             ? ld_stream_v4(p.tiles + ((size_t)rt * p.nkt + kt) * 32 + lane)
+                             : make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
             }
         };
-        fetch(0);
-        for (int kt = 0; kt < p.nkt; ++kt) {
+        fetch(0, wv[0]);
+        fetch(1, wv[1]);
+        for (int kt2 = 0; kt2 < p.nkt; kt2 += 2) {
+#pragma unroll
+          for (int par = 0; par < 2; ++par) {
+            const int kt = kt2 + par;
+            if (kt >= p.nkt) break;
             const int s = kt % T5_STAGES;
-            if (!t5_wait(smem_u32(&s_empty[s]), ((kt / T5_STAGES) & 1) ^ 1, abort_flag, p.status, 0x7c000001u)) break;
+            if (!t5_wait(smem_u32(&s_empty[s]), ((kt / T5_STAGES) & 1) ^ 1, abort_flag, p.status, 0x7c000001u)) {
+                kt2 = p.nkt;  // leave both loops
+                break;
+            }
             const uint32_t bbase = ring + s * T5_STAGE_BYTES + T5_A_BYTES;
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+                const uint32_t pw[4] = {wv[par][u].x, wv[par][u].y, wv[par][u].z, wv[par][u].w};
 #pragma unroll
                 for (int rh = 0; rh < 2; ++rh) {
                     // operand row R = 16 (4 warp + u) + g + 8 rh; R % 8 == g; K bytes [32 t, 32 t + 32)
@@ -144,7 +155,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s_full[s])) : "memory");
-            if (kt + 1 < p.nkt) fetch(kt + 1);
+            fetch(kt + 2, wv[par]);
+          }
         }
         // ---------------- epilogue: lane = token, 32 columns (weight rows) per load
         // (warp-uniform decision: the tensor-memory loads below are warp-wide instructions)
