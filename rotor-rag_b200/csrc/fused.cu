@@ -15,8 +15,8 @@ RB_TRACE_DEFINE(rotor_b200_trace_read_fused)
 
 namespace rb {
 
-template <bool USE_MMA, int NCOL>
-__global__ void __launch_bounds__(FG_THREADS, 1) fused_gemv_kernel(const __grid_constant__ FusedGemvParams p) {
+template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP>
+__global__ void __launch_bounds__(DEEP ? FG_THREADS_DEEP : FG_THREADS, 1) fused_gemv_kernel(const __grid_constant__ FusedGemvParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ float s_sx[8];
     __shared__ int s_xsum[8];
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(FG_THREADS, 1) fused_gemv_kernel(const __grid_
     RB_STAMP(tr, 1);
     pdl_wait();  // the weights above are constants; everything below depends on earlier kernels
     RB_STAMP(tr, 2);
-    product_run<USE_MMA, NCOL>(p, c, wv, s_sx, s_xsum);
+    product_run<USE_MMA, NCOL, WIDE, DEEP>(p, c, wv, s_sx, s_xsum);
     RB_STAMP(tr, 5);
     RB_TRACE_COMMIT(tr, p.st.mode * 10 + p.halves);
 }
@@ -45,13 +45,13 @@ static int sm_count() {
     return g_sm_count;
 }
 
-template <bool USE_MMA, int NCOL>
+template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP>
 static int launch_fused(const FusedGemvParams& p, int grid, cudaStream_t st) {
     const size_t smem = fused_smem(p);
     if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(FG_THREADS);
+    cfg.blockDim = dim3(DEEP ? FG_THREADS_DEEP : FG_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -59,7 +59,7 @@ static int launch_fused(const FusedGemvParams& p, int grid, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_use_pdl ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, fused_gemv_kernel<USE_MMA, NCOL>, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, fused_gemv_kernel<USE_MMA, NCOL, WIDE, DEEP>, p) != cudaSuccess) {
         ++g_launch_count;
         return ROTOR_B200_ERR_CUDA;
     }
@@ -67,9 +67,16 @@ static int launch_fused(const FusedGemvParams& p, int grid, cudaStream_t st) {
 }
 
 int configure_fused_gemv() {
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    const int big = 200 * 1024;
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
     sm_count();
     return ROTOR_B200_OK;
 }
@@ -78,8 +85,10 @@ int configure_fused_gemv() {
 // activation terms each.
 bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int halves, int merge_weights) {
     const int cols = rows * terms;
-    if (rows < 1 || cols > 8 || terms > 3 || in % 4 || in > 4 * FG_V * FG_THREADS) return false;
+    if (rows < 1 || cols > 8 || terms > 3 || in % 4) return false;
     FusedGemvParams p = {};
+    p.st.n = (int)in;
+    if (fused_wide(p.st) && merge_weights) return false;
     p.cols = cols;
     p.nkt = (int)(kpad_of(in) / TILE_K);
     p.halves = halves;
@@ -98,9 +107,21 @@ int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int 
     int rc = make_fused_params(p, tiles, out, in, halves, rows, stage, y, scale, seg1, seg2, ffn_act, grid);
     if (rc) return rc;
     if (grid > p.units) grid = p.units;
-    if (p.cols == 1) return launch_fused<false, 1>(p, grid, st);
-    if (p.cols == 2) return launch_fused<false, 2>(p, grid, st);
-    return launch_fused<true, 1>(p, grid, st);
+    // large matrices (eight or more weight tiles per warp) stream: they take the pipelined loop
+    const long tiles_per_warp = (long)p.units * p.halves * p.nkt / ((long)grid * FG_WARPS);
+    if (fused_wide(p.st)) {
+        if (p.cols == 1) return launch_fused<false, 1, true, true>(p, grid, st);
+        if (p.cols == 2) return launch_fused<false, 2, true, true>(p, grid, st);
+        return launch_fused<true, 1, true, true>(p, grid, st);
+    }
+    if (tiles_per_warp >= 8) {
+        if (p.cols == 1) return launch_fused<false, 1, false, true>(p, grid, st);
+        if (p.cols == 2) return launch_fused<false, 2, false, true>(p, grid, st);
+        return launch_fused<true, 1, false, true>(p, grid, st);
+    }
+    if (p.cols == 1) return launch_fused<false, 1, false, false>(p, grid, st);
+    if (p.cols == 2) return launch_fused<false, 2, false, false>(p, grid, st);
+    return launch_fused<true, 1, false, false>(p, grid, st);
 }
 
 int fused_sm_count() { return sm_count(); }

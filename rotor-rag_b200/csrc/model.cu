@@ -11,6 +11,7 @@
 // and a generation step ends with the tied LM head fused with the greedy pick.  A
 // generation step reads the position and the input token from device memory, so one
 // captured CUDA graph replays for every step.
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -430,12 +431,17 @@ static bool fused_step_ok(const Model& m, int batch, int seq) {
     const Ctx& c = m.c;
     static const bool off = getenv("ROTOR_B200_NO_FUSED_STEP") != nullptr;  // measurement aid
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
-    return !off && c.tp_size <= 1 && seq == 1 && batch <= FUSED_MAX_ROWS && batch <= c.max_batch && c.terms <= 3 &&
-           batch * c.terms <= 8 && c.ff % 16 == 0 &&
-           fused_gemv_supported(qkv_out, c.d, batch, c.terms, 1, 0) &&
-           fused_gemv_supported(c.d, c.dq, batch, c.terms, 1, c.n_heads * c.nsplit) &&
-           fused_gemv_supported(c.ff, c.d, batch, c.terms, 2, 0) &&
-           fused_gemv_supported(c.d, c.ff, batch, c.terms, 1, 0);
+    const bool shape_ok = !off && c.tp_size <= 1 && seq == 1 && batch <= FUSED_MAX_ROWS && batch <= c.max_batch &&
+                          c.terms <= 3 && batch * c.terms <= 8 && c.ff % 16 == 0;
+    const bool q = fused_gemv_supported(qkv_out, c.d, batch, c.terms, 1, 0);
+    const bool o = fused_gemv_supported(c.d, c.dq, batch, c.terms, 1, c.n_heads * c.nsplit);
+    const bool g = fused_gemv_supported(c.ff, c.d, batch, c.terms, 2, 0);
+    const bool dn = fused_gemv_supported(c.d, c.ff, batch, c.terms, 1, 0);
+    static const bool verbose = getenv("ROTOR_B200_VERBOSE") != nullptr;
+    if (verbose && seq == 1)
+        fprintf(stderr, "rotor_b200: fused step shape %d qkv %d o %d gate/up %d down %d (batch %d terms %d tp %d)\n",
+                (int)shape_ok, (int)q, (int)o, (int)g, (int)dn, batch, c.terms, c.tp_size);
+    return shape_ok && q && o && g && dn;
 }
 
 // With record == true nothing is launched: the parameter blocks go to m.mega_host / m.mega_lm.

@@ -4,10 +4,12 @@
 #pragma once
 #include "gemv_core.cuh"
 #include "leanstage.cuh"
+#include "vecstage.cuh"
 
 namespace rb {
 
 constexpr int FG_THREADS = 1024;
+constexpr int FG_THREADS_DEEP = 512;  // large matrices: twice the registers per thread for the pipelined tile loop
 constexpr int FG_WARPS = FG_THREADS / 32;
 constexpr int FG_U = 4;  // weight tiles in flight per warp
 constexpr int FG_V = 2;  // float4 groups per thread in the prologue: input width <= 8192
@@ -27,11 +29,17 @@ struct FusedGemvParams {
     int ffn_act;
 };
 
+// Input rows wider than the register-resident prologue holds (4 * FG_V * FG_THREADS elements)
+// are staged as float32 in shared memory instead; only the plain mode (optional norm, then
+// quantise: the down projection's prologue) has such rows.
+__host__ __device__ inline bool fused_wide(const LeanStage& st) { return st.n > 4 * FG_V * FG_THREADS; }
+
 // Shared memory one product needs.
 inline size_t fused_smem(const FusedGemvParams& p) {
     const size_t xs = (size_t)p.cols * (p.nkt * TILE_K + XS_PAD);
     const size_t aux = p.st.mode == LM_ATTN ? 2 * (size_t)p.st.n_heads * p.st.nsplit : 0;
-    return xs + (size_t)p.upc * p.halves * 512 + (64 + aux) * sizeof(float);
+    const size_t wide = fused_wide(p.st) ? (size_t)p.st.n : 0;
+    return xs + (size_t)p.upc * p.halves * 512 + (64 + aux + wide) * sizeof(float);
 }
 
 // Fills the parameter block of one product for a grid of `grid` CTAs.  out: output rows per
@@ -60,7 +68,8 @@ inline int make_fused_params(FusedGemvParams& p, const void* tiles, size_t out, 
     p.ffn_act = ffn_act;
     if (p.cols < 1 || p.cols > 8 || stage.terms > 3 || halves < 1 || halves > 2) return ROTOR_B200_ERR_ARG;
     if (halves == 2 && out % TILE_ROWS) return ROTOR_B200_ERR_SHAPE;
-    if (stage.n != (int)in || in % 4 || in > 4 * FG_V * FG_THREADS) return ROTOR_B200_ERR_SHAPE;
+    if (stage.n != (int)in || in % 4) return ROTOR_B200_ERR_SHAPE;
+    if (fused_wide(stage) && stage.mode != LM_PLAIN) return ROTOR_B200_ERR_SHAPE;
     if (grid > p.units) grid = p.units;
     p.upc = (p.units + grid - 1) / grid;
     return ROTOR_B200_OK;
@@ -84,7 +93,8 @@ __device__ __forceinline__ ProductCtx product_ctx(const FusedGemvParams& p, unsi
     c.xs = reinterpret_cast<int8_t*>(smem_raw);                                      // [cols][xs_stride]
     c.merge = reinterpret_cast<int*>(smem_raw + (size_t)p.cols * c.xs_stride);       // [slots][128]
     c.scratch = reinterpret_cast<float*>(c.merge + c.slots * 128);                   // [64]
-    c.aux = c.scratch + 64;                                                          // attention merge weights
+    c.aux = c.scratch + 64;                                                          // attention merge weights,
+                                                                                     // or the staged wide row
     // units (row tiles / row-tile pairs) of this CTA, and the warp's share of their tiles
     // (32-bit arithmetic: units * gridDim.x stays far below 2^31)
     c.u0 = (int)((unsigned)p.units * blockIdx.x / gridDim.x);
@@ -114,7 +124,11 @@ __device__ __forceinline__ void product_prefetch(const FusedGemvParams& p, const
 
 // Prologue, tile products and epilogue.  All threads of the CTA must call; `wv` as left by
 // product_prefetch for the same p.  Uses the CTA barrier.
-template <bool USE_MMA, int NCOL>
+// WIDE: the input row is staged in shared memory (see fused_wide).  DEEP: many weight tiles per warp
+// (large matrices): the loop requests the following batch of tiles before multiplying the
+// current one and tracks its position by counting; the shallow loop (a few tiles per warp, the
+// latency-bound small matrices) keeps the shortest code path.
+template <bool USE_MMA, int NCOL, bool WIDE = false, bool DEEP = false>
 __device__ __forceinline__ void product_run(const FusedGemvParams& p, const ProductCtx& c, uint4 (&wv)[FG_U],
                                             float* s_sx, int* s_xsum) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -130,11 +144,26 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
 
     // ---- prologue: activation rows -> int8 in shared memory
     const bool writer = blockIdx.x == 0;
-    for (int m = 0; m < p.rows; ++m) {
-        float4 v[FG_V];
-        lean_row<FG_V>(p.st, m, v, scratch, aux, writer);
-        lean_quantize<FG_V>(p.st, v, scratch, xs + (size_t)m * p.st.terms * xs_stride, (size_t)xs_stride,
-                            s_sx + m * p.st.terms, s_xsum + m * p.st.terms);
+    if constexpr (WIDE) {
+        float* row = aux;  // [n] float32
+        const int n = p.st.n;
+        for (int m = 0; m < p.rows; ++m) {
+            __syncthreads();  // the previous row's quantiser is done with the buffer
+            for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4)
+                *reinterpret_cast<float4*>(row + i) = ldcg4(p.st.y + (size_t)m * n + i);
+            __syncthreads();
+            if (p.st.norm1) rmsnorm_inplace(row, n, p.st.norm1, p.st.eps, scratch);
+            quantize_row_from_smem(row, n, p.st.kpad, p.st.terms, xs + (size_t)m * p.st.terms * xs_stride,
+                                   s_sx + m * p.st.terms, s_xsum + m * p.st.terms, scratch, (size_t)xs_stride);
+        }
+    } else {
+        constexpr int V = DEEP ? 2 * FG_V : FG_V;  // the deep variant runs half as many threads
+        for (int m = 0; m < p.rows; ++m) {
+            float4 v[V];
+            lean_row<V>(p.st, m, v, scratch, aux, writer);
+            lean_quantize<V>(p.st, v, scratch, xs + (size_t)m * p.st.terms * xs_stride, (size_t)xs_stride,
+                             s_sx + m * p.st.terms, s_xsum + m * p.st.terms);
+        }
     }
     __syncthreads();
 
@@ -172,24 +201,68 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
     };
     clear();
     int cur = -1;
-    for (int base = w0; base < w1; base += FG_U) {
-#pragma unroll
-        for (int u = 0; u < FG_U; ++u) {
-            const int lt = base + u;
-            if (lt < w1) {
-                const int slot = lt / p.nkt, kt = lt - slot * p.nkt;
-                if (slot != cur) {  // warp-uniform
-                    if (cur >= 0) flush(cur);
-                    clear();
-                    cur = slot;
+    if constexpr (DEEP) {
+        // positions advance by counting, not by dividing: `slot`/`kt` is the tile being multiplied,
+        // `pslot`/`pkt`/`pptr` the tile being requested (FG_U tiles ahead)
+        auto slot_ptr = [&](int sl) {
+            const int u = u0 + (p.halves == 2 ? sl >> 1 : sl), half = p.halves == 2 ? (sl & 1) : 0;
+            return p.tiles + ((size_t)half * p.units + u) * p.nkt * 32 + lane;
+        };
+        int slot = w0 / p.nkt, kt = w0 - slot * p.nkt;
+        int pslot = (w0 + FG_U) / p.nkt, pkt = (w0 + FG_U) - pslot * p.nkt;
+        const uint4* pptr = slot_ptr(pslot) + (size_t)pkt * 32;
+        for (int base = w0; base < w1; base += FG_U) {
+            // the following batch of weight tiles is requested before this one is multiplied
+            uint4 wn[FG_U];
+    #pragma unroll
+            for (int u = 0; u < FG_U; ++u)
+                if (base + FG_U + u < w1) {
+                    wn[u] = ld_stream_v4(pptr);
+                    pptr += 32;
+                    if (++pkt == p.nkt) {
+                        pkt = 0;
+                        pptr = slot_ptr(++pslot);
+                    }
                 }
-                const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-                tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, kt * TILE_K + 32 * t, g, p.cols, accm, accd);
+    #pragma unroll
+            for (int u = 0; u < FG_U; ++u) {
+                if (base + u < w1) {
+                    if (slot != cur) {  // warp-uniform
+                        if (cur >= 0) flush(cur);
+                        clear();
+                        cur = slot;
+                    }
+                    const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+                    tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, kt * TILE_K + 32 * t, g, p.cols, accm, accd);
+                    if (++kt == p.nkt) {
+                        kt = 0;
+                        ++slot;
+                    }
+                }
             }
+    #pragma unroll
+            for (int u = 0; u < FG_U; ++u) wv[u] = wn[u];
         }
+    } else {
+        for (int base = w0; base < w1; base += FG_U) {
 #pragma unroll
-        for (int u = 0; u < FG_U; ++u)
-            if (base + FG_U + u < w1) wv[u] = ld_stream_v4(tile_ptr(base + FG_U + u));
+            for (int u = 0; u < FG_U; ++u) {
+                const int lt = base + u;
+                if (lt < w1) {
+                    const int slot = lt / p.nkt, kt = lt - slot * p.nkt;
+                    if (slot != cur) {  // warp-uniform
+                        if (cur >= 0) flush(cur);
+                        clear();
+                        cur = slot;
+                    }
+                    const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+                    tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, kt * TILE_K + 32 * t, g, p.cols, accm, accd);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < FG_U; ++u)
+                if (base + FG_U + u < w1) wv[u] = ld_stream_v4(tile_ptr(base + FG_U + u));
+        }
     }
     if (cur >= 0) flush(cur);
     __syncthreads();

@@ -33,7 +33,9 @@ int launch_vec_stage(const VecStageParams& p, int rows, cudaStream_t st) {
         RB_CUDA(cudaFuncSetAttribute(vec_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         configured = 200 * 1024;
     }
-    const int threads = p.n >= 2048 ? 1024 : (p.n >= 512 ? 256 : 128);
+    // one CTA per row: a single row wants the widest CTA; with many rows (prefill) narrower CTAs let
+    // several rows share an SM and hide each other's reduction and load latencies
+    const int threads = rows >= 64 ? (p.n >= 512 ? 256 : 128) : (p.n >= 2048 ? 1024 : (p.n >= 512 ? 256 : 128));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(rows);
     cfg.blockDim = dim3(threads);

@@ -74,8 +74,16 @@ def ffn_case():
     return lw, x1, x16
 
 
+# FFN wider than 8192: the down projection's input row takes the shared-memory prologue of the
+# generation-step kernels (no fixture from the reference: checked against the oracle only)
+EXTRA_MODELS = {
+    "wide_ffn": dict(cfg=dict(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=9216),
+                     seed=777, prompt_len=6),
+}
+
+
 def tiny_model(name):
-    spec = TINY_MODELS[name]
+    spec = TINY_MODELS.get(name) or EXTRA_MODELS[name]
     om = O.synth_model(spec["cfg"], spec["seed"])
     rng = np.random.default_rng(spec["seed"] + 1)
     prompt = rng.integers(0, spec["cfg"]["vocab_size"], size=spec["prompt_len"]).astype(np.int64)

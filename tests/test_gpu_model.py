@@ -305,3 +305,19 @@ def test_tiled_prefill_attention(rb, name, causal):
     want2, _ = O.attention(x2, lw, cfg, osem, wc, True)
     got2, cache2 = att.forward(x2, mask=mask2, kv_cache=cache, use_cache=True)
     assert rel_err(got2, want2) < TOL and cache2.length == 187
+
+
+def test_wide_ffn_generation_step(rb):
+    """d_ff above 8192: the down projection's prologue stages its input row in shared memory.
+    Logits within tolerance and the same 32 greedy tokens as the oracle, published semantics."""
+    om, prompt, model = _tiny(rb, "wide_ffn", rb.sem.BASELINE)
+    osem = o_sem(rb.sem.BASELINE)
+    want, _ = O.model_forward(om, prompt[None, :], osem)
+    got, _ = model.forward(prompt[None, :])
+    assert rel_err(got, want) < TOL
+    ids = O.generate_greedy(om, prompt, G.N_NEW, osem)[len(prompt):]
+    before = rb.tr.abi.lib.rotor_b200_launch_count()
+    assert model.generate_greedy(prompt, G.N_NEW, use_graph=False) == ids
+    per_step = (rb.tr.abi.lib.rotor_b200_launch_count() - before) / G.N_NEW
+    assert per_step <= 5 * om["cfg"]["n_layers"] + 2     # the five-launch block (the unfused path takes 8 per block)
+    assert model.generate_greedy(prompt, G.N_NEW, use_graph=True) == ids
