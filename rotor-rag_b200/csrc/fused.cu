@@ -101,11 +101,17 @@ bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int halves
 }
 
 int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int rows, const LeanStage& stage, float* y,
-                      const float* scale, int seg1, int seg2, int ffn_act, cudaStream_t st) {
+                      const float* scale, int seg1, int seg2, int ffn_act, cudaStream_t st, const FusedTpExtra* tp) {
     FusedGemvParams p;
     int grid = sm_count();
     int rc = make_fused_params(p, tiles, out, in, halves, rows, stage, y, scale, seg1, seg2, ffn_act, grid);
     if (rc) return rc;
+    if (tp) {
+        if (stage.terms != 1 || rows > XS_ROWS || (tp->part && halves != 1)) return ROTOR_B200_ERR_ARG;
+        p.xs = tp->xs;
+        p.part = tp->part;
+        p.sx_out = tp->sx_out;
+    }
     if (grid > p.units) grid = p.units;
     // large matrices (eight or more weight tiles per warp) stream: they take the pipelined loop
     const long tiles_per_warp = (long)p.units * p.halves * p.nkt / ((long)grid * FG_WARPS);

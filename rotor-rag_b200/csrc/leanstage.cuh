@@ -11,6 +11,7 @@
 #pragma once
 #include "model.cuh"
 #include "quant.cuh"
+#include "xch.cuh"
 
 namespace rb {
 
@@ -36,6 +37,10 @@ struct LeanStage {
     // quantiser
     int terms;
     int kpad;
+    // tensor parallel: the row is this rank's slice of a longer one.  Exchange index + 1 (0 = none)
+    // of the sum of squares under norm1 and of the absolute maximum under the quantiser; norm_n is
+    // the width of the whole row.
+    int xi_sum, xi_max, norm_n;
 };
 
 __device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
@@ -51,7 +56,7 @@ __device__ __forceinline__ float amax4(const float4& v) {
 // All threads of the block must call.
 template <int LEAN_V>
 __device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[LEAN_V], float* scratch, float* aux,
-                                         bool writer) {
+                                         bool writer, const XchScalarDev* x = nullptr) {
     const int n4 = p.n >> 2, bd = blockDim.x;
     const size_t ro = (size_t)m * p.n;
 #pragma unroll
@@ -152,7 +157,8 @@ __device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) ss += sq4(v[j]);
         ss = block_sum(ss, scratch);
-        const float inv = 1.0f / sqrtf(ss / (float)p.n + p.eps);
+        if (x && p.xi_sum) ss = xch_scalar(*x, p.xi_sum - 1, m, ss, false, writer, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)(p.norm_n ? p.norm_n : p.n) + p.eps);
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) {
             v[j].x *= inv * w1[j].x;
@@ -168,13 +174,15 @@ __device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[
 // Same results as quantize_row_from_smem.  Requires kpad <= 4 * LEAN_V * blockDim.x.
 template <int LEAN_V>
 __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LEAN_V], float* scratch, int8_t* xq,
-                                              size_t tstride, float* sx, int* xsum) {
+                                              size_t tstride, float* sx, int* xsum, int m = 0, bool writer = false,
+                                              const XchScalarDev* x = nullptr) {
     const int n4 = p.n >> 2, k4 = p.kpad >> 2, bd = blockDim.x;
     for (int t = 0; t < p.terms; ++t) {
         float mx = 0.f;
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) mx = fmaxf(mx, amax4(v[j]));
         mx = block_max(mx, scratch);
+        if (x && p.xi_max && t == 0) mx = xch_scalar(*x, p.xi_max - 1, m, mx, true, writer, scratch);
         const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
         const float rs = __fdiv_rn(1.0f, s);
         int lsum = 0;

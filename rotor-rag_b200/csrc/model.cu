@@ -431,7 +431,10 @@ static bool fused_step_ok(const Model& m, int batch, int seq) {
     const Ctx& c = m.c;
     static const bool off = getenv("ROTOR_B200_NO_FUSED_STEP") != nullptr;  // measurement aid
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
-    const bool shape_ok = !off && c.tp_size <= 1 && seq == 1 && batch <= FUSED_MAX_ROWS && batch <= c.max_batch &&
+    static const bool tp_unfused = getenv("ROTOR_B200_TP_UNFUSED") != nullptr;  // measurement aid
+    const bool tp_ok = c.tp_size <= 1 || (!tp_unfused && c.terms == 1 && tp_fused_ready(c.tp) &&
+                                          (size_t)batch * c.d <= (size_t)XCH_CAP);
+    const bool shape_ok = !off && tp_ok && seq == 1 && batch <= FUSED_MAX_ROWS && batch <= c.max_batch &&
                           c.terms <= 3 && batch * c.terms <= 8 && c.ff % 16 == 0;
     const bool q = fused_gemv_supported(qkv_out, c.d, batch, c.terms, 1, 0);
     const bool o = fused_gemv_supported(c.d, c.dq, batch, c.terms, 1, c.n_heads * c.nsplit);
@@ -566,7 +569,7 @@ static int mega_prepare(Model& m, int batch, cudaStream_t st) {
     if (m.mega_batch == batch) return ROTOR_B200_OK;
     m.mega_batch = batch;
     m.mega_ok = 0;
-    if (off || !fused_step_ok(m, batch, 1)) return ROTOR_B200_OK;
+    if (off || m.c.tp_size > 1 || !fused_step_ok(m, batch, 1)) return ROTOR_B200_OK;
     if (!m.mega_host) m.mega_host = calloc((size_t)m.cfg.n_layers, mega_layer_bytes());
     if (!m.mega_host) return ROTOR_B200_ERR_ARG;
     RB_TRY(run_step_fused(m, m.cur_ids, batch, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st, true, true));
@@ -838,12 +841,136 @@ static int run_layers_tp(Model& m, const long long* ids, int batch, int seq, int
     return ROTOR_B200_OK;
 }
 
+// Generation step of a tensor-parallel model with the vector stages fused into the products
+// and the exchanges fused into them where they are scalars: per block
+//   q/k/v product (this rank's heads)          <- residual add, input norm, quantise
+//   attention (this rank's heads)
+//   o product (this rank's columns)            <- merge partials, [max exchange], quantise; int32 partials out
+//   all-reduce + dequantise                    -> float o output, replicated
+//   gate/up product (this rank's channels)     <- sub-norm, residual add, post-attention norm, quantise; gating
+//   down product (this rank's columns)         <- [sum exchange] sub-norm, [max exchange] quantise; int32 partials out
+//   all-reduce + dequantise                    -> float down output, replicated
+// then the LM head over this rank's vocabulary slice and the pick across ranks.  Seven launches
+// per block; five exchanges, all through peer memory.  One activation term only.
+static int run_step_fused_tp(Model& m, const long long* ids, int batch, long long* next_ids, cudaStream_t st,
+                             bool advance) {
+    Ctx& c = m.c;
+    const int d = c.d;
+    const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
+    FusedTpExtra ex = {};
+    ex.xs = tp_scalar_dev(c.tp);
+    int xi = 0, big = 0;  // exchanges so far in this step; vector exchanges so far (slot parity)
+    LeanStage ls;
+    auto stage = [&](int mode, int n) {
+        ls = {};
+        ls.mode = mode;
+        ls.n = n;
+        ls.eps = c.eps;
+        ls.terms = 1;
+        ls.kpad = (int)kpad_of(n);
+    };
+    const float none[3] = {1.f, 1.f, 1.f};
+    for (int l = 0; l < m.cfg.n_layers; ++l) {
+        const rotor_b200_layer_weights& L = m.layers[l];
+        if (l == 0) {
+            stage(LM_EMBED, d);
+            ls.ids = ids;
+            ls.embed = m.embed;
+        } else {
+            stage(LM_ADD, d);
+            ls.y = c.fy[3];
+            ls.h = c.h2;
+        }
+        ls.h_out = c.h;
+        ls.norm1 = L.input_norm;
+        const float sqkv[3] = {L.q_scale, L.k_scale, L.v_scale};
+        RB_TRY(launch_fused_gemv(L.qkv_tiles, qkv_out, d, 1, batch, ls, c.fy[0], sqkv, c.dq, c.dq + c.dkv, 0, st));
+
+        AttnDecodeParams dp = {};
+        dp.qkv_f = c.fy[0];
+        dp.n_heads = c.n_heads;
+        dp.n_kv_heads = c.n_kv_heads;
+        dp.head_dim = c.head_dim;
+        dp.max_seq = c.max_seq;
+        dp.nsplit = c.nsplit;
+        dp.past_len = c.d_pos;
+        dp.rope = c.rope;
+        dp.k_cache = L.k_cache;
+        dp.v_cache = L.v_cache;
+        dp.part_o = c.part_o;
+        dp.part_m = c.part_m;
+        dp.part_l = c.part_l;
+        RB_TRY(launch_attn_decode(dp, batch, st));
+
+        stage(LM_ATTN, c.dq);
+        ls.part_o = c.part_o;
+        ls.part_m = c.part_m;
+        ls.part_l = c.part_l;
+        ls.nsplit = c.nsplit;
+        ls.n_heads = c.n_heads;
+        ls.head_dim = c.head_dim;
+        ls.xi_max = ++xi;  // (index + 1)
+        ex.part = c.accB;
+        ex.sx_out = c.sx[1];
+        RB_TRY(launch_fused_gemv(L.o_tiles, d, c.dq, 1, batch, ls, c.fy[1], none, d, d, 0, st, &ex));
+        RB_TRY(tp_allreduce_dequant(c.tp, big++, xi++, c.accB, c.sx[1], L.o_scale, c.fy[1], batch, d, st));
+
+        stage(LM_SUBNORM_ADD, d);
+        ls.y = c.fy[1];
+        ls.h = c.h;
+        ls.h_out = c.h2;
+        ls.norm0 = L.attn_sub_norm;
+        ls.norm1 = L.post_attn_norm;
+        const float sgu[3] = {L.gate_scale, L.up_scale, 0.f};
+        RB_TRY(launch_fused_gemv(L.gate_up_tiles, c.ff, d, 2, batch, ls, c.fy[2], sgu, 0, 0, c.ffn_act, st));
+
+        stage(LM_PLAIN, c.ff);
+        ls.y = c.fy[2];
+        ls.norm1 = L.ffn_sub_norm;  // this rank's slice of the weight
+        ls.norm_n = c.ff_total;
+        ls.xi_sum = ++xi;
+        ls.xi_max = ++xi;
+        RB_TRY(launch_fused_gemv(L.down_tiles, d, c.ff, 1, batch, ls, c.fy[3], none, d, d, 0, st, &ex));
+        RB_TRY(tp_allreduce_dequant(c.tp, big++, xi++, c.accB, c.sx[1], L.down_scale, c.fy[3], batch, d, st));
+    }
+    // LM head over this rank's vocabulary slice (residual add and final norm in its prologue), pick across ranks
+    const int vl = m.cfg.vocab_size / c.tp_size, rank = tp_rank(c.tp);
+    LmHeadParams lp = {};
+    lp.embed = m.embed + (size_t)rank * vl * d;
+    lp.vocab = vl;
+    lp.d = d;
+    lp.part_val = m.part_val;
+    lp.part_idx = m.part_idx;
+    lp.argmax_out = m.pick_idx;
+    lp.argmax_val = m.pick_val;
+    lp.nparts = lmhead_parts();
+    lp.tail_counter = c.counters + 3;
+    lp.pro_y = c.fy[3];
+    lp.pro_h = c.h2;
+    lp.pro_norm = m.final_norm;
+    lp.pro_eps = c.eps;
+    RB_TRY(launch_lmhead(lp, batch, st));
+    pack_pick_kernel<<<(batch + 127) / 128, 128, 0, st>>>(m.pick_val, m.pick_idx, (long long)rank * vl, batch, m.pick_send);
+    RB_TRY(launch_status());
+    RB_TRY(tp_allgather_bytes(c.tp, m.pick_send, m.pick_recv, (size_t)batch * 12, st));
+    final_pick_kernel<<<(batch + 127) / 128, 128, 0, st>>>(m.pick_recv, c.tp_size, batch, next_ids);
+    RB_TRY(launch_status());
+    if (advance) {
+        advance_kernel<<<1, 1024, 0, st>>>(next_ids, m.tok_log, batch, m.max_log, c.d_pos, m.d_step);
+        RB_TRY(launch_status());
+    }
+    return tp_step_end(c.tp, xi, st);
+}
+
+
 // ids: device [batch*seq]; the position is read from c.d_pos by the kernels.
 static int run_layers(Model& m, const long long* ids, int batch, int seq, int logits_mode, float* logits,
                       long long* next_ids, cudaStream_t st, bool advance = false) {
     Ctx& c = m.c;
     if (c.tp_size > 1) {
         if (!c.tp) return ROTOR_B200_ERR_ARG;  // rotor_b200_model_set_tp has not been called
+        if (fused_step_ok(m, batch, seq) && next_ids && logits_mode == ROTOR_B200_LOGITS_NONE)
+            return run_step_fused_tp(m, ids, batch, next_ids, st, advance);
         return run_layers_tp(m, ids, batch, seq, logits_mode, logits, next_ids, st, advance);
     }
     if (fused_step_ok(m, batch, seq) && (logits_mode != ROTOR_B200_LOGITS_NONE || next_ids))

@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 
 #include "common.cuh"
+#include "xch.cuh"
 
 namespace rb {
 
@@ -80,8 +81,16 @@ int launch_gemm_mma(const void* tiles, size_t out, size_t in, const int8_t* xq, 
 
 // Generation-step product with the consuming vector stage fused in (fused.cu, leanstage.cuh).
 struct LeanStage;
+// Tensor-parallel extras of a product: the scalar exchange ring its prologue uses and, for a
+// row-parallel product, where the int32 partial sums and the activation scales go.
+struct FusedTpExtra {
+    XchScalarDev xs;
+    int32_t* part;
+    float* sx_out;
+};
 int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int rows, const LeanStage& stage, float* y,
-                      const float* scale, int seg1, int seg2, int ffn_act, cudaStream_t st);
+                      const float* scale, int seg1, int seg2, int ffn_act, cudaStream_t st,
+                      const FusedTpExtra* tp = nullptr);
 bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int halves, int merge_weights);
 int configure_fused_gemv();
 int fused_sm_count();
@@ -188,5 +197,11 @@ int tp_size(void* comm);
 int tp_allreduce_sum_i32(void* comm, int32_t* buf, size_t n, cudaStream_t st);
 int tp_allreduce_f32(void* comm, float* buf, size_t n, bool max_op, cudaStream_t st);
 int tp_allgather_bytes(void* comm, const void* send, void* recv, size_t bytes_per_rank, cudaStream_t st);
+// Exchanges of the generation-step path (see xch.cuh): available when the peer-memory set-up succeeded.
+bool tp_fused_ready(void* comm);
+XchScalarDev tp_scalar_dev(void* comm);
+int tp_allreduce_dequant(void* comm, int slotsel, int idx, const int32_t* part, const float* sx, float scale, float* y,
+                         int rows, int n, cudaStream_t st);
+int tp_step_end(void* comm, int nexchanges, cudaStream_t st);
 
 }  // namespace rb

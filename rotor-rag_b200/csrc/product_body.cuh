@@ -27,6 +27,12 @@ struct FusedGemvParams {
     float scale[3];       // per-tensor weight scales of up to three stacked row segments
     int seg1, seg2;       // first row of the second / third segment (plain); halves == 2: scale[0]=gate, [1]=up
     int ffn_act;
+    // tensor parallel (row-parallel products): scalar exchange ring (size 0: none); with `part` set
+    // the epilogue hands over exact int32 partial sums [rows][out] and the activation scales
+    // instead of dequantised floats (one activation term only)
+    XchScalarDev xs;
+    int32_t* part;
+    float* sx_out;
 };
 
 // Input rows wider than the register-resident prologue holds (4 * FG_V * FG_THREADS elements)
@@ -152,17 +158,42 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
             for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4)
                 *reinterpret_cast<float4*>(row + i) = ldcg4(p.st.y + (size_t)m * n + i);
             __syncthreads();
-            if (p.st.norm1) rmsnorm_inplace(row, n, p.st.norm1, p.st.eps, scratch);
+            __shared__ float s_ext[2];
+            const XchScalarDev* x = p.xs.size ? &p.xs : nullptr;
+            if (p.st.norm1) {
+                if (x && p.st.xi_sum) {  // sum of squares of the whole (sharded) row
+                    float ss = 0.f;
+                    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += row[i] * row[i];
+                    ss = block_sum(ss, scratch);
+                    ss = xch_scalar(*x, p.st.xi_sum - 1, m, ss, false, writer, scratch);
+                    if (threadIdx.x == 0) s_ext[0] = ss;
+                    __syncthreads();
+                    rmsnorm_inplace(row, n, p.st.norm1, p.st.eps, scratch, &s_ext[0], p.st.norm_n);
+                } else {
+                    rmsnorm_inplace(row, n, p.st.norm1, p.st.eps, scratch);
+                }
+            }
+            const float* given = nullptr;
+            if (x && p.st.xi_max) {  // absolute maximum of the whole row
+                float mx = 0.f;
+                for (int i = threadIdx.x; i < n; i += blockDim.x) mx = fmaxf(mx, fabsf(row[i]));
+                mx = block_max(mx, scratch);
+                mx = xch_scalar(*x, p.st.xi_max - 1, m, mx, true, writer, scratch);
+                if (threadIdx.x == 0) s_ext[1] = mx;
+                __syncthreads();
+                given = &s_ext[1];
+            }
             quantize_row_from_smem(row, n, p.st.kpad, p.st.terms, xs + (size_t)m * p.st.terms * xs_stride,
-                                   s_sx + m * p.st.terms, s_xsum + m * p.st.terms, scratch, (size_t)xs_stride);
+                                   s_sx + m * p.st.terms, s_xsum + m * p.st.terms, scratch, (size_t)xs_stride, given);
         }
     } else {
         constexpr int V = DEEP ? 2 * FG_V : FG_V;  // the deep variant runs half as many threads
         for (int m = 0; m < p.rows; ++m) {
             float4 v[V];
-            lean_row<V>(p.st, m, v, scratch, aux, writer);
+            const XchScalarDev* x = p.xs.size ? &p.xs : nullptr;
+            lean_row<V>(p.st, m, v, scratch, aux, writer, x);
             lean_quantize<V>(p.st, v, scratch, xs + (size_t)m * p.st.terms * xs_stride, (size_t)xs_stride,
-                             s_sx + m * p.st.terms, s_xsum + m * p.st.terms);
+                             s_sx + m * p.st.terms, s_xsum + m * p.st.terms, m, writer, x);
         }
     }
     __syncthreads();
@@ -273,6 +304,10 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         const int m = e % p.rows, rl = (e / p.rows) & 15, lu = e / (p.rows * 16);
         const int orow = (u0 + lu) * TILE_ROWS + rl;
         if (orow >= p.out) continue;
+        if (p.part) {  // exact partial sum of this rank's columns; summed across ranks and dequantised later
+            p.part[(size_t)m * p.out + orow] = merge[lu * 128 + rl * 8 + m] - s_xsum[m];
+            continue;
+        }
         float val[2] = {0.f, 0.f};
         for (int half = 0; half < p.halves; ++half) {
             const int* src = merge + (lu * p.halves + half) * 128 + rl * 8 + m * T;
@@ -295,6 +330,7 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         }
         p.y[(size_t)m * p.out + orow] = r;
     }
+    if (p.part && writer && (int)threadIdx.x < p.rows) p.sx_out[threadIdx.x] = s_sx[threadIdx.x];
 }
 
 }  // namespace rb

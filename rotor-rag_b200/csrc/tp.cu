@@ -22,6 +22,7 @@
 #include <cstring>
 
 #include "model.cuh"
+#include "xch.cuh"
 
 namespace rb {
 
@@ -52,10 +53,6 @@ static int load_nccl() {
     return ROTOR_B200_OK;
 }
 
-constexpr int XCH_MAX_RANKS = 8;
-constexpr int XCH_CAP = 1 << 16;  // 32-bit elements per one-shot collective
-constexpr long long XCH_SPIN_CYCLES = 2000000000LL;  // about one second
-
 // Device view of the exchange: rank r's buffer is uint2 [2 slots][size][XCH_CAP].
 struct XchDev {
     uint2* buf[XCH_MAX_RANKS];  // this process's mapping of every rank's buffer (own included)
@@ -72,17 +69,10 @@ struct TpComm {
     XchDev x;
     void* own;                  // this rank's exchange buffer (cudaMalloc)
     void* peer[XCH_MAX_RANKS];  // IPC mappings to close
-    unsigned* ctr;              // seq, done
+    unsigned* ctr;              // seq, done (self-advancing collectives); seq2 (step-advanced exchanges)
+    XchDev fused;               // vector exchange of the generation-step path (own buffer region, seq2)
+    XchScalarDev scalar;        // scalar ring of the generation-step path
 };
-
-__device__ __forceinline__ void st_pair(uint2* p, unsigned v, unsigned g) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v), "r"(g) : "memory");
-}
-__device__ __forceinline__ uint2 ld_pair(const uint2* p) {
-    uint2 r;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
-    return r;
-}
 
 enum { XOP_SUM_I32 = 0, XOP_SUM_F32 = 1, XOP_MAX_F32 = 2 };
 
@@ -146,17 +136,61 @@ static int launch_oneshot(TpComm* t, const void* in, void* out, size_t n, cudaSt
     return launch_status();
 }
 
+
+// Vector exchange of the generation-step path: int32 partial sums of a row-parallel product are
+// summed across ranks and dequantised in one pass, y = (float)sum * sx[row] * scale -- the
+// arithmetic of the single-GPU product epilogue.  Generation = step counter + 1 + idx; the
+// counter is advanced once per step by xch_bump_kernel.  `slotsel` alternates between the two
+// vector exchanges of a block.
+__global__ void __launch_bounds__(256) oneshot_allreduce_dequant_kernel(const __grid_constant__ XchDev t, int slotsel,
+                                                                        int idx, const int* part, const float* sx,
+                                                                        float scale, float* y, int rows, int n) {
+    const unsigned gen = *reinterpret_cast<const volatile unsigned*>(t.seq) + 1u + (unsigned)idx;
+    const size_t slot = (size_t)slotsel * t.size;
+    const int total = rows * n;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int v = part[i];
+        for (int p = 0; p < t.size; ++p)
+            if (p != t.rank) st_pair(t.buf[p] + (slot + t.rank) * XCH_CAP + i, (unsigned)v, gen);
+        int acc = 0;
+        for (int src = 0; src < t.size; ++src)
+            acc += src == t.rank ? v : (int)xch_poll(t.buf[t.rank] + (slot + src) * XCH_CAP + i, gen, t.status, src);
+        y[i] = __fmul_rn(__fmul_rn((float)acc, sx[i / n]), scale);
+    }
+}
+
+__global__ void xch_bump_kernel(unsigned* seq, unsigned n) { *seq += n; }
+
+bool tp_fused_ready(void* c) { return c && static_cast<TpComm*>(c)->oneshot; }
+XchScalarDev tp_scalar_dev(void* c) { return static_cast<TpComm*>(c)->scalar; }
+int tp_allreduce_dequant(void* c, int slotsel, int idx, const int32_t* part, const float* sx, float scale, float* y,
+                         int rows, int n, cudaStream_t st) {
+    TpComm* t = static_cast<TpComm*>(c);
+    if (!t->oneshot || (size_t)rows * n > (size_t)XCH_CAP) return ROTOR_B200_ERR_ARG;
+    int grid = (rows * n + 255) / 256;
+    if (grid > 64) grid = 64;
+    oneshot_allreduce_dequant_kernel<<<grid, 256, 0, st>>>(t->fused, slotsel & 1, idx, part, sx, scale, y, rows, n);
+    return launch_status();
+}
+int tp_step_end(void* c, int nexchanges, cudaStream_t st) {
+    TpComm* t = static_cast<TpComm*>(c);
+    xch_bump_kernel<<<1, 1, 0, st>>>(t->ctr + 2, (unsigned)nexchanges);
+    return launch_status();
+}
+
 // Peer-memory set-up: allocate and zero the exchange buffer, swap IPC handles through the
 // NCCL communicator, map every peer.  Failure leaves the communicator on NCCL alone.
 static int setup_oneshot(TpComm* t) {
     if (t->size > XCH_MAX_RANKS || t->size < 2) return ROTOR_B200_ERR_ARG;
-    const size_t bytes = 2 * (size_t)t->size * XCH_CAP * sizeof(uint2);
+    const size_t big = 2 * (size_t)t->size * XCH_CAP;             // uint2 words of one vector-exchange region
+    const size_t ring = (size_t)XS_RING * t->size * XS_ROWS;      // uint2 words of the scalar ring
+    const size_t bytes = (2 * big + ring) * sizeof(uint2);
     unsigned char* scratch = nullptr;
     RB_CUDA(cudaMalloc(&t->own, bytes));
-    RB_CUDA(cudaMalloc(&t->ctr, 2 * sizeof(unsigned)));
+    RB_CUDA(cudaMalloc(&t->ctr, 4 * sizeof(unsigned)));
     RB_CUDA(cudaMalloc(&scratch, (size_t)(t->size + 1) * sizeof(cudaIpcMemHandle_t)));
     RB_CUDA(cudaMemset(t->own, 0, bytes));
-    RB_CUDA(cudaMemset(t->ctr, 0, 2 * sizeof(unsigned)));
+    RB_CUDA(cudaMemset(t->ctr, 0, 4 * sizeof(unsigned)));
     cudaIpcMemHandle_t mine, all[XCH_MAX_RANKS];
     RB_CUDA(cudaIpcGetMemHandle(&mine, t->own));
     RB_CUDA(cudaMemcpy(scratch, &mine, sizeof(mine), cudaMemcpyHostToDevice));
@@ -180,6 +214,17 @@ static int setup_oneshot(TpComm* t) {
     t->x.rank = t->rank;
     t->x.size = t->size;
     if (!t->x.status) return ROTOR_B200_ERR_CUDA;
+    t->fused = t->x;
+    t->fused.seq = t->ctr + 2;
+    t->fused.done = nullptr;
+    t->scalar.seq = t->ctr + 2;
+    t->scalar.status = t->x.status;
+    t->scalar.rank = t->rank;
+    t->scalar.size = t->size;
+    for (int p = 0; p < t->size; ++p) {
+        t->fused.buf[p] = t->x.buf[p] + big;
+        t->scalar.buf[p] = t->x.buf[p] + 2 * big;
+    }
     t->oneshot = true;
     return ROTOR_B200_OK;
 }

@@ -79,6 +79,9 @@ def ffn_case():
 EXTRA_MODELS = {
     "wide_ffn": dict(cfg=dict(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=9216),
                      seed=777, prompt_len=6),
+    # per-rank FFN slice still wider than 8192 when split two ways
+    "wide_tp": dict(cfg=dict(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=18432),
+                    seed=778, prompt_len=6),
 }
 
 

@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, port, out_dir):
+def _worker(rank, port, out_dir, name):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -35,16 +35,19 @@ def _worker(rank, port, out_dir):
     group = None
     try:
         group = TPGroup()
-        om, prompt = G.tiny_model("hd128")
+        om, prompt = G.tiny_model(name)
         model = ShardedBitNetModel(om["cfg"], group, semantics=BASELINE.with_(act_terms=1), max_seq=64)
         model.load_from_params(om)
         logits = model.forward(prompt[None, :])                      # [1, S, V/2]
         last = model.forward(prompt[None, :], logits_positions="last")
+        from rotor_b200 import abi
+        before = abi.lib.rotor_b200_launch_count()
         eager = model.generate_greedy(prompt, G.N_NEW, use_graph=False)
+        per_step = (abi.lib.rotor_b200_launch_count() - before) / G.N_NEW
         graph = model.generate_greedy(prompt, G.N_NEW, use_graph=True)
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), logits=logits, last=last, eager=np.array(eager),
-                 graph=np.array(graph))
+                 graph=np.array(graph), per_step=per_step)
         del model
     finally:
         if group is not None:
@@ -52,13 +55,14 @@ def _worker(rank, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_two_gpu_model_matches_oracle(tmp_path):
+@pytest.mark.parametrize("name", ["hd128", "wide_tp"])
+def test_two_gpu_model_matches_oracle(tmp_path, name):
     import torch
     if torch.cuda.device_count() < WORLD:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(_free_port(), str(tmp_path)), nprocs=WORLD, join=True)
-    om, prompt = G.tiny_model("hd128")
+    mp.spawn(_worker, args=(_free_port(), str(tmp_path), name), nprocs=WORLD, join=True)
+    om, prompt = G.tiny_model(name)
     sem = O.with_semantics(O.BASELINE, act_terms=1)
     want, _ = O.model_forward(om, prompt[None, :], sem)
     ids = O.generate_greedy(om, prompt, G.N_NEW, sem)[len(prompt):]
@@ -71,3 +75,5 @@ def test_two_gpu_model_matches_oracle(tmp_path):
         assert np.max(np.abs(got["last"][:, 0] - ref[:, -1])) / rms < TOL
         assert list(got["eager"]) == ids
         assert list(got["graph"]) == ids
+        # generation steps take the seven-launch block with in-kernel exchanges (+ LM head, pick, advance, bump)
+        assert float(got["per_step"]) <= 7 * om["cfg"]["n_layers"] + 8
