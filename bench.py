@@ -414,6 +414,54 @@ def run_prefill(args, rank, world):
         "gpu_launches": int(launches), "clocks": clocks}), flush=True)
 
 
+def run_ffn_block(args):
+    """Config 2: the 2B-shape FFN block (pre-norm, gate/up BitLinear 2560 -> 6912, squared-ReLU gating,
+    sub-norm over 6912, down BitLinear 6912 -> 2560) for 1 and 16 token rows.  64 blocks with distinct
+    weights (850 MB > L2) run back to back in one CUDA graph."""
+    import torch
+    from rotor_b200 import semantics
+    from rotor_b200.transformer import GatedFFN, RMSNorm
+    torch.cuda.set_device(0)
+    d, ff, nblk = 2560, 6912, 64
+    blocks = []
+    for i in range(nblk):
+        f = GatedFFN(d, ff, semantics=semantics.BASELINE)
+        for p in (f.gate_proj, f.up_proj, f.down_proj):
+            p.load_from_int8(torch.randint(-1, 2, (p.out_features, p.in_features), device="cuda", dtype=torch.int8), 0.016)
+        blocks.append(f)
+    pre = RMSNorm(d, eps=semantics.BASELINE.eps)
+    peak, peak_kind = measured_peak_gbs()
+    out = {"metric": "2B-shape FFN block time", "unit": "us per block", "higher_is_better": False, "data": "synthetic",
+           "config": {"workload": "RMSNorm + gate/up 2560->6912 + relu^2 gating + sub-norm + down 6912->2560, "
+                                  "64 distinct blocks per graph replay"}, "rows": {}}
+    st = torch.cuda.Stream()
+    for m in (1, 16):
+        x = torch.randn(m, d, device="cuda")
+        with torch.cuda.stream(st):
+            for f in blocks:          # every block once outside the capture: device copies of the norm weights
+                f.forward_device(x, pre_norm=pre)
+            st.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                for f in blocks:
+                    y = f.forward_device(x, pre_norm=pre)
+            for _ in range(3):
+                g.replay()
+            st.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(10):
+                g.replay()
+            e1.record(st)
+            st.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (10 * nblk)
+        alg = 3 * d * ff // 4 + (2 * d + ff) * 4 + 2 * m * d * 4    # tiles + norm weights + rows in and out
+        out["rows"][str(m)] = {"us_per_block": us, "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3,
+                               "frac_of_peak": alg / us / 1e3 / peak}
+    out["peak_kind"] = peak_kind
+    print(json.dumps(out), flush=True)
+
+
 def run_xl_tp(args, rank, world):
     """Batch-1 greedy decode of the XL shape, sharded over `world` GPUs (1 = unsharded)."""
     import numpy as np
@@ -429,33 +477,35 @@ def run_xl_tp(args, rank, world):
     if args.layers:
         cfg["n_layers"] = args.layers
     K, W = args.steps, max(args.warmup, 3)
+    B = args.batch or 1
     max_seq = PROMPT_LEN + 1 + W + K + 8
     sem = semantics.BASELINE
     group = None
     if world > 1:
-        dist.init_process_group("gloo")   # carries the communicator id only; the data path is the library's NCCL
+        dist.init_process_group("gloo")   # carries the communicator id only; the data path is the library's own
         group = TPGroup()
-        model = ShardedBitNetModel(cfg, group, semantics=sem, max_seq=max_seq, max_rows=PROMPT_LEN)
+        model = ShardedBitNetModel(cfg, group, semantics=sem, max_seq=max_seq, max_batch=B, max_rows=B * PROMPT_LEN)
         model.load_random(seed=4321)
-        handle = model._ensure_handle(1, PROMPT_LEN, max_seq)
+        handle = model._ensure_handle(B, PROMPT_LEN, max_seq)
     else:
-        model = random_model_on_device(cfg, seed=4321, semantics=sem, max_seq=max_seq, max_rows=PROMPT_LEN)
-        handle = model._ensure_handle(1, PROMPT_LEN, max_seq).h
+        model = random_model_on_device(cfg, seed=4321, semantics=sem, max_seq=max_seq, max_batch=B,
+                                       max_rows=B * PROMPT_LEN)
+        handle = model._ensure_handle(B, PROMPT_LEN, max_seq).h
 
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
 
-    prompt = np.random.default_rng(7).integers(0, cfg["vocab_size"], size=PROMPT_LEN).astype(np.int64)
+    prompt = np.random.default_rng(7).integers(0, cfg["vocab_size"], size=(B, PROMPT_LEN)).astype(np.int64)
     st = torch.cuda.Stream()
     with torch.cuda.stream(st):
         s = st.cuda_stream
-        ids_d = torch.from_numpy(prompt.reshape(1, -1)).cuda()
-        first = torch.empty(1, dtype=torch.int64, device="cuda")
-        abi.check(abi.lib.rotor_b200_model_forward(handle, ids_d.data_ptr(), 1, PROMPT_LEN, 0, abi.LOGITS_NONE, None,
+        ids_d = torch.from_numpy(prompt).cuda()
+        first = torch.empty(B, dtype=torch.int64, device="cuda")
+        abi.check(abi.lib.rotor_b200_model_forward(handle, ids_d.data_ptr(), B, PROMPT_LEN, 0, abi.LOGITS_NONE, None,
                                                    first.data_ptr(), s), "prefill")
-        abi.check(abi.lib.rotor_b200_model_decode_begin(handle, first.data_ptr(), 1, PROMPT_LEN, s), "begin")
+        abi.check(abi.lib.rotor_b200_model_decode_begin(handle, first.data_ptr(), B, PROMPT_LEN, s), "begin")
         abi.check(abi.lib.rotor_b200_model_decode_steps(handle, W, int(args.graph), s), "warmup")
         barrier()
         sampler = ClockSampler(local)
@@ -474,7 +524,7 @@ def run_xl_tp(args, rank, world):
         clocks = sampler.stop(t0, t1)
         launches = abi.lib.rotor_b200_launch_count() - before
         sec = e0.elapsed_time(e1) * 1e-3
-        toks = np.empty(W + K, dtype=np.int64)
+        toks = np.empty((W + K) * B, dtype=np.int64)
         abi.check(abi.lib.rotor_b200_model_read_tokens(handle, 0, W + K, toks.ctypes.data, s), "read_tokens")
     abi.device_status()
     if world > 1:
@@ -485,12 +535,12 @@ def run_xl_tp(args, rank, world):
         peak, peak_kind = measured_peak_gbs()
         step_bytes = algorithmic_bytes_per_token(cfg, PROMPT_LEN + 1 + W + K // 2)
         print(json.dumps({
-            "metric": "XL-shape greedy decode tokens/s (batch 1, tensor parallel)", "value": K / sec, "unit": UNIT,
+            "metric": f"XL-shape greedy decode tokens/s (batch {B}, tensor parallel)", "value": B * K / sec, "unit": UNIT,
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": sec * 1e3 / K, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "data": "synthetic",
             "dtype": "int8 activations x ternary weights -> int32 (float32 glue, bf16 LM head)",
             "config": {"workload": f"random-init {cfg['n_layers']}-layer d {cfg['d_model']} ffn {cfg['d_ff']} "
-                                   f"{cfg['n_heads']}q/{cfg['n_kv_heads']}kv model, greedy decode batch 1 after a "
+                                   f"{cfg['n_heads']}q/{cfg['n_kv_heads']}kv model, greedy decode batch {B} after a "
                                    f"{PROMPT_LEN}-token prompt", "parallelism": f"tp{world}",
                        "cuda_graph": bool(args.graph), "l2": "inputs larger than L2"},
             "gpu_launches": int(launches), "clocks": clocks,
@@ -515,9 +565,9 @@ def main():
                     help="profiling aid: run only the device-resident decode section, the GEMV section, or one "
                          "prefill GEMM (--m tokens)")
     ap.add_argument("--m", type=int, default=16384, help="--only gemm: activation columns (tokens)")
-    ap.add_argument("--workload", default="decode_2b", choices=["decode_2b", "xl_tp", "prefill_2b"],
+    ap.add_argument("--workload", default="decode_2b", choices=["decode_2b", "xl_tp", "prefill_2b", "ffn_block"],
                     help="decode_2b: the headline line; xl_tp: the tensor-parallel XL shape (separate line)")
-    ap.add_argument("--batch", type=int, default=0, help="prefill_2b: sequences (0 = 8)")
+    ap.add_argument("--batch", type=int, default=0, help="prefill_2b: sequences (0 = 8); xl_tp: sequences (0 = 1)")
     ap.add_argument("--seq", type=int, default=0, help="prefill_2b: positions per sequence (0 = 2048)")
     ap.add_argument("--layers", type=int, default=0, help="xl_tp: override the layer count (0 = 80)")
     ap.add_argument("--graph", type=int, default=1, help="xl_tp: replay the step as a CUDA graph (1) or launch it (0)")
@@ -544,6 +594,9 @@ def main():
         run_reference(args, rank)
     elif args.workload == "xl_tp":
         run_xl_tp(args, rank, world)
+    elif args.workload == "ffn_block":
+        if rank == 0:
+            run_ffn_block(args)
     elif args.workload == "prefill_2b":
         if rank == 0:
             run_prefill(args, rank, world)

@@ -15,7 +15,7 @@ RB_TRACE_DEFINE(rotor_b200_trace_read_fused)
 
 namespace rb {
 
-template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP>
+template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP, bool TP>
 __global__ void __launch_bounds__(DEEP ? FG_THREADS_DEEP : FG_THREADS, 1) fused_gemv_kernel(const __grid_constant__ FusedGemvParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ float s_sx[8];
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(DEEP ? FG_THREADS_DEEP : FG_THREADS, 1) fused_
     RB_STAMP(tr, 1);
     pdl_wait();  // the weights above are constants; everything below depends on earlier kernels
     RB_STAMP(tr, 2);
-    product_run<USE_MMA, NCOL, WIDE, DEEP>(p, c, wv, s_sx, s_xsum);
+    product_run<USE_MMA, NCOL, WIDE, DEEP, TP>(p, c, wv, s_sx, s_xsum);
     RB_STAMP(tr, 5);
     RB_TRACE_COMMIT(tr, p.st.mode * 10 + p.halves);
 }
@@ -45,8 +45,14 @@ static int sm_count() {
     return g_sm_count;
 }
 
-template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP>
-static int launch_fused(const FusedGemvParams& p, int grid, cudaStream_t st) {
+template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP, bool TP>
+static int launch_fused_tp(const FusedGemvParams& p, int grid, cudaStream_t st) {
+    static bool configured = false;  // each variant raises its own shared-memory limit once
+    if (!configured) {
+        RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<USE_MMA, NCOL, WIDE, DEEP, TP>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured = true;
+    }
     const size_t smem = fused_smem(p);
     if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     cudaLaunchConfig_t cfg = {};
@@ -59,24 +65,30 @@ static int launch_fused(const FusedGemvParams& p, int grid, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_use_pdl ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, fused_gemv_kernel<USE_MMA, NCOL, WIDE, DEEP>, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, fused_gemv_kernel<USE_MMA, NCOL, WIDE, DEEP, TP>, p) != cudaSuccess) {
         ++g_launch_count;
         return ROTOR_B200_ERR_CUDA;
     }
     return launch_status();
 }
 
+template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP>
+static int launch_fused(const FusedGemvParams& p, int grid, cudaStream_t st) {
+    if (p.xs.size || p.part) return launch_fused_tp<USE_MMA, NCOL, WIDE, DEEP, true>(p, grid, st);
+    return launch_fused_tp<USE_MMA, NCOL, WIDE, DEEP, false>(p, grid, st);
+}
+
 int configure_fused_gemv() {
     const int big = 200 * 1024;
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 1, true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<false, 2, true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<true, 1, true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
     sm_count();
     return ROTOR_B200_OK;
 }

@@ -134,7 +134,8 @@ __device__ __forceinline__ void product_prefetch(const FusedGemvParams& p, const
 // (large matrices): the loop requests the following batch of tiles before multiplying the
 // current one and tracks its position by counting; the shallow loop (a few tiles per warp, the
 // latency-bound small matrices) keeps the shortest code path.
-template <bool USE_MMA, int NCOL, bool WIDE = false, bool DEEP = false>
+// TP: tensor-parallel hooks compiled in (scalar exchanges in the prologue, int32 partial output).
+template <bool USE_MMA, int NCOL, bool WIDE = false, bool DEEP = false, bool TP = false>
 __device__ __forceinline__ void product_run(const FusedGemvParams& p, const ProductCtx& c, uint4 (&wv)[FG_U],
                                             float* s_sx, int* s_xsum) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -159,7 +160,7 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
                 *reinterpret_cast<float4*>(row + i) = ldcg4(p.st.y + (size_t)m * n + i);
             __syncthreads();
             __shared__ float s_ext[2];
-            const XchScalarDev* x = p.xs.size ? &p.xs : nullptr;
+            const XchScalarDev* x = (TP && p.xs.size) ? &p.xs : nullptr;
             if (p.st.norm1) {
                 if (x && p.st.xi_sum) {  // sum of squares of the whole (sharded) row
                     float ss = 0.f;
@@ -190,7 +191,7 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         constexpr int V = DEEP ? 2 * FG_V : FG_V;  // the deep variant runs half as many threads
         for (int m = 0; m < p.rows; ++m) {
             float4 v[V];
-            const XchScalarDev* x = p.xs.size ? &p.xs : nullptr;
+            const XchScalarDev* x = (TP && p.xs.size) ? &p.xs : nullptr;
             lean_row<V>(p.st, m, v, scratch, aux, writer, x);
             lean_quantize<V>(p.st, v, scratch, xs + (size_t)m * p.st.terms * xs_stride, (size_t)xs_stride,
                              s_sx + m * p.st.terms, s_xsum + m * p.st.terms, m, writer, x);
@@ -304,7 +305,7 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         const int m = e % p.rows, rl = (e / p.rows) & 15, lu = e / (p.rows * 16);
         const int orow = (u0 + lu) * TILE_ROWS + rl;
         if (orow >= p.out) continue;
-        if (p.part) {  // exact partial sum of this rank's columns; summed across ranks and dequantised later
+        if (TP && p.part) {  // exact partial sum of this rank's columns; summed across ranks and dequantised later
             p.part[(size_t)m * p.out + orow] = merge[lu * 128 + rl * 8 + m] - s_xsum[m];
             continue;
         }
@@ -330,7 +331,7 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         }
         p.y[(size_t)m * p.out + orow] = r;
     }
-    if (p.part && writer && (int)threadIdx.x < p.rows) p.sx_out[threadIdx.x] = s_sx[threadIdx.x];
+    if (TP && p.part && writer && (int)threadIdx.x < p.rows) p.sx_out[threadIdx.x] = s_sx[threadIdx.x];
 }
 
 }  // namespace rb
