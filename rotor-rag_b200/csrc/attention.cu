@@ -8,6 +8,7 @@
 // 1/sqrt(head_dim) (line 267) and no mask is applied unless asked for (line 270-271).
 // The cache is a fixed [batch][n_kv][max_seq][D] float32 buffer written in place at
 // position past_len + s instead of the reference's per-step np.concatenate.
+#include <cstdlib>
 #include "attn_body.cuh"
 #include "quant.cuh"
 
@@ -157,7 +158,10 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnParams p) {
 }
 
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st) {
-    if (attn_prefill_supported(p)) return launch_attn_prefill(p, rows, st);
+    if (attn_prefill_supported(p)) {
+        static const bool fp32 = getenv("ROTOR_B200_ATTN_FP32") != nullptr;  // comparison aid: the FP32-pipe kernel
+        return fp32 ? launch_attn_prefill(p, rows, st) : launch_attn_prefill_tc(p, rows, st);
+    }
     dim3 grid(p.n_heads, rows);
     switch (p.head_dim) {
         case 32: attention_kernel<1><<<grid, 128, 0, st>>>(p); break;
@@ -308,7 +312,8 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    return configure_attn_prefill();
+    int rc = configure_attn_prefill();
+    return rc ? rc : configure_attn_prefill_tc();
 }
 
 }  // namespace rb

@@ -156,6 +156,8 @@ int launch_attention(const AttnParams& p, int rows, cudaStream_t st);
 bool attn_prefill_supported(const AttnParams& p);
 int launch_attn_prefill(const AttnParams& p, int rows, cudaStream_t st);
 int configure_attn_prefill();
+int launch_attn_prefill_tc(const AttnParams& p, int rows, cudaStream_t st);
+int configure_attn_prefill_tc();
 
 struct LmHeadParams {
     const __nv_bfloat16* embed;  // [vocab][d]
