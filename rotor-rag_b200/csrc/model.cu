@@ -1291,6 +1291,38 @@ int rotor_b200_ffn_forward(const rotor_b200_model_config* cfg, const rotor_b200_
     RB_REQUIRE(((uintptr_t)workspace & 255) == 0);
     Ctx c;
     cudaStream_t st = as_stream(stream);
+    {
+        // a few token rows: two launches, the vector stages ride in the products' prologues
+        RB_TRY(block_derive(c, cfg));
+        static const bool off = getenv("ROTOR_B200_NO_FUSED_STEP") != nullptr;
+        if (!off && rows <= FUSED_MAX_ROWS && c.terms <= 3 && rows * c.terms <= 8 && c.ff % 16 == 0 &&
+            fused_gemv_supported(c.ff, c.d, rows, c.terms, 2, 0) && fused_gemv_supported(c.d, c.ff, rows, c.terms, 1, 0)) {
+            Carve cv{(unsigned char*)workspace, 0};
+            carve_ctx(c, cv, (size_t)rows);
+            if (cv.off > workspace_bytes) return ROTOR_B200_ERR_WORKSPACE;
+            static bool configured = false;
+            if (!configured) {
+                RB_TRY(configure_fused_gemv());
+                configured = true;
+            }
+            LeanStage ls = {};
+            ls.mode = LM_PLAIN;
+            ls.n = c.d;
+            ls.y = x;
+            ls.norm1 = pre_norm;
+            ls.eps = c.eps;
+            ls.terms = c.terms;
+            ls.kpad = (int)kpad_of(c.d);
+            const float sgu[3] = {layer->gate_scale, layer->up_scale, 0.f};
+            RB_TRY(launch_fused_gemv(layer->gate_up_tiles, c.ff, c.d, 2, rows, ls, c.fy[2], sgu, 0, 0, c.ffn_act, st));
+            ls.n = c.ff;
+            ls.y = c.fy[2];
+            ls.norm1 = layer->ffn_sub_norm;
+            ls.kpad = (int)kpad_of(c.ff);
+            const float sd[3] = {layer->down_scale, layer->down_scale, layer->down_scale};
+            return launch_fused_gemv(layer->down_tiles, c.d, c.ff, 1, rows, ls, y, sd, c.d, c.d, 0, st);
+        }
+    }
     RB_TRY(block_ctx(c, cfg, rows, workspace, workspace_bytes, st));
     VecStageParams e = {};
     e.mode = VS_PLAIN;
