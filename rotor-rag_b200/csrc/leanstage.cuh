@@ -171,7 +171,8 @@ __device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[
 
 // Absmax int8 quantiser over the register row: term t of the row goes to xq + t*tstride
 // (shared memory, zero padded to kpad), its scale and sum to sx[t] / xsum[t] (shared).
-// Same results as quantize_row_from_smem.  Requires kpad <= 4 * LEAN_V * blockDim.x.
+// Same results as quantize_row_from_smem.  Requires kpad <= 4 * LEAN_V * blockDim.x; sx / xsum are
+// complete after the next CTA barrier.
 template <int LEAN_V>
 __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LEAN_V], float* scratch, int8_t* xq,
                                               size_t tstride, float* sx, int* xsum, int m = 0, bool writer = false,
@@ -181,6 +182,7 @@ __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LE
         float mx = 0.f;
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) mx = fmaxf(mx, amax4(v[j]));
+        if (threadIdx.x == 0) xsum[t] = 0;  // ordered before the atomics below by the reduction's barriers
         mx = block_max(mx, scratch);
         if (x && p.xi_max && t == 0) mx = xch_scalar(*x, p.xi_max - 1, m, mx, true, writer, scratch);
         const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
@@ -207,11 +209,11 @@ __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LE
                 *reinterpret_cast<int*>(xq + (size_t)t * tstride + (size_t)g * 4) = packed;
             }
         }
-        lsum = block_sum_i(lsum, reinterpret_cast<int*>(scratch));
-        if (threadIdx.x == 0) {
-            sx[t] = s;
-            xsum[t] = lsum;
-        }
+        // the sum of the quantised values is only read after the caller's barrier: warps add
+        // their shares with a shared-memory atomic instead of a second block-wide reduction
+        lsum = warp_sum_i(lsum);
+        if ((threadIdx.x & 31) == 0 && lsum) atomicAdd(&xsum[t], lsum);
+        if (threadIdx.x == 0) sx[t] = s;
     }
 }
 
