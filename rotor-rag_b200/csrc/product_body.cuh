@@ -243,37 +243,74 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         int slot = w0 / p.nkt, kt = w0 - slot * p.nkt;
         int pslot = (w0 + FG_U) / p.nkt, pkt = (w0 + FG_U) - pslot * p.nkt;
         const uint4* pptr = slot_ptr(pslot) + (size_t)pkt * 32;
-        for (int base = w0; base < w1; base += FG_U) {
-            // the following batch of weight tiles is requested before this one is multiplied
-            uint4 wn[FG_U];
-    #pragma unroll
-            for (int u = 0; u < FG_U; ++u)
-                if (base + FG_U + u < w1) {
-                    wn[u] = ld_stream_v4(pptr);
-                    pptr += 32;
-                    if (++pkt == p.nkt) {
-                        pkt = 0;
-                        pptr = slot_ptr(++pslot);
-                    }
+        int pnext = w0 + FG_U;  // index of the next tile to request
+        // Requests FG_U tiles starting at tile index pnext.  Whole batch inside one row tile and inside
+        // the warp's range: four loads at constant offsets, no per-tile checks.
+        auto request = [&](uint4 (&dst)[FG_U]) {
+            if (pnext + FG_U <= w1 && pkt + FG_U <= p.nkt) {
+#pragma unroll
+                for (int u = 0; u < FG_U; ++u) dst[u] = ld_stream_v4(pptr + 32 * u);
+                pptr += 32 * FG_U;
+                pkt += FG_U;
+                if (pkt == p.nkt) {
+                    pkt = 0;
+                    pptr = slot_ptr(++pslot);
                 }
-    #pragma unroll
-            for (int u = 0; u < FG_U; ++u) {
-                if (base + u < w1) {
-                    if (slot != cur) {  // warp-uniform
-                        if (cur >= 0) flush(cur);
-                        clear();
-                        cur = slot;
+            } else {
+#pragma unroll
+                for (int u = 0; u < FG_U; ++u)
+                    if (pnext + u < w1) {
+                        dst[u] = ld_stream_v4(pptr);
+                        pptr += 32;
+                        if (++pkt == p.nkt) {
+                            pkt = 0;
+                            pptr = slot_ptr(++pslot);
+                        }
                     }
-                    const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-                    tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, kt * TILE_K + 32 * t, g, p.cols, accm, accd);
-                    if (++kt == p.nkt) {
-                        kt = 0;
-                        ++slot;
+            }
+            pnext += FG_U;
+        };
+        // Multiplies FG_U tiles starting at tile index `base`.
+        auto multiply = [&](const uint4 (&src)[FG_U], int base) {
+            if (base + FG_U <= w1 && kt + FG_U <= p.nkt && slot == cur) {
+#pragma unroll
+                for (int u = 0; u < FG_U; ++u) {
+                    const uint32_t pw[4] = {src[u].x, src[u].y, src[u].z, src[u].w};
+                    tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, (kt + u) * TILE_K + 32 * t, g, p.cols, accm, accd);
+                }
+                kt += FG_U;
+                if (kt == p.nkt) {
+                    kt = 0;
+                    ++slot;
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < FG_U; ++u) {
+                    if (base + u < w1) {
+                        if (slot != cur) {  // warp-uniform
+                            if (cur >= 0) flush(cur);
+                            clear();
+                            cur = slot;
+                        }
+                        const uint32_t pw[4] = {src[u].x, src[u].y, src[u].z, src[u].w};
+                        tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, kt * TILE_K + 32 * t, g, p.cols, accm, accd);
+                        if (++kt == p.nkt) {
+                            kt = 0;
+                            ++slot;
+                        }
                     }
                 }
             }
-    #pragma unroll
-            for (int u = 0; u < FG_U; ++u) wv[u] = wn[u];
+        };
+        // two register sets alternate: one is multiplied while the other is in flight
+        uint4 wn[FG_U];
+        for (int base = w0; base < w1; base += 2 * FG_U) {
+            request(wn);
+            multiply(wv, base);
+            if (base + FG_U < w1) {
+                request(wv);
+                multiply(wn, base + FG_U);
+            }
         }
     } else {
         for (int base = w0; base < w1; base += FG_U) {

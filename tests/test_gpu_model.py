@@ -89,6 +89,36 @@ def test_ffn_block_config2(rb, golden_dir, mode):
         assert rel_err(y_api, want) < TOL
 
 
+@pytest.mark.parametrize("rows", [1, 2, 3])
+def test_ffn_large_matrix_variants(rb, rows):
+    """An FFN big enough (2048 -> 2 x 20480 -> 2048) that the generation-step products take their
+    large-matrix variants: the pipelined tile loop (eight or more weight tiles per warp) and, for the
+    20480-wide input of the down projection, the shared-memory prologue.  One, two and three rows
+    select the one-column DP4A, two-column DP4A and tensor-core tile products."""
+    import torch
+    from rotor_b200 import ops
+    d, ff = 2048, 20480
+    rng = np.random.default_rng(1000 + rows)
+    lw = {"gate": (O.synth_ternary(rng, ff, d), 0.017), "up": (O.synth_ternary(rng, ff, d), 0.015),
+          "down": (O.synth_ternary(rng, d, ff), 0.016),
+          "ffn_sub_norm": (1.0 + 0.1 * rng.standard_normal(ff)).astype(np.float32)}
+    pre_w = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    x = rng.standard_normal((rows, d)).astype(np.float32)
+    sem = rb.sem.BASELINE
+    ffn = rb.tr.GatedFFN(d, ff, semantics=sem)
+    pre = rb.tr.RMSNorm(d, eps=sem.eps)
+    pre.weight = pre_w
+    ffn.ffn_norm.weight = lw["ffn_sub_norm"]
+    for nm, proj in (("gate", ffn.gate_proj), ("up", ffn.up_proj), ("down", ffn.down_proj)):
+        proj.load_from_int8(lw[nm][0], lw[nm][1])
+    before = rb.tr.abi.lib.rotor_b200_launch_count()
+    got = ffn.forward_device(ops.to_device(x, torch.float32), pre_norm=pre).cpu().numpy()
+    assert rb.tr.abi.lib.rotor_b200_launch_count() - before == 2     # the fused two-launch route
+    want = O.ffn(O.rmsnorm(x, pre_w, sem.eps), lw, o_sem(sem))
+    assert rel_err(got, want) < TOL, rel_err(got, want)
+    rb.tr.abi.device_status()
+
+
 def _tiny(rb, name, sem, **kw):
     om, prompt = G.tiny_model(name)
     kw.setdefault("max_seq", 64)
