@@ -414,6 +414,40 @@ def run_prefill(args, rank, world):
         "gpu_launches": int(launches), "clocks": clocks}), flush=True)
 
 
+def cpu_layer_samples():
+    """The reference's CPU path (NumPy port in oracle/) on this box's host cores for the single layer of
+    config 1 and the FFN block of config 2: median of 10 calls after 2 warm-up calls."""
+    import numpy as np
+    from oracle import bitlinear_np as O
+    rng = np.random.default_rng(11)
+    d, ff = 2560, 6912
+    lw = {"gate": (O.synth_ternary(rng, ff, d), 0.016), "up": (O.synth_ternary(rng, ff, d), 0.016),
+          "down": (O.synth_ternary(rng, d, ff), 0.016), "ffn_sub_norm": np.ones(ff, np.float32)}
+    pre = np.ones(d, np.float32)
+
+    def med(fn):
+        ts = []
+        for i in range(12):
+            t0 = time.perf_counter()
+            fn()
+            if i >= 2:
+                ts.append(time.perf_counter() - t0)
+        return statistics.median(ts) * 1e6
+    out = {}
+    x1 = rng.standard_normal((1, d)).astype(np.float32)
+    out["bitlinear_2560x6912_m1_us"] = med(lambda: O.bitlinear(x1, lw["gate"][0], lw["gate"][1], O.REFERENCE))
+    for m in (1, 16):
+        x = rng.standard_normal((m, d)).astype(np.float32)
+        out[f"ffn_block_m{m}_us"] = med(lambda: O.ffn(O.rmsnorm(x, pre, 1e-5), lw, O.REFERENCE))
+    try:
+        from threadpoolctl import threadpool_info
+        out["cores"] = max([p.get("num_threads", 1) for p in threadpool_info()] or [os.cpu_count() or 1])
+    except Exception:
+        out["cores"] = os.cpu_count() or 1
+    out["kind"] = "port"
+    return out
+
+
 def run_ffn_block(args):
     """Config 2: the 2B-shape FFN block (pre-norm, gate/up BitLinear 2560 -> 6912, squared-ReLU gating,
     sub-norm over 6912, down BitLinear 6912 -> 2560) for 1 and 16 token rows.  64 blocks with distinct
@@ -459,6 +493,8 @@ def run_ffn_block(args):
         out["rows"][str(m)] = {"us_per_block": us, "algorithmic_bytes": alg, "achieved_gbs": alg / us / 1e3,
                                "frac_of_peak": alg / us / 1e3 / peak}
     out["peak_kind"] = peak_kind
+    if not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_layer_samples()
     print(json.dumps(out), flush=True)
 
 
