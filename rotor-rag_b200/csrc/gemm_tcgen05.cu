@@ -83,6 +83,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     const uint32_t ring = (smem_u32(t5_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok0 = blockIdx.x * T5_TOK, rt0 = blockIdx.y * (T5_ROWS / TILE_ROWS);
+    const int nhalf = p.ncols - tok0 > 128 ? 2 : 1;  // token halves of this CTA that hold any token
     volatile int* abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
@@ -165,7 +166,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row0 = rt0 * TILE_ROWS;
 #pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
+            for (int half = 0; half < nhalf; ++half) {
                 const int token = tok0 + half * 128 + warp * 32 + lane;
 #pragma unroll 1
                 for (int ch = 0; ch < T5_ROWS / 32; ++ch) {
@@ -206,10 +207,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                 const int s = kt % T5_STAGES;
                 if (!t5_wait(smem_u32(&s_empty[s]), ((kt / T5_STAGES) & 1) ^ 1, abort_flag, p.status, 0x7c000003u)) break;
                 const uint32_t bar = smem_u32(&s_full[s]);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(T5_A_BYTES)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                             "r"(nhalf * (T5_A_BYTES / 2))
                              : "memory");
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
+                for (int half = 0; half < nhalf; ++half) {
                     const uint32_t dst = ring + s * T5_STAGE_BYTES + half * (T5_A_BYTES / 2);
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
@@ -231,8 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t abase = ring + s * T5_STAGE_BYTES, bbase = abase + T5_A_BYTES;
-#pragma unroll
-                for (int half = 0; half < 2; ++half)
+                for (int half = 0; half < nhalf; ++half)
 #pragma unroll
                     for (int k4 = 0; k4 < TILE_K / 32; ++k4) {
                         const uint64_t da = t5_desc(abase + half * (T5_A_BYTES / 2) + k4 * 32);
@@ -279,10 +279,13 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 static EncodeTiledFn g_encode = nullptr;
 static bool g_tc5_ready = false;
 
-// Shapes this kernel takes: enough tokens to fill its tile, 16-byte aligned operands.
+// Shapes this kernel takes: enough tokens to be worth its tile, 16-byte aligned operands.
 bool gemm_tcgen05_supported(size_t out, size_t in, int ncols, const void* xq) {
     static const bool off = getenv("ROTOR_B200_NO_TCGEN05") != nullptr;  // measurement aid: legacy mma.sync path
-    return !off && ncols >= T5_TOK && out >= 16 && in >= 4 && ((uintptr_t)xq & 15) == 0;
+    // from 64 tokens on: with fewer than 256 the tile is partly empty, but the product is then bound by
+    // the weight stream, which this kernel moves faster than the mma.sync kernel does
+    static const int min_cols = getenv("ROTOR_B200_TCGEN05_MIN") ? atoi(getenv("ROTOR_B200_TCGEN05_MIN")) : 64;
+    return !off && ncols >= min_cols && out >= 16 && in >= 4 && ((uintptr_t)xq & 15) == 0;
 }
 
 int configure_gemm_tcgen05() {

@@ -77,9 +77,10 @@ def test_integer_accumulators_bit_exact(ops, abi, variant, shape):
 
 
 @pytest.mark.parametrize("shape", [(6912, 2560, 130), (2560, 6912, 257), (48, 1280, 32), (33, 260, 300), (640, 2560, 1024),
-                                   (400, 2560, 517), (3840, 384, 256), (272, 128, 700)])
+                                   (400, 2560, 517), (3840, 384, 256), (272, 128, 700), (2560, 2560, 64), (528, 640, 100),
+                                   (6912, 2560, 192)])
 def test_many_column_product_bit_exact(ops, abi, shape):
-    """Prefill-sized products: 32 to 255 activation columns take the mma.sync tiled GEMM, 256 and
+    """Prefill-sized products: 32 to 63 activation columns take the mma.sync tiled GEMM, 64 and
     more the tcgen05 kernel (TMA-fed token operand, weights decoded into shared memory, int32
     accumulators in tensor memory).  Ragged token counts, row counts that do not fill the
     256-row tile, and K that is not a multiple of the 128-wide weight tile."""
