@@ -80,11 +80,10 @@ def test_integer_accumulators_bit_exact(ops, abi, variant, shape):
                                    (400, 2560, 517), (3840, 384, 256), (272, 128, 700), (2560, 2560, 64), (528, 640, 100),
                                    (6912, 2560, 192)])
 def test_many_column_product_bit_exact(ops, abi, shape):
-    """Prefill-sized products (32 activation columns and more) take the tcgen05 kernel; the mma.sync tiled
-    GEMM remains behind ROTOR_B200_NO_TCGEN05.  Here: 32 and
-    more the tcgen05 kernel (TMA-fed token operand, weights decoded into shared memory, int32
-    accumulators in tensor memory).  Ragged token counts, row counts that do not fill the
-    256-row tile, and K that is not a multiple of the 128-wide weight tile."""
+    """Prefill-sized products (32 activation columns and more) take the tcgen05 kernel (TMA-fed token
+    operand, weights decoded into shared memory, int32 accumulators in tensor memory); the mma.sync
+    tiled GEMM remains behind ROTOR_B200_NO_TCGEN05.  Ragged token counts, row counts that do not fill
+    the 256-row tile, and K that is not a multiple of the 128-wide weight tile."""
     out, inn, ncols = shape
     rng = np.random.default_rng(out * 3 + inn + ncols)
     w = O.synth_ternary(rng, out, inn)
