@@ -247,6 +247,16 @@ int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void*
 int rotor_b200_model_read_tokens(void* handle, int first_step, int count, int64_t* tokens_host, void* stream);
 int rotor_b200_model_position(void* handle);
 
+/* ---------------------------------------------------------------- sampling
+ * TopKSampling.sample / TopPSampling.sample (src/rotor/generation.py:45-145) on the device: logits
+ * [rows][vocab] float32 (device) are divided by `temperature`; mode 0 keeps the top_k largest, mode 1
+ * the shortest probability-sorted prefix whose mass reaches top_p; one token per row is drawn from
+ * the softmax over what is kept and written to out[rows] (device).  The reference draws from NumPy's
+ * global generator; here the uniform of row r is SplitMix64 of (seed, counter + r) and the kept
+ * tokens are walked in vocabulary order: the reference's distribution, this library's own stream. */
+int rotor_b200_sample(const float* logits, int rows, int vocab, int mode, int top_k, float top_p,
+                      float temperature, uint64_t seed, uint64_t counter, int64_t* out, void* stream);
+
 /* ---------------------------------------------------------------- tensor parallel (new design)
  * The reference is single-device.  For models large enough to shard, BitLinear is split
  * Megatron-style over the GPUs of one box, one process per GPU: q/k/v, gate and up by output

@@ -101,6 +101,7 @@ _SIGNATURES.update({
     "rotor_b200_model_position": (_i, [_p]),
     "rotor_b200_block_workspace_bytes": (_sz, [_cfgp, _i]),
     "rotor_b200_set_pdl": (_i, [_i]),
+    "rotor_b200_sample": (_i, [_p, _i, _i, _i, _i, C.c_float, C.c_float, C.c_uint64, C.c_uint64, _p, _p]),
     "rotor_b200_tp_unique_id": (_i, [_p]),
     "rotor_b200_tp_init": (_i, [_i, _i, _p, C.POINTER(_p)]),
     "rotor_b200_tp_destroy": (None, [_p]),

@@ -191,6 +191,22 @@ class BitNetModel:
         caches = [KVCache(l.attention, past + seq, batch) for l in self.layers] if use_cache else None
         return out, caches
 
+    def forward_last_logits_device(self, input_ids, past_kv_cache=None):
+        """Like ``forward(..., use_cache=True, logits_positions='last')`` but the logits stay on the
+        device: returns (CUDA float32 [batch, vocab], caches)."""
+        torch = abi.require_cuda()
+        ids = np.asarray(input_ids)
+        if ids.ndim == 1:
+            ids = ids[None, :]
+        batch, seq = ids.shape
+        past = 0 if past_kv_cache is None else past_kv_cache[0].length
+        h = self._ensure_handle(batch, seq, past + seq)
+        ids_d = ops.to_device(ids.astype(np.int64))
+        logits = torch.empty((batch, self.vocab_size), dtype=torch.float32, device="cuda")
+        check(lib.rotor_b200_model_forward(h.h, ptr(ids_d), batch, seq, past, abi.LOGITS_LAST, ptr(logits), None,
+                                           abi.stream()), "model_forward")
+        return logits, [KVCache(l.attention, past + seq, batch) for l in self.layers]
+
     # -- device-resident greedy generation ---------------------------------------------------
     def greedy_chunks(self, prompt_ids, max_new_tokens: int, use_graph: bool = True, chunk: int = 0):
         """Generator over lists of new token ids.  The prompt is prefilled once; every later

@@ -4,9 +4,11 @@
 With a rotor_b200 BitNetModel, greedy generation with the cache stays on the device:
 the prompt is prefilled once, every later step is a replay of one CUDA graph whose
 greedy pick feeds the next step, and token ids come back to the host only to test for
-EOS and to feed the per-token callback.  Other strategies (or ``use_cache=False``)
-take logits of the last position back to the host each step and sample there with the
-reference's NumPy procedure.
+EOS and to feed the per-token callback.  Top-k / top-p strategies constructed with ``device=True`` keep the logits on the device as
+well and draw there (rotor_b200_sample: the reference's distribution from a seeded
+counter-based stream instead of NumPy's global generator); only the drawn token id comes
+back.  Otherwise (or with ``use_cache=False``) the logits of the last position go to the
+host each step and are sampled with the reference's NumPy procedure.
 """
 from __future__ import annotations
 
@@ -32,11 +34,32 @@ def _softmax(x: np.ndarray) -> np.ndarray:
     return e / np.sum(e)
 
 
-class TopKSampling(SamplingStrategy):
-    """Sample among the k largest logits (reference :45-88)."""
+class _DeviceDraw:
+    """Device-side draw shared by the top-k / top-p strategies (``device=True``)."""
+    mode = 0
+    k, p = 50, 0.9
 
-    def __init__(self, k: int = 50):
+    def _init_device(self, device, seed):
+        self.device = bool(device)
+        self.seed = int(np.random.randint(0, 2 ** 31 - 1)) if seed is None else int(seed)
+        self.counter = 0
+
+    def sample_device(self, logits, temperature: float = 1.0):
+        """logits: CUDA float32 [rows, vocab]; returns a CUDA int64 tensor [rows] and advances the stream."""
+        from . import ops
+        out = ops.sample(logits, self.mode, top_k=self.k, top_p=self.p, temperature=temperature, seed=self.seed,
+                         counter=self.counter)
+        self.counter += logits.shape[0]
+        return out
+
+
+class TopKSampling(SamplingStrategy, _DeviceDraw):
+    """Sample among the k largest logits (reference :45-88).  ``device=True``: draw on the GPU."""
+    mode = 0
+
+    def __init__(self, k: int = 50, *, device: bool = False, seed: Optional[int] = None):
         self.k = k
+        self._init_device(device, seed)
 
     def sample(self, logits: np.ndarray, temperature: float = 1.0) -> int:
         if temperature != 1.0:
@@ -46,11 +69,14 @@ class TopKSampling(SamplingStrategy):
         return int(top[np.random.choice(len(top), p=probs)])
 
 
-class TopPSampling(SamplingStrategy):
-    """Sample from the smallest set whose probability mass reaches p (reference :91-145)."""
+class TopPSampling(SamplingStrategy, _DeviceDraw):
+    """Sample from the smallest set whose probability mass reaches p (reference :91-145).
+    ``device=True``: draw on the GPU."""
+    mode = 1
 
-    def __init__(self, p: float = 0.9):
+    def __init__(self, p: float = 0.9, *, device: bool = False, seed: Optional[int] = None):
         self.p = p
+        self._init_device(device, seed)
 
     def sample(self, logits: np.ndarray, temperature: float = 1.0) -> int:
         if temperature != 1.0:
@@ -109,6 +135,18 @@ class TextGenerator:
             return
         self.kv_cache = None
         seq = list(ids)
+        if self.use_cache and getattr(self.sampling_strategy, "device", False) and \
+                hasattr(self.model, "forward_last_logits_device"):
+            # logits stay on the device; one token id per step comes back
+            for step in range(n):
+                feed = np.asarray(seq if step == 0 else seq[-1:], dtype=np.int64).reshape(1, -1)
+                logits, self.kv_cache = self.model.forward_last_logits_device(feed, self.kv_cache)
+                tok = int(self.sampling_strategy.sample_device(logits, temperature).cpu()[0])
+                if stop_on_eos and eos is not None and tok == eos:
+                    return
+                seq.append(tok)
+                yield tok
+            return
         for step in range(n):
             logits = self._get_next_token_logits(np.asarray(seq, dtype=np.int64), is_first_step=(step == 0))
             tok = self.sampling_strategy.sample(logits, temperature)

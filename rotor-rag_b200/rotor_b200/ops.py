@@ -147,3 +147,14 @@ def bitlinear_forward(tiles, out, inn, x, terms, wscale=1.0, wscale_vec=None, va
                                            ptr(wscale_vec), ptr(y), ptr(workspace), workspace.numel(),
                                            variant, abi.stream()), "bitlinear_forward")
     return y
+
+
+def sample(logits, mode, top_k=50, top_p=0.9, temperature=1.0, seed=0, counter=0):
+    """One token per row of CUDA float32 logits [rows, vocab]; mode 0 top-k, 1 top-p.  Returns a CUDA int64 [rows]."""
+    torch = _torch()
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int64, device="cuda")
+    abi.check(abi.lib.rotor_b200_sample(abi.ptr(logits), rows, vocab, int(mode), int(top_k), float(top_p),
+                                        float(temperature), int(seed) & (2 ** 64 - 1), int(counter) & (2 ** 64 - 1),
+                                        abi.ptr(out), abi.stream()), "sample")
+    return out

@@ -216,6 +216,39 @@ def main():
         report.append(f"model {name}: oracle logits within 1e-9, greedy ids identical "
                       f"({G.N_NEW} tokens, min top-2 margin {margin.min():.2e} of RMS)")
 
+    # --- sampling: the set the reference's strategies draw from and its probabilities, read off the
+    # reference's own code by standing in for np.random.choice (generation.py:78-80, 135-137)
+    from oracle import sampling_np as S
+    logits = G.sampling_logits()
+    fx = {}
+    for ci, (mode, k, p, temp) in enumerate(G.SAMPLING_CASES):
+        strat = gen.TopKSampling(k) if mode == 0 else gen.TopPSampling(p)
+        seen = {}
+        real_choice = np.random.choice
+        try:
+            state = {"j": 0}
+
+            def fake_choice(n, p=None):
+                seen["n"], seen["p"] = n, np.array(p, dtype=np.float64)
+                return state["j"]
+            np.random.choice = fake_choice
+            strat.sample(logits.copy(), temp)
+            toks = []
+            for j in range(seen["n"]):
+                state["j"] = j
+                toks.append(strat.sample(logits.copy(), temp))
+        finally:
+            np.random.choice = real_choice
+        toks = np.asarray(toks, dtype=np.int64)
+        order = np.argsort(toks)
+        ref_idx, ref_p = toks[order], seen["p"][order]
+        idx, pr = S.kept_set(logits, mode, k, p, temp)
+        assert np.array_equal(idx, ref_idx), (ci, len(idx), len(ref_idx))
+        assert np.max(np.abs(pr - ref_p)) < 1e-6
+        fx[f"idx{ci}"], fx[f"p{ci}"] = ref_idx, ref_p
+    np.savez_compressed(os.path.join(HERE, "sampling.npz"), **fx)
+    report.append(f"sampling: kept sets and probabilities of {len(G.SAMPLING_CASES)} top-k / top-p cases identical")
+
     print("\n".join(report))
 
 

@@ -91,3 +91,15 @@ def tiny_model(name):
     rng = np.random.default_rng(spec["seed"] + 1)
     prompt = rng.integers(0, spec["cfg"]["vocab_size"], size=spec["prompt_len"]).astype(np.int64)
     return om, prompt
+
+
+# sampling: seeded logits with a peaked head and a long tail; (mode, k, p, temperature) cases
+SAMPLING_CASES = [(0, 10, 0.0, 1.0), (0, 50, 0.0, 0.7), (0, 1, 0.0, 1.0), (1, 0, 0.9, 1.0), (1, 0, 0.5, 0.6),
+                  (1, 0, 0.999, 1.3)]
+
+
+def sampling_logits(vocab=2000, seed=99):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(vocab).astype(np.float32) * np.float32(1.5)
+    x[rng.integers(0, vocab, size=12)] += np.float32(4.0)
+    return x

@@ -1,0 +1,87 @@
+"""GPU: device-side top-k / top-p sampling (rotor_b200_sample) against the reference's kept sets
+(fixture from the reference's own strategies) and against the oracle's statement of the draw."""
+import os
+
+import numpy as np
+import pytest
+
+import golden_inputs as G
+from oracle import sampling_np as S
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from rotor_b200 import ops
+    return ops
+
+
+def _draws(ops, logits, mode, k, p, temp, seed, n):
+    """n draws for counters 0..n-1: the rows of one launch take counter + row."""
+    import torch
+    x = torch.from_numpy(np.tile(logits[None, :], (n, 1))).cuda()
+    return ops.sample(x, mode, top_k=max(k, 1), top_p=p if p > 0 else 0.9, temperature=temp, seed=seed,
+                      counter=0).cpu().numpy()
+
+
+def test_draws_stay_in_the_reference_set_and_follow_the_oracle(ops, golden_dir):
+    z = np.load(os.path.join(golden_dir, "sampling.npz"))
+    logits = G.sampling_logits()
+    for ci, (mode, k, p, temp) in enumerate(G.SAMPLING_CASES):
+        got = _draws(ops, logits, mode, k, p, temp, seed=1234 + ci, n=512)
+        kept = set(z[f"idx{ci}"].tolist())
+        assert set(got.tolist()) <= kept, (ci, sorted(set(got.tolist()) - kept))
+        want = np.array([S.sample(logits, mode, k, p, temp, seed=1234 + ci, counter=0, row=r) for r in range(512)])
+        # float32 sums on the device against float64 in the oracle can move a CDF boundary by an ulp
+        assert np.mean(got == want) >= 0.99, (ci, float(np.mean(got == want)))
+
+
+def test_distribution_matches_reference_probabilities(ops, golden_dir):
+    z = np.load(os.path.join(golden_dir, "sampling.npz"))
+    logits = G.sampling_logits()
+    for ci in (0, 4):   # top-k 10 at T = 1, top-p 0.5 at T = 0.6: small sets, every token drawn often
+        mode, k, p, temp = G.SAMPLING_CASES[ci]
+        n = 40000
+        got = _draws(ops, logits, mode, k, p, temp, seed=77, n=n)
+        idx, pr = z[f"idx{ci}"], z[f"p{ci}"]
+        freq = np.array([(got == t).mean() for t in idx])
+        sigma = np.sqrt(pr * (1 - pr) / n)
+        assert np.all(np.abs(freq - pr) < 5 * sigma + 1e-4), (ci, np.max(np.abs(freq - pr) / sigma))
+
+
+def test_edge_cases(ops):
+    import torch
+    logits = G.sampling_logits()
+    assert int(_draws(ops, logits, 0, 1, 0.0, 1.0, 3, 4)[0]) == int(np.argmax(logits))       # k = 1
+    flat = np.zeros(300, dtype=np.float32)                                                  # all ties
+    got = _draws(ops, flat, 0, 7, 0.0, 1.0, 9, 2000)
+    assert set(got.tolist()) == set(range(7))          # ties admitted in vocabulary order
+    got = _draws(ops, flat, 1, 0, 0.25, 1.0, 9, 2000)
+    assert set(got.tolist()) == set(range(75))         # 75 of 300 equal tokens carry a quarter of the mass
+    full = _draws(ops, logits, 1, 0, 1.0, 1.0, 11, 3000)                                    # p = 1 keeps everything
+    assert len(set(full.tolist())) > 200
+    a = ops.sample(torch.from_numpy(logits[None, :]).cuda(), 1, top_p=0.9, seed=5, counter=17).cpu().numpy()
+    b = ops.sample(torch.from_numpy(logits[None, :]).cuda(), 1, top_p=0.9, seed=5, counter=17).cpu().numpy()
+    assert a[0] == b[0]
+
+
+def test_text_generator_device_sampling():
+    """TextGenerator with a device-side strategy: logits never leave the GPU; same seed, same text."""
+    from rotor_b200 import semantics
+    from rotor_b200.generation import TextGenerator, TopKSampling, TopPSampling
+    from rotor_b200.synth import PassThroughTokenizer, model_from_oracle_params
+    om, prompt = G.tiny_model("hd64")
+    model = model_from_oracle_params(om, semantics=semantics.REFERENCE, max_seq=64)
+    text = " ".join(map(str, prompt))
+    outs = []
+    for _ in range(2):
+        gen = TextGenerator(model, PassThroughTokenizer(), sampling_strategy=TopPSampling(0.9, device=True, seed=42),
+                            temperature=0.8, max_length=40)
+        outs.append(gen.generate(text, max_new_tokens=12, stop_on_eos=False))
+    assert outs[0] == outs[1] and len(outs[0].split()) == len(prompt) + 12
+    gen = TextGenerator(model, PassThroughTokenizer(), sampling_strategy=TopKSampling(1, device=True, seed=1),
+                        max_length=40)
+    greedy = TextGenerator(model, PassThroughTokenizer(), max_length=40)
+    assert gen.generate(text, max_new_tokens=8, stop_on_eos=False) == greedy.generate(text, max_new_tokens=8,
+                                                                                     stop_on_eos=False)

@@ -194,3 +194,20 @@ def test_oracle_against_live_reference(tmp_path):
     out = subprocess.run(["python", os.path.join(ROOT, "tests", "golden", "make_golden.py"), "--check-only"],
                          env=env, capture_output=True, text=True)
     assert out.returncode == 0, out.stdout + out.stderr
+
+
+def test_sampling_kept_sets_match_reference_fixture(golden_dir):
+    """Top-k / top-p: the set the reference's strategies draw from and its probabilities
+    (fixture taken from the reference's own code with np.random.choice stood in for)."""
+    from oracle import sampling_np as S
+    z = np.load(os.path.join(golden_dir, "sampling.npz"))
+    logits = G.sampling_logits()
+    for ci, (mode, k, p, temp) in enumerate(G.SAMPLING_CASES):
+        idx, pr = S.kept_set(logits, mode, k, p, temp)
+        assert np.array_equal(idx, z[f"idx{ci}"])
+        assert np.max(np.abs(pr - z[f"p{ci}"])) < 1e-6
+    # the draw: deterministic in (seed, counter), inside the kept set, k = 1 is the argmax
+    assert S.sample(logits, 0, top_k=1) == int(np.argmax(logits))
+    a = [S.sample(logits, 1, top_p=0.9, seed=5, counter=c) for c in range(50)]
+    assert a == [S.sample(logits, 1, top_p=0.9, seed=5, counter=c) for c in range(50)]
+    assert set(a) <= set(S.kept_set(logits, 1, top_p=0.9)[0].tolist()) and len(set(a)) > 5
