@@ -203,3 +203,30 @@ def test_errors_are_reported_not_swallowed(ops, abi):
     st = abi.lib.rotor_b200_bitlinear_forward(tiles.data_ptr(), 16, 128, x.data_ptr(), 1, 1, 1.0, None,
                                               y.data_ptr(), small.data_ptr(), 8, 0, None)
     assert st == 4   # workspace too small
+
+
+def test_mma_sync_gemm_kept_as_comparison_path():
+    """The mma.sync tiled GEMM (the pre-tcgen05 path) stays selectable with ROTOR_B200_NO_TCGEN05=1 and
+    stays bit-exact.  The switch is read once per process, hence the child process."""
+    import subprocess
+    import sys
+    code = r'''
+import sys, numpy as np
+sys.path[:0] = [%r, %r]
+from oracle import bitlinear_np as O
+from rotor_b200 import abi, ops
+rng = np.random.default_rng(4)
+for out, inn, ncols in ((640, 2560, 300), (6912, 384, 64)):
+    w = O.synth_ternary(rng, out, inn)
+    kpad = abi.lib.rotor_b200_in_padded(inn)
+    q = np.zeros((ncols, kpad), dtype=np.int8)
+    q[:, :inn] = rng.integers(-128, 128, size=(ncols, inn), dtype=np.int8)
+    acc = ops.bitlinear_acc(ops.int8_to_tiles(w), out, inn, ops.to_device(q),
+                            ops.to_device(q.astype(np.int32).sum(axis=1).astype(np.int32)), abi.VARIANT_AUTO).cpu().numpy()
+    assert np.array_equal(acc, q[:, :inn].astype(np.int32) @ w.astype(np.int32).T)
+print("ok")
+''' % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+       os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "rotor-rag_b200"))
+    env = dict(os.environ, ROTOR_B200_NO_TCGEN05="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-2000:]
