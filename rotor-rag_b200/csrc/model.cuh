@@ -56,6 +56,8 @@ struct VecStageParams {
 };
 
 int launch_vec_stage(const VecStageParams& p, int rows, cudaStream_t st);
+bool row_stage_supported(const VecStageParams& p, int rows);
+int launch_row_stage(const VecStageParams& p, int rows, cudaStream_t st);
 int configure_vec_stage();
 int configure_gemv_kernels();
 int configure_lmhead();

@@ -1,0 +1,194 @@
+// Vector stages for many token rows (prompt prefill): the stages of vecstage.cuh with the row
+// held in registers.
+//
+// With thousands of rows the stages are pure HBM traffic (int32 accumulators in, residual stream
+// in and out, int8 activations out); what matters is bytes in flight.  One CTA of 128 threads
+// per row; a thread owns up to V groups of four consecutive elements and issues ALL of its
+// 128-bit loads (accumulators of every term, residual stream, norm weights) before the first
+// use.  The row never visits shared memory: sums of squares and absolute maxima are
+// block reductions over register values, and the quantiser writes packed int8 words straight
+// to the activation buffer (leanstage.cuh).  Arithmetic and its association follow
+// vec_stage_row, which this kernel replaces when there are at least RS_MIN_ROWS rows.
+#include <cstdlib>
+
+#include "leanstage.cuh"
+#include "model.cuh"
+
+namespace rb {
+
+constexpr int RS_THREADS = 128;
+constexpr int RS_MIN_ROWS = 64;
+
+__device__ __forceinline__ float4 rs_deq(const VecStageParams& p, size_t col0, int off, int g, const float (&sxv)[3],
+                                         float wscale) {
+    float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+    int4 a[3];
+#pragma unroll
+    for (int t = 0; t < 3; ++t)
+        if (t < p.terms)
+            a[t] = __ldcg(reinterpret_cast<const int4*>(p.acc.acc + (col0 + t) * p.acc.out + off) + g);
+#pragma unroll
+    for (int t = 0; t < 3; ++t)
+        if (t < p.terms) {
+            f.x += (float)a[t].x * sxv[t];
+            f.y += (float)a[t].y * sxv[t];
+            f.z += (float)a[t].z * sxv[t];
+            f.w += (float)a[t].w * sxv[t];
+        }
+    return make_float4(f.x * wscale, f.y * wscale, f.z * wscale, f.w * wscale);
+}
+
+__device__ __forceinline__ float rs_gate(float gate, float up, int act) {
+    if (act == ROTOR_B200_FFN_RELU2) {
+        const float q = fmaxf(gate, 0.f);
+        return q * q * up;
+    }
+    const float c = fminf(fmaxf(up, -20.f), 20.f);
+    return gate * (c / (1.f + expf(-c)));
+}
+
+// Wide rows (V > 8) are capped at 128 registers so that four CTAs share an SM: with fewer, the
+// reductions and the quantiser of one row leave the memory pipe idle.
+// RESID: the stage adds to the residual stream (VS_OPROJ, VS_DOWN) and keeps a second register
+// row for it; the other modes are compiled without it.
+template <int V, bool RESID>
+__global__ void __launch_bounds__(RS_THREADS, V > 8 ? 4 : 5) row_stage_kernel(const __grid_constant__ VecStageParams p) {
+    __shared__ float scratch[64];
+    const int m = blockIdx.x, n = p.n, n4 = n >> 2, tid = threadIdx.x;
+    const size_t ro = (size_t)m * n, col0 = (size_t)m * p.terms;
+    const bool from_acc = p.mode == VS_OPROJ || p.mode == VS_FFN || p.mode == VS_DOWN || p.mode == VS_DEQ;
+    float sxv[3] = {0.f, 0.f, 0.f};
+    if (from_acc)
+        for (int t = 0; t < p.terms; ++t) sxv[t] = __ldcg(&p.sx_in[col0 + t]);
+    float* hdst = p.h_out ? p.h_out : p.h;
+
+    // ---- build the row: every load of the stage in flight together
+    float4 v[V], aux[RESID ? V : 1];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int g = tid + j * RS_THREADS;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (RESID) aux[RESID ? j : 0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g >= n4) continue;
+        if (p.mode == VS_EMBED) {
+            const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.embed + (size_t)p.ids[m] * n) + g);
+            v[j] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                               __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+        } else if (p.mode == VS_PLAIN) {
+            v[j] = ldcg4(p.src + ro + 4 * g);
+        } else {
+            float4 a = rs_deq(p, col0, 0, g, sxv, p.wscale0);
+            if (p.mode == VS_FFN) {  // gating right away: the up half is not kept
+                const float4 b = rs_deq(p, col0, n, g, sxv, p.wscale1);
+                a = make_float4(rs_gate(a.x, b.x, p.ffn_act), rs_gate(a.y, b.y, p.ffn_act),
+                                rs_gate(a.z, b.z, p.ffn_act), rs_gate(a.w, b.w, p.ffn_act));
+            }
+            v[j] = a;
+            if (RESID) aux[RESID ? j : 0] = ldcg4(p.h + ro + 4 * g);
+        }
+    }
+    if constexpr (RESID) {
+        if (p.mode == VS_OPROJ) {  // h += subnorm(row)
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < V; ++j) ss += sq4(v[j]);
+            ss = block_sum(ss, scratch);
+            const float inv = 1.0f / sqrtf(ss / (float)n + p.eps);
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                const int g = tid + j * RS_THREADS;
+                const float4 w0 = g < n4 ? ldg4(p.norm0 + 4 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
+                // (multiply, multiply, add: no fused multiply-add, like the shared-memory version)
+                v[j].x = __fadd_rn(__fmul_rn(__fmul_rn(v[j].x, inv), w0.x), aux[j].x);
+                v[j].y = __fadd_rn(__fmul_rn(__fmul_rn(v[j].y, inv), w0.y), aux[j].y);
+                v[j].z = __fadd_rn(__fmul_rn(__fmul_rn(v[j].z, inv), w0.z), aux[j].z);
+                v[j].w = __fadd_rn(__fmul_rn(__fmul_rn(v[j].w, inv), w0.w), aux[j].w);
+            }
+        } else {  // VS_DOWN: residual add
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+                v[j] = make_float4(v[j].x + aux[j].x, v[j].y + aux[j].y, v[j].z + aux[j].z, v[j].w + aux[j].w);
+        }
+    }
+    if (p.mode == VS_OPROJ || p.mode == VS_DOWN || p.mode == VS_EMBED) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const int g = tid + j * RS_THREADS;
+            if (g < n4) *reinterpret_cast<float4*>(hdst + ro + 4 * g) = v[j];
+        }
+    }
+
+    // ---- pre-norm of the consumer (its weights are fetched as they are applied: they come from L2
+    // and holding them all would cost the registers that keep four rows per SM in flight)
+    if (p.norm1) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) ss += sq4(v[j]);
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)n + p.eps);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const int g = tid + j * RS_THREADS;
+            const float4 w = g < n4 ? ldg4(p.norm1 + 4 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[j].x = v[j].x * inv * w.x;
+            v[j].y = v[j].y * inv * w.y;
+            v[j].z = v[j].z * inv * w.z;
+            v[j].w = v[j].w * inv * w.w;
+        }
+    }
+    if (p.y_out) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const int g = tid + j * RS_THREADS;
+            if (g < n4) *reinterpret_cast<float4*>(p.y_out + ro + 4 * g) = v[j];
+        }
+    }
+    if (p.xq) {
+        LeanStage q = {};
+        q.n = n;
+        q.kpad = p.kpad;
+        q.terms = p.terms_out;
+        lean_quantize<V>(q, v, scratch, p.xq + (size_t)m * p.terms_out * p.kpad, (size_t)p.kpad,
+                         p.sx_out + (size_t)m * p.terms_out, p.xsum_out + (size_t)m * p.terms_out);
+    }
+}
+
+// Whether the register-resident kernel takes this stage: enough rows, complete accumulators in
+// one plane, 16-byte aligned rows, no sharded-row statistics.
+bool row_stage_supported(const VecStageParams& p, int rows) {
+    static const bool off = getenv("ROTOR_B200_NO_ROWSTAGE") != nullptr;  // comparison aid
+    if (off || rows < RS_MIN_ROWS) return false;
+    if (p.mode != VS_EMBED && p.mode != VS_PLAIN && p.mode != VS_OPROJ && p.mode != VS_FFN && p.mode != VS_DOWN &&
+        p.mode != VS_DEQ)
+        return false;
+    const bool from_acc = p.mode == VS_OPROJ || p.mode == VS_FFN || p.mode == VS_DOWN || p.mode == VS_DEQ;
+    if (from_acc && (p.acc.planes != 1 || p.acc.out % 4 || p.terms < 1 || p.terms > 3)) return false;
+    if (p.n % 4 || p.n > 4 * 16 * RS_THREADS) return false;
+    if (p.xq && (p.kpad > 4 * 16 * RS_THREADS || p.terms_out < 1 || p.terms_out > 4)) return false;
+    if (p.ext_sumsq || p.ext_absmax || p.out_sumsq || p.out_absmax) return false;
+    return true;
+}
+
+template <bool RESID>
+static void launch_row_stage_v(const VecStageParams& p, int rows, int v, cudaStream_t st) {
+    if (v <= 5)
+        row_stage_kernel<5, RESID><<<rows, RS_THREADS, 0, st>>>(p);
+    else if (v <= 8)
+        row_stage_kernel<8, RESID><<<rows, RS_THREADS, 0, st>>>(p);
+    else if (v <= 14)
+        row_stage_kernel<14, RESID><<<rows, RS_THREADS, 0, st>>>(p);
+    else
+        row_stage_kernel<16, RESID><<<rows, RS_THREADS, 0, st>>>(p);
+}
+
+int launch_row_stage(const VecStageParams& p, int rows, cudaStream_t st) {
+    const int width = p.xq && p.kpad > p.n ? p.kpad : p.n;   // the quantiser also writes the zero padding
+    const int v = (width / 4 + RS_THREADS - 1) / RS_THREADS;
+    if (p.mode == VS_OPROJ || p.mode == VS_DOWN)
+        launch_row_stage_v<true>(p, rows, v, st);
+    else
+        launch_row_stage_v<false>(p, rows, v, st);
+    return launch_status();
+}
+
+}  // namespace rb

@@ -26,6 +26,7 @@ int configure_vec_stage() {
 }
 
 int launch_vec_stage(const VecStageParams& p, int rows, cudaStream_t st) {
+    if (row_stage_supported(p, rows)) return launch_row_stage(p, rows, st);  // many rows: register-resident kernel
     const size_t smem = 64 * 4 + (size_t)p.n * 4;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
