@@ -12,7 +12,8 @@
 //
 // CTA: 256 threads = 8 warps, 128 query rows of one KV head (128/G positions x G heads of
 // the group); warp w owns rows 16w..16w+15.  Keys are walked 64 at a time.  Q (scaled), K and
-// V tiles are converted to hi/lo bf16 on their way into shared memory; rows are 16-byte-chunk
+// V tiles are converted to hi/lo bf16 on their way into shared memory (K and V through a
+// float32 landing area filled by cp.async during the previous tile's MMAs); rows are 16-byte-chunk
 // swizzled (chunk ^= row & 7) so that every ldmatrix phase reads eight distinct bank groups.
 // S accumulators become the A operand of the second product in registers (the m16n8k16
 // accumulator and A-fragment layouts coincide pairwise); the online-softmax row statistics
@@ -54,7 +55,8 @@ __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t&
 
 template <int D>
 size_t attn_prefill_tc_smem() {
-    return (size_t)(2 * TC_BM + 4 * TC_BN) * D * 2;  // Q hi/lo, K hi/lo, V hi/lo, bf16
+    return (size_t)(2 * TC_BM + 4 * TC_BN) * D * 2   // Q hi/lo, K hi/lo, V hi/lo, bf16
+           + (size_t)2 * TC_BN * D * 4;              // float32 landing area of the next K and V tile
 }
 
 // Converts `rows` x D floats (row r from src + r * src_stride, zero when !valid(r)) into the
@@ -87,6 +89,8 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const __grid_co
     const uint32_t qh = base, ql = qh + TC_BM * ROWB;
     const uint32_t kh = ql + TC_BM * ROWB, kl = kh + TC_BN * ROWB;
     const uint32_t vh = kl + TC_BN * ROWB, vl = vh + TC_BN * ROWB;
+    float* kst = reinterpret_cast<float*>(tc_smem + (size_t)(2 * TC_BM + 4 * TC_BN) * ROWB);  // [TC_BN][D] float32
+    float* vst = kst + TC_BN * D;
     const int G = p.n_heads / p.n_kv_heads, QT = TC_BM / G;
     const int qt = gridDim.x - 1 - blockIdx.x;  // late query tiles see the most keys: start them first
     const int hk = blockIdx.y, b = blockIdx.z;
@@ -125,16 +129,32 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const __grid_co
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
 
     const int ntiles = (t_all + TC_BN - 1) / TC_BN;
+    // The float32 rows of key tile kt travel to the landing area with cp.async (zero fill past the
+    // last key) while tile kt - 1 is being multiplied; the split into hi / lo bf16 then runs from
+    // shared memory.
+    auto request = [&](int kt) {
+        const int t0 = kt * TC_BN;
+        for (int idx = threadIdx.x; idx < TC_BN * (D / 4); idx += 256) {
+            const int r = idx / (D / 4), c4 = idx - r * (D / 4);
+            const bool valid = t0 + r < t_all;
+            const size_t off = (size_t)(valid ? t0 + r : 0) * D + 4 * c4;
+            const unsigned dk = (unsigned)__cvta_generic_to_shared(kst + r * D + 4 * c4);
+            const unsigned dv = (unsigned)__cvta_generic_to_shared(vst + r * D + 4 * c4);
+            const int sz = valid ? 16 : 0;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dk), "l"(kbase + off), "r"(sz) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dv), "l"(vbase + off), "r"(sz) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    request(0);
     for (int kt = 0; kt < ntiles; ++kt) {
         const int t0 = kt * TC_BN;
-        __syncthreads();  // the previous tile's K and V are no longer read
-        stage_split<D>(kh, kl, TC_BN, [&](int r) -> const float* {
-            return t0 + r < t_all ? kbase + (size_t)(t0 + r) * D : nullptr;
-        }, 1.0f);
-        stage_split<D>(vh, vl, TC_BN, [&](int r) -> const float* {
-            return t0 + r < t_all ? vbase + (size_t)(t0 + r) * D : nullptr;
-        }, 1.0f);
-        __syncthreads();
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // the landing area is complete; the previous tile's K and V are no longer read
+        stage_split<D>(kh, kl, TC_BN, [&](int r) -> const float* { return kst + r * D; }, 1.0f);
+        stage_split<D>(vh, vl, TC_BN, [&](int r) -> const float* { return vst + r * D; }, 1.0f);
+        __syncthreads();  // operands ready, landing area free
+        if (kt + 1 < ntiles) request(kt + 1);
 
         // ---- S = Q K^T: 16 rows x 64 keys per warp
         float sacc[TC_BN / 8][4];
