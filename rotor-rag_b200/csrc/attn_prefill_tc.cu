@@ -53,10 +53,39 @@ __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t&
     lo = (uint32_t)__bfloat16_as_ushort(xl) | ((uint32_t)__bfloat16_as_ushort(yl) << 16);
 }
 
+// Shared memory: Q hi/lo plus either one K/V operand set and a float32 landing area (in-kernel
+// split) or two operand sets (K/V already split in global memory): 192 KB for D = 128 both ways.
 template <int D>
 size_t attn_prefill_tc_smem() {
-    return (size_t)(2 * TC_BM + 4 * TC_BN) * D * 2   // Q hi/lo, K hi/lo, V hi/lo, bf16
-           + (size_t)2 * TC_BN * D * 4;              // float32 landing area of the next K and V tile
+    return (size_t)(2 * TC_BM + 4 * TC_BN) * D * 2 + (size_t)2 * TC_BN * D * 4;
+}
+
+// Splits the float32 K/V cache rows [0, past + seq) of `batch` sequences into hi / lo bf16 planes
+// (K hi, K lo, V hi, V lo; plane stride split_plane elements; same [batch][kv head][position][D]
+// indexing as the cache), once per attention call, so that the attention CTAs that share a key tile
+// do not each repeat the conversion.
+__global__ void __launch_bounds__(256) kv_split_kernel(const __grid_constant__ AttnParams p, int batch) {
+    const int D = p.head_dim, c4n = D / 4;
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    const size_t per_seq = (size_t)p.n_kv_heads * p.max_seq * c4n;
+    if (idx >= per_seq * batch) return;
+    const int c4 = (int)(idx % c4n);
+    const int t = (int)((idx / c4n) % p.max_seq);
+    int t_all = *p.past_len + p.seq;
+    if (t_all > p.max_seq) t_all = p.max_seq;
+    if (t >= t_all) return;
+    const size_t e = (idx / c4n) * D + 4 * c4;  // element offset: ((b * n_kv + hk) * max_seq + t) * D + 4 c4
+    const float4 k = *reinterpret_cast<const float4*>(p.k_cache + e);
+    const float4 v = *reinterpret_cast<const float4*>(p.v_cache + e);
+    uint2 kh, kl, vh, vl;
+    split2(k.x, k.y, kh.x, kl.x);
+    split2(k.z, k.w, kh.y, kl.y);
+    split2(v.x, v.y, vh.x, vl.x);
+    split2(v.z, v.w, vh.y, vl.y);
+    *reinterpret_cast<uint2*>(p.kv_split + e) = kh;
+    *reinterpret_cast<uint2*>(p.kv_split + p.split_plane + e) = kl;
+    *reinterpret_cast<uint2*>(p.kv_split + 2 * p.split_plane + e) = vh;
+    *reinterpret_cast<uint2*>(p.kv_split + 3 * p.split_plane + e) = vl;
 }
 
 // Converts `rows` x D floats (row r from src + r * src_stride, zero when !valid(r)) into the
@@ -79,7 +108,9 @@ __device__ __forceinline__ void stage_split(uint32_t hi, uint32_t lo, int rows, 
     }
 }
 
-template <int D>
+// PRE: K/V come pre-split from p.kv_split (kv_split_kernel) and are double buffered; otherwise they
+// are split here from the float32 cache through a landing area.
+template <int D, bool PRE>
 __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const __grid_constant__ AttnParams p) {
     constexpr int ROWB = D * 2;        // bytes per tile row
     constexpr int KS = D / 16;         // k steps of Q K^T
@@ -87,10 +118,11 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const __grid_co
     extern __shared__ __align__(128) unsigned char tc_smem[];
     const uint32_t base = (uint32_t)__cvta_generic_to_shared(tc_smem);
     const uint32_t qh = base, ql = qh + TC_BM * ROWB;
-    const uint32_t kh = ql + TC_BM * ROWB, kl = kh + TC_BN * ROWB;
-    const uint32_t vh = kl + TC_BN * ROWB, vl = vh + TC_BN * ROWB;
+    const uint32_t kv0 = ql + TC_BM * ROWB;            // operand set 0: K hi, K lo, V hi, V lo
+    constexpr uint32_t SETB = 4 * TC_BN * ROWB;        // bytes of one operand set
+    uint32_t kh = kv0, kl = kh + TC_BN * ROWB, vh = kl + TC_BN * ROWB, vl = vh + TC_BN * ROWB;
     float* kst = reinterpret_cast<float*>(tc_smem + (size_t)(2 * TC_BM + 4 * TC_BN) * ROWB);  // [TC_BN][D] float32
-    float* vst = kst + TC_BN * D;
+    float* vst = kst + TC_BN * D;                      // (PRE: this area is operand set 1 instead)
     const int G = p.n_heads / p.n_kv_heads, QT = TC_BM / G;
     const int qt = gridDim.x - 1 - blockIdx.x;  // late query tiles see the most keys: start them first
     const int hk = blockIdx.y, b = blockIdx.z;
@@ -134,15 +166,30 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const __grid_co
     // shared memory.
     auto request = [&](int kt) {
         const int t0 = kt * TC_BN;
-        for (int idx = threadIdx.x; idx < TC_BN * (D / 4); idx += 256) {
-            const int r = idx / (D / 4), c4 = idx - r * (D / 4);
-            const bool valid = t0 + r < t_all;
-            const size_t off = (size_t)(valid ? t0 + r : 0) * D + 4 * c4;
-            const unsigned dk = (unsigned)__cvta_generic_to_shared(kst + r * D + 4 * c4);
-            const unsigned dv = (unsigned)__cvta_generic_to_shared(vst + r * D + 4 * c4);
-            const int sz = valid ? 16 : 0;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dk), "l"(kbase + off), "r"(sz) : "memory");
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dv), "l"(vbase + off), "r"(sz) : "memory");
+        if constexpr (PRE) {
+            // four planes x 64 rows x (D / 8) 16-byte chunks, swizzled on the way in
+            constexpr int CH = D / 8;
+            const uint32_t set = kv0 + (uint32_t)(kt & 1) * SETB;
+            const size_t head = ((size_t)b * p.n_kv_heads + hk) * p.max_seq;
+            for (int idx = threadIdx.x; idx < 4 * TC_BN * CH; idx += 256) {
+                const int c = idx % CH, r = (idx / CH) % TC_BN, pl = idx / (CH * TC_BN);
+                const bool valid = t0 + r < t_all;
+                const __nv_bfloat16* src = p.kv_split + (size_t)pl * p.split_plane + (head + (valid ? t0 + r : 0)) * D + 8 * c;
+                const uint32_t dst = set + (uint32_t)pl * (TC_BN * ROWB) + (uint32_t)r * ROWB + (uint32_t)((c ^ (r & 7)) << 4);
+                const int sz = valid ? 16 : 0;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < TC_BN * (D / 4); idx += 256) {
+                const int r = idx / (D / 4), c4 = idx - r * (D / 4);
+                const bool valid = t0 + r < t_all;
+                const size_t off = (size_t)(valid ? t0 + r : 0) * D + 4 * c4;
+                const unsigned dk = (unsigned)__cvta_generic_to_shared(kst + r * D + 4 * c4);
+                const unsigned dv = (unsigned)__cvta_generic_to_shared(vst + r * D + 4 * c4);
+                const int sz = valid ? 16 : 0;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dk), "l"(kbase + off), "r"(sz) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dv), "l"(vbase + off), "r"(sz) : "memory");
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -150,11 +197,19 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const __grid_co
     for (int kt = 0; kt < ntiles; ++kt) {
         const int t0 = kt * TC_BN;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();  // the landing area is complete; the previous tile's K and V are no longer read
-        stage_split<D>(kh, kl, TC_BN, [&](int r) -> const float* { return kst + r * D; }, 1.0f);
-        stage_split<D>(vh, vl, TC_BN, [&](int r) -> const float* { return vst + r * D; }, 1.0f);
-        __syncthreads();  // operands ready, landing area free
-        if (kt + 1 < ntiles) request(kt + 1);
+        __syncthreads();  // tile kt has landed; every warp is done with tile kt - 1
+        if constexpr (PRE) {
+            kh = kv0 + (uint32_t)(kt & 1) * SETB;
+            kl = kh + TC_BN * ROWB;
+            vh = kl + TC_BN * ROWB;
+            vl = vh + TC_BN * ROWB;
+            if (kt + 1 < ntiles) request(kt + 1);  // into the other operand set, behind this tile's MMAs
+        } else {
+            stage_split<D>(kh, kl, TC_BN, [&](int r) -> const float* { return kst + r * D; }, 1.0f);
+            stage_split<D>(vh, vl, TC_BN, [&](int r) -> const float* { return vst + r * D; }, 1.0f);
+            __syncthreads();  // operands ready, landing area free
+            if (kt + 1 < ntiles) request(kt + 1);
+        }
 
         // ---- S = Q K^T: 16 rows x 64 keys per warp
         float sacc[TC_BN / 8][4];
@@ -257,9 +312,13 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const __grid_co
 }
 
 int configure_attn_prefill_tc() {
-    RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)attn_prefill_tc_smem<64>()));
-    RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)attn_prefill_tc_smem<128>()));
+    RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)attn_prefill_tc_smem<64>()));
+    RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)attn_prefill_tc_smem<128>()));
     return ROTOR_B200_OK;
 }
@@ -268,10 +327,21 @@ int launch_attn_prefill_tc(const AttnParams& p, int rows, cudaStream_t st) {
     const int G = p.n_heads / p.n_kv_heads, QT = TC_BM / G;
     const int batch = rows / p.seq;
     dim3 grid((p.seq + QT - 1) / QT, p.n_kv_heads, batch);
+    if (p.kv_split) {
+        const size_t n = (size_t)batch * p.n_kv_heads * p.max_seq * (p.head_dim / 4);
+        kv_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p, batch);
+        const int rc = launch_status();
+        if (rc) return rc;
+        if (p.head_dim == 64)
+            attn_prefill_tc_kernel<64, true><<<grid, 256, attn_prefill_tc_smem<64>(), st>>>(p);
+        else
+            attn_prefill_tc_kernel<128, true><<<grid, 256, attn_prefill_tc_smem<128>(), st>>>(p);
+        return launch_status();
+    }
     if (p.head_dim == 64)
-        attn_prefill_tc_kernel<64><<<grid, 256, attn_prefill_tc_smem<64>(), st>>>(p);
+        attn_prefill_tc_kernel<64, false><<<grid, 256, attn_prefill_tc_smem<64>(), st>>>(p);
     else
-        attn_prefill_tc_kernel<128><<<grid, 256, attn_prefill_tc_smem<128>(), st>>>(p);
+        attn_prefill_tc_kernel<128, false><<<grid, 256, attn_prefill_tc_smem<128>(), st>>>(p);
     return launch_status();
 }
 

@@ -41,6 +41,8 @@ struct Ctx {
     int* d_pos;
     float2* rope;        // cos/sin table, or null
     float2* rope_buf;    // storage for it
+    __nv_bfloat16* kvsplit;  // prefill attention: hi / lo bf16 planes of one layer's K/V rows (or null)
+    size_t kvsplit_plane;
     float* part_o;       // decode-attention partials
     float* part_m;
     float* part_l;
@@ -162,6 +164,8 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     c.part_m = cv.take<float>(heads);
     c.part_l = cv.take<float>(heads);
     c.counters = cv.take<unsigned>(8 + (size_t)c.max_batch);
+    c.kvsplit_plane = (size_t)c.max_batch * c.n_kv_heads * c.max_seq * c.head_dim;
+    c.kvsplit = rows >= 64 ? cv.take<__nv_bfloat16>(4 * c.kvsplit_plane) : nullptr;  // prompts long enough to tile
     c.stat[0] = cv.take<float>(rows);
     c.stat[1] = cv.take<float>(rows);
     c.gated = cv.take<float>(c.tp_size > 1 ? rows * ff : 1);
@@ -339,6 +343,8 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     ap.past_len = c.d_pos;
     ap.max_seq = c.max_seq;
     ap.causal = c.causal;
+    ap.kv_split = c.kvsplit;
+    ap.split_plane = c.kvsplit_plane;
     RB_TRY(launch_attention(ap, rows, st));
     VecStageParams qa = {};
     qa.mode = VS_PLAIN;
@@ -692,6 +698,8 @@ static int run_blocks_tp(Model& m, int l0, int l1, const float* next_norm, bool 
             ap.past_len = c.d_pos;
             ap.max_seq = c.max_seq;
             ap.causal = c.causal;
+            ap.kv_split = c.kvsplit;
+            ap.split_plane = c.kvsplit_plane;
             RB_TRY(launch_attention(ap, rows, st));
         }
         // o projection input: global absolute maximum, then quantise the local slice

@@ -153,6 +153,8 @@ struct AttnParams {
     const int* past_len;
     int max_seq;
     int causal;
+    __nv_bfloat16* kv_split;  // optional scratch: K hi, K lo, V hi, V lo planes of the cache rows in use
+    size_t split_plane;       // elements per plane (batch capacity * n_kv_heads * max_seq * head_dim)
 };
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st);
 bool attn_prefill_supported(const AttnParams& p);
