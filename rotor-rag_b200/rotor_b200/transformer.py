@@ -59,6 +59,8 @@ class RMSNorm:
     def forward(self, x: np.ndarray) -> np.ndarray:
         torch = abi.require_cuda()
         rows, lead = _as_rows(x)
+        if rows.shape[0] == 0:  # empty input: empty output, like the NumPy reference
+            return np.zeros((*lead, self.dim), dtype=np.float32)
         xd = ops.to_device(rows, torch.float32)
         y = torch.empty_like(xd)
         check(lib.rotor_b200_rmsnorm(ptr(xd), xd.shape[0], self.dim, ptr(self.device_weight()), float(self.eps),
@@ -154,6 +156,8 @@ class TernaryLinear:
         rows, lead = _as_rows(x)
         if rows.shape[1] != self.in_features:
             raise ValueError(f"input has {rows.shape[1]} features, expected {self.in_features}")
+        if rows.shape[0] == 0:  # empty input: empty output, like the NumPy reference
+            return np.zeros((*lead, self.out_features), dtype=np.float32)
         y = self.forward_device(ops.to_device(rows, torch.float32))
         return y.cpu().numpy().reshape(*lead, self.out_features)
 
@@ -352,6 +356,8 @@ class GatedFFN(_BlockBase):
     def forward(self, x: np.ndarray) -> np.ndarray:
         torch = abi.require_cuda()
         rows, lead = _as_rows(x)
+        if rows.shape[0] == 0:
+            return np.zeros((*lead, self.d_model), dtype=np.float32)
         y = self.forward_device(ops.to_device(rows, torch.float32))
         return y.cpu().numpy().reshape(*lead, self.d_model)
 

@@ -351,3 +351,21 @@ def test_wide_ffn_generation_step(rb):
     per_step = (rb.tr.abi.lib.rotor_b200_launch_count() - before) / G.N_NEW
     assert per_step <= 5 * om["cfg"]["n_layers"] + 2     # the five-launch block (the unfused path takes 8 per block)
     assert model.generate_greedy(prompt, G.N_NEW, use_graph=True) == ids
+
+
+def test_empty_and_single_element_inputs(rb):
+    """Zero token rows give empty outputs (the reference's NumPy path does the same); one row of one
+    sequence is the smallest real call."""
+    lin = rb.tr.TernaryLinear(64, 48)
+    lin.load_from_int8(np.ones((48, 64), dtype=np.int8), 0.5)
+    assert lin.forward(np.zeros((0, 64), dtype=np.float32)).shape == (0, 48)
+    assert lin.forward(np.zeros((2, 0, 64), dtype=np.float32)).shape == (2, 0, 48)
+    y = lin.forward(np.ones((1, 64), dtype=np.float32))
+    assert y.shape == (1, 48) and np.allclose(y, 32.0, rtol=1e-5)
+    norm = rb.tr.RMSNorm(64)
+    assert norm.forward(np.zeros((0, 64), dtype=np.float32)).shape == (0, 64)
+    ffn = rb.tr.GatedFFN(64, 128)
+    assert ffn.gate_proj.in_features == 64
+    for p in (ffn.gate_proj, ffn.up_proj, ffn.down_proj):
+        p.load_from_int8(np.ones((p.out_features, p.in_features), dtype=np.int8), 0.1)
+    assert ffn.forward(np.zeros((0, 64), dtype=np.float32)).shape == (0, 64)
