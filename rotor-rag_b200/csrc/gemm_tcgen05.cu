@@ -28,13 +28,19 @@
 namespace rb {
 
 constexpr int T5_TOK = 256;                        // tokens per CTA (two MMA M halves)
-constexpr int T5_ROWS = 256;                       // weight rows per CTA (MMA N)
 constexpr int T5_STAGES = 3;
 constexpr int T5_A_BYTES = T5_TOK * TILE_K;        // token operand per stage
-constexpr int T5_B_BYTES = T5_ROWS * TILE_K;       // weight operand per stage
-constexpr int T5_STAGE_BYTES = T5_A_BYTES + T5_B_BYTES;
 constexpr int T5_THREADS = 192;                    // warps 0-3 decode + epilogue, 4 TMA + TMEM, 5 MMA
-constexpr int T5_SMEM = T5_STAGES * T5_STAGE_BYTES + 1024;  // + slack to align the ring to 1024 bytes
+// Weight rows per CTA (MMA N) is a template argument: 256 for large grids; 64 when 256-row tiles
+// would leave most SMs without a CTA (few tokens and a narrow output, e.g. 64 tokens x 8192 rows).
+template <int ROWS>
+struct T5Cfg {
+    static constexpr int B_BYTES = ROWS * TILE_K;                  // weight operand per stage
+    static constexpr int STAGE_BYTES = T5_A_BYTES + B_BYTES;
+    static constexpr int SMEM = T5_STAGES * STAGE_BYTES + 1024;    // + slack to align the ring to 1024 bytes
+    static constexpr int TMEM_COLS = 2 * ROWS < 32 ? 32 : 2 * ROWS;  // two accumulators of ROWS columns
+    static constexpr int TILES_PER_WARP = ROWS / TILE_ROWS / 4;    // row tiles each decoder warp handles
+};
 constexpr long long T5_SPIN_CYCLES = 400000000LL;  // about 0.2 s
 
 struct Tc5Params {
@@ -74,8 +80,11 @@ __device__ __forceinline__ uint64_t t5_desc(uint32_t smem_addr) {
 // codes {0,1,2} in four bytes -> signed bytes {-1,0,+1}
 __device__ __forceinline__ uint32_t t5_s8(uint32_t codes) { return (codes + 0x7f7f7f7fu) ^ 0x80808080u; }
 
+template <int ROWS>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Tc5Params p) {
+    using Cfg = T5Cfg<ROWS>;
+    constexpr int T5_ROWS = ROWS, T5_STAGE_BYTES = Cfg::STAGE_BYTES, TPW = Cfg::TILES_PER_WARP;
     extern __shared__ unsigned char t5_raw[];
     __shared__ __align__(8) unsigned long long s_full[T5_STAGES], s_empty[T5_STAGES], s_accf;
     __shared__ uint32_t s_tmem;
@@ -95,9 +104,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_accf)), "r"(1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {  // the whole warp allocates all 512 tensor-memory columns (one CTA per SM)
+    if (warp == 4) {  // the whole warp allocates the accumulators' tensor-memory columns (one CTA per SM)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)),
-                     "r"(512));
+                     "r"(Cfg::TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -106,15 +115,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     const uint32_t tmem = s_tmem;
 
     if (warp < 4) {
-        // ---------------- weight decoders: warp w owns row tiles 4w .. 4w+3 of the CTA's 16
+        // ---------------- weight decoders: warp w owns row tiles TPW w .. TPW w + TPW - 1 of the CTA's
         const int g = lane >> 2, t = lane & 3;
         // weight tiles are requested two K steps ahead of their decode, so that the L2 / HBM latency
         // hides behind the decode of the step in between and the wait for a free stage
-        uint4 wv[2][4];
-        auto fetch = [&](int kt, uint4 (&dst)[4]) {
+        uint4 wv[2][TPW];
+        auto fetch = [&](int kt, uint4 (&dst)[TPW]) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int rt = rt0 + warp * 4 + u;
+            for (int u = 0; u < TPW; ++u) {
+                const int rt = rt0 + warp * TPW + u;
                 dst[u] = (rt < p.nrt && kt < p.nkt)
                              ? ld_stream_v4(p.tiles + ((size_t)rt * p.nkt + kt) * 32 + lane)
                              : make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
@@ -134,12 +143,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
             }
             const uint32_t bbase = ring + s * T5_STAGE_BYTES + T5_A_BYTES;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < TPW; ++u) {
                 const uint32_t pw[4] = {wv[par][u].x, wv[par][u].y, wv[par][u].z, wv[par][u].w};
 #pragma unroll
                 for (int rh = 0; rh < 2; ++rh) {
-                    // operand row R = 16 (4 warp + u) + g + 8 rh; R % 8 == g; K bytes [32 t, 32 t + 32)
-                    const uint32_t row = bbase + (uint32_t)((warp * 4 + u) * 2 + rh) * 1024u + (uint32_t)g * 128u;
+                    // operand row R = 16 (TPW warp + u) + g + 8 rh; R % 8 == g; K bytes [32 t, 32 t + 32)
+                    const uint32_t row = bbase + (uint32_t)((warp * TPW + u) * 2 + rh) * 1024u + (uint32_t)g * 128u;
                     const uint32_t lo = pw[rh], hi = pw[rh + 2];
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {  // 16-byte chunk 2 t + c holds bit pairs 2 c and 2 c + 1
@@ -171,7 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
 #pragma unroll 1
                 for (int ch = 0; ch < T5_ROWS / 32; ++ch) {
                     uint32_t v[32];
-                    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(half * 256 + ch * 32);
+                    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(half * ROWS + ch * 32);
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -243,7 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                             ".reg .pred p;\n\t"
                             "setp.ne.b32 p, %4, 0;\n\t"
                             "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
-                            "}\n" ::"r"(tmem + (uint32_t)(half * 256)),
+                            "}\n" ::"r"(tmem + (uint32_t)(half * ROWS)),
                             "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
                             : "memory");
                     }
@@ -269,7 +278,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     __syncthreads();
     if (warp == 4) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS));
     }
 }
 
@@ -295,7 +304,8 @@ int configure_gemm_tcgen05() {
     RB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
     if (!fn || q != cudaDriverEntryPointSuccess) return ROTOR_B200_ERR_CUDA;
     g_encode = (EncodeTiledFn)fn;
-    RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T5_SMEM));
+    RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<256>::SMEM));
+    RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<64>::SMEM));
     g_tc5_ready = true;
     return ROTOR_B200_OK;
 }
@@ -323,8 +333,21 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return ROTOR_B200_ERR_CUDA;
-    dim3 grid((ncols + T5_TOK - 1) / T5_TOK, (p.nrt * TILE_ROWS + T5_ROWS - 1) / T5_ROWS);
-    gemm_tcgen05_kernel<<<grid, T5_THREADS, T5_SMEM, st>>>(tmap, p);
+    const int tok_tiles = (ncols + T5_TOK - 1) / T5_TOK, rows = p.nrt * TILE_ROWS;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    if (tok_tiles * ((rows + 255) / 256) < sms) {  // 256-row tiles would leave SMs idle
+        dim3 grid(tok_tiles, (rows + 63) / 64);
+        gemm_tcgen05_kernel<64><<<grid, T5_THREADS, T5Cfg<64>::SMEM, st>>>(tmap, p);
+    } else {
+        dim3 grid(tok_tiles, (rows + 255) / 256);
+        gemm_tcgen05_kernel<256><<<grid, T5_THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);
+    }
     return launch_status();
 }
 

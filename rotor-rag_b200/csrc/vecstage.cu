@@ -27,7 +27,8 @@ int configure_vec_stage() {
 
 int launch_vec_stage(const VecStageParams& p, int rows, cudaStream_t st) {
     if (row_stage_supported(p, rows)) return launch_row_stage(p, rows, st);  // many rows: register-resident kernel
-    const size_t smem = 64 * 4 + (size_t)p.n * 4;
+    const size_t smem = 64 * 4 + (size_t)p.n * 4 +
+                        (p.mode == VS_ATTN ? 2 * (size_t)p.n_heads * p.nsplit * 4 : 0);  // merge weights behind the row
     static size_t configured = 48 * 1024;
     if (smem > configured) {
         if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;

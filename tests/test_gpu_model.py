@@ -369,3 +369,21 @@ def test_empty_and_single_element_inputs(rb):
     for p in (ffn.gate_proj, ffn.up_proj, ffn.down_proj):
         p.load_from_int8(np.ones((p.out_features, p.in_features), dtype=np.int8), 0.1)
     assert ffn.forward(np.zeros((0, 64), dtype=np.float32)).shape == (0, 64)
+
+
+@pytest.mark.parametrize("batch", [2, 9])
+def test_batched_decode_step(rb, batch):
+    """One-token steps for several sequences at once against the oracle run sequence by sequence.
+    Eight sequences and more merge the attention partials in a stage of their own."""
+    om, prompt, model = _tiny(rb, "hd128", rb.sem.REFERENCE, max_batch=batch)
+    rng = np.random.default_rng(40 + batch)
+    vocab = om["cfg"]["vocab_size"]
+    ids = rng.integers(0, vocab, size=(batch, 6))
+    nxt = rng.integers(0, vocab, size=(batch, 1))
+    _, caches = model.forward(ids, use_cache=True)
+    got, caches2 = model.forward(nxt, past_kv_cache=caches, use_cache=True)
+    assert caches2[0].length == 7
+    for b in range(batch):
+        _, oc = O.model_forward(om, ids[b:b + 1], O.REFERENCE, use_cache=True)
+        want, _ = O.model_forward(om, nxt[b:b + 1], O.REFERENCE, past_kv_cache=oc, use_cache=True)
+        assert rel_err(got[b], want[0]) < TOL, (b, rel_err(got[b], want[0]))
