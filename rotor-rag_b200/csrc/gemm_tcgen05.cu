@@ -2,14 +2,15 @@
 // acc[c][o] = sum_k xq[c][k] * w[o][k], exact int32, for hundreds to thousands of
 // activation columns c (tokens).
 //
-// CTA tile: 256 tokens x 256 weight rows, K walked 128 at a time through a 3-stage ring of
-// shared-memory operand tiles.  tcgen05.mma.kind::i8 (M = 128 tokens, N = 256 weight rows,
-// K = 32 per instruction) accumulates into tensor memory: two 128-lane x 256-column int32
-// accumulators, all 512 TMEM columns of the SM.  Per stage:
+// CTA tile: 256 tokens x 256 weight rows (64 weight rows when the larger tile would leave SMs
+// without work), K walked 128 at a time through a 3-stage ring of shared-memory operand tiles.
+// tcgen05.mma.kind::i8 (M = 128 tokens, N = 256 or 64 weight rows, K = 32 per instruction)
+// accumulates into tensor memory: two 128-lane int32 accumulators of N columns (with N = 256,
+// all 512 TMEM columns of the SM).  A token half without tokens is skipped.  Per stage:
 //   * the token operand (2 x 128 rows of 128 int8) arrives by TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past the last token zero filled),
-//   * four decoder warps turn 16 packed weight tiles (2 bits per weight, 8 KB) into 32 KB of
-//     signed int8 in the same swizzled K-major layout: a lane's 128-bit tile word holds, per
+//   * four decoder warps turn the stage's packed weight tiles (2 bits per weight; 16 tiles = 8 KB
+//     for N = 256) into signed int8 (32 KB) in the same swizzled K-major layout: a lane's 128-bit tile word holds, per
 //     row, 32 consecutive K positions, i.e. two 16-byte chunks of the operand row,
 //   * one thread issues the eight MMAs and commits them to the stage's "empty" barrier.
 // The weights are signed int8 (-1, 0, +1) in shared memory, so no code-offset correction is
