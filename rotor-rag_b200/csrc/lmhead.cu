@@ -93,6 +93,7 @@ static int launch_lm(const LmHeadParams& p, int row0, cudaStream_t st) {
 }
 
 int configure_lmhead() {
+    if (int rc = configure_lmhead_mma()) return rc;
     RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -111,6 +112,19 @@ int launch_lmhead(const LmHeadParams& pin, int rows, cudaStream_t st) {
         p.tail_counter = nullptr;
     }
     int rc = ROTOR_B200_OK;
+    if (p.xsplit && !p.pro_y && !fused && lmhead_mma_supported(rows, p.d)) {
+        // many rows: one pass over the table on the tensor cores
+        const bool pick = p.argmax_out != nullptr;
+        rc = launch_lmhead_mma(p.embed, p.x, p.xsplit, rows, p.vocab, p.d, p.logits, pick ? p.part_val : nullptr,
+                               p.part_idx, st);
+        if (rc) return rc;
+        if (pick) {
+            argmax_final_kernel<<<rows, 256, 0, st>>>(p.part_val, p.part_idx, lmhead_mma_parts(p.vocab), p.argmax_out,
+                                                      p.argmax_val);
+            rc = launch_status();
+        }
+        return rc;
+    }
     for (int r0 = 0; r0 < rows && !rc; r0 += LM_ROWS) {
         const int n = rows - r0 < LM_ROWS ? rows - r0 : LM_ROWS;
         switch (n) {

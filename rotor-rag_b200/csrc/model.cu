@@ -85,6 +85,7 @@ struct Model {
     int mega_batch;   // batch the plan is valid for (0 = none)
     int mega_ok;      // the device can run the step kernel for that plan
     // tensor parallel greedy pick: (value, global index) of every rank's best row
+    __nv_bfloat16* xsplit;  // LM head over more than four rows: hi / lo bf16 split of its input rows
     float* pick_val;      // [rows]
     long long* pick_idx;  // [rows]
     unsigned char* pick_send;  // [rows] x 12 bytes
@@ -190,8 +191,11 @@ static void carve(Model& m, unsigned char* base, size_t* total) {
     const size_t rows = (size_t)c.max_rows;
     Carve cv{base, 0};
     carve_ctx(m.c, cv, rows);
-    m.part_val = cv.take<float>(rows * lmhead_parts());
-    m.part_idx = cv.take<int>(rows * lmhead_parts());
+    const size_t nparts = (size_t)(lmhead_parts() > lmhead_mma_parts(c.vocab_size) ? lmhead_parts()
+                                                                                  : lmhead_mma_parts(c.vocab_size));
+    m.part_val = cv.take<float>(rows * nparts);
+    m.part_idx = cv.take<int>(rows * nparts);
+    m.xsplit = rows > 4 ? cv.take<__nv_bfloat16>(2 * rows * (size_t)c.d_model) : nullptr;
     m.cur_ids = cv.take<long long>(c.max_batch);
     m.max_log = c.max_seq;
     m.tok_log = cv.take<long long>((size_t)m.max_log * c.max_batch);
@@ -824,6 +828,7 @@ static int run_layers_tp(Model& m, const long long* ids, int batch, int seq, int
     LmHeadParams lp = {};
     lp.embed = m.embed + (size_t)rank * vl * d;
     lp.x = x;
+    lp.xsplit = m.xsplit;
     lp.vocab = vl;
     lp.d = d;
     lp.logits = logits_mode == ROTOR_B200_LOGITS_NONE ? nullptr : logits;
@@ -1012,6 +1017,7 @@ static int run_layers(Model& m, const long long* ids, int batch, int seq, int lo
     LmHeadParams lp = {};
     lp.embed = m.embed;
     lp.x = x;
+    lp.xsplit = m.xsplit;
     lp.vocab = m.cfg.vocab_size;
     lp.d = d;
     lp.logits = logits_mode == ROTOR_B200_LOGITS_NONE ? nullptr : logits;

@@ -183,7 +183,16 @@ struct LmHeadParams {
     const float* pro_h;
     const float* pro_norm;
     float pro_eps;
+    // more than four rows: scratch for the hi / lo bf16 split of x (2 * rows * d elements) lets the
+    // tensor-core kernel read the table once for up to 64 rows; part_* must then hold
+    // rows * max(nparts, lmhead_mma_parts(vocab)) entries
+    __nv_bfloat16* xsplit;
 };
+int lmhead_mma_parts(int vocab);
+bool lmhead_mma_supported(int rows, int d);
+int configure_lmhead_mma();
+int launch_lmhead_mma(const __nv_bfloat16* embed, const float* x, __nv_bfloat16* xsplit, int rows, int vocab, int d,
+                      float* logits, float* part_val, int* part_idx, cudaStream_t st);
 int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st);
 int lmhead_parts();
 
