@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnParams p) {
 }
 
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st) {
-    if (attn_prefill_supported(p)) {
+    if (attn_prefill_supported(p, rows)) {
         static const bool fp32 = getenv("ROTOR_B200_ATTN_FP32") != nullptr;  // comparison aid: the FP32-pipe kernel
         return fp32 ? launch_attn_prefill(p, rows, st) : launch_attn_prefill_tc(p, rows, st);
     }

@@ -197,10 +197,12 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const __grid_constant
 }
 
 // Whether the tiled kernel takes this shape (the per-query kernel covers the rest).
-bool attn_prefill_supported(const AttnParams& p) {
+bool attn_prefill_supported(const AttnParams& p, int rows) {
     if (p.head_dim != 64 && p.head_dim != 128) return false;
     const int G = p.n_heads / p.n_kv_heads;
-    return G >= 1 && G <= AP_BM && AP_BM % G == 0 && p.seq >= 16;
+    // long prompts, or many sequences with few new positions each (a CTA then serves one sequence's
+    // group of heads and streams that sequence's cache once)
+    return G >= 1 && G <= AP_BM && AP_BM % G == 0 && (p.seq >= 16 || rows >= 16);
 }
 
 int configure_attn_prefill() {

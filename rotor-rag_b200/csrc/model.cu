@@ -287,7 +287,9 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
     AccView va;
     RB_TRY(gemv(c, L.qkv_tiles, qkv_out, c.d, cols, 0, c.accA, &va, st));
-    if (seq == 1 && batch <= c.max_batch) {
+    // (sixteen and more sequences: the tiled attention kernel streams each sequence's cache once per
+    // group of heads, which beats thousands of small split CTAs; measured on the XL shape, batch 64)
+    if (seq == 1 && batch <= c.max_batch && batch < 16) {
         // generation step: dequantise, rotate, append to the cache, attend, merge and quantise in one launch
         AttnDecodeParams dp = {};
         dp.acc = va;
@@ -347,7 +349,7 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     ap.past_len = c.d_pos;
     ap.max_seq = c.max_seq;
     ap.causal = c.causal;
-    ap.kv_split = c.kvsplit;
+    ap.kv_split = seq >= 16 ? c.kvsplit : nullptr;  // a key tile shared by several query tiles is split once
     ap.split_plane = c.kvsplit_plane;
     RB_TRY(launch_attention(ap, rows, st));
     VecStageParams qa = {};
@@ -648,7 +650,7 @@ static int run_blocks_tp(Model& m, int l0, int l1, const float* next_norm, bool 
         AccView va, vb;
         // ---- attention on this rank's heads
         RB_TRY(acc1(c, L.qkv_tiles, qkv_out, d, cols, 0, c.accA, &va, st));
-        if (seq == 1 && batch <= c.max_batch) {
+        if (seq == 1 && batch <= c.max_batch && batch < 16) {
             AttnDecodeParams dp = {};
             dp.acc = va;
             dp.sx = c.sx[0];
@@ -702,7 +704,7 @@ static int run_blocks_tp(Model& m, int l0, int l1, const float* next_norm, bool 
             ap.past_len = c.d_pos;
             ap.max_seq = c.max_seq;
             ap.causal = c.causal;
-            ap.kv_split = c.kvsplit;
+            ap.kv_split = seq >= 16 ? c.kvsplit : nullptr;  // a key tile shared by several query tiles is split once
             ap.split_plane = c.kvsplit_plane;
             RB_TRY(launch_attention(ap, rows, st));
         }

@@ -157,7 +157,7 @@ struct AttnParams {
     size_t split_plane;       // elements per plane (batch capacity * n_kv_heads * max_seq * head_dim)
 };
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st);
-bool attn_prefill_supported(const AttnParams& p);
+bool attn_prefill_supported(const AttnParams& p, int rows);
 int launch_attn_prefill(const AttnParams& p, int rows, cudaStream_t st);
 int configure_attn_prefill();
 int launch_attn_prefill_tc(const AttnParams& p, int rows, cudaStream_t st);

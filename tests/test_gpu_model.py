@@ -371,10 +371,10 @@ def test_empty_and_single_element_inputs(rb):
     assert ffn.forward(np.zeros((0, 64), dtype=np.float32)).shape == (0, 64)
 
 
-@pytest.mark.parametrize("batch", [2, 9])
+@pytest.mark.parametrize("batch", [2, 9, 17])
 def test_batched_decode_step(rb, batch):
     """One-token steps for several sequences at once against the oracle run sequence by sequence.
-    Eight sequences and more merge the attention partials in a stage of their own."""
+    Sixteen sequences and more take the tiled attention kernel instead of the split decode kernel."""
     om, prompt, model = _tiny(rb, "hd128", rb.sem.REFERENCE, max_batch=batch)
     rng = np.random.default_rng(40 + batch)
     vocab = om["cfg"]["vocab_size"]
