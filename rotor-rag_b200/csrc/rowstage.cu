@@ -18,6 +18,7 @@ namespace rb {
 
 constexpr int RS_THREADS = 128;
 constexpr int RS_MIN_ROWS = 64;
+constexpr int RS_WIDE_THREADS = 512;
 
 __device__ __forceinline__ float4 rs_deq(const VecStageParams& p, size_t col0, int off, int g, const float (&sxv)[3],
                                          float wscale) {
@@ -51,8 +52,9 @@ __device__ __forceinline__ float rs_gate(float gate, float up, int act) {
 // reductions and the quantiser of one row leave the memory pipe idle.
 // RESID: the stage adds to the residual stream (VS_OPROJ, VS_DOWN) and keeps a second register
 // row for it; the other modes are compiled without it.
-template <int V, bool RESID>
-__global__ void __launch_bounds__(RS_THREADS, V > 8 ? 4 : 5) row_stage_kernel(const __grid_constant__ VecStageParams p) {
+// TH: threads per row; 128 for rows up to 8192 elements, 512 for wider ones (XL FFN rows).
+template <int V, bool RESID, int TH = RS_THREADS>
+__global__ void __launch_bounds__(TH, TH > 128 ? 1 : (V > 8 ? 4 : 5)) row_stage_kernel(const __grid_constant__ VecStageParams p) {
     __shared__ float scratch[64];
     const int m = blockIdx.x, n = p.n, n4 = n >> 2, tid = threadIdx.x;
     const size_t ro = (size_t)m * n, col0 = (size_t)m * p.terms;
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(RS_THREADS, V > 8 ? 4 : 5) row_stage_kernel(co
     float4 v[V], aux[RESID ? V : 1];
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-        const int g = tid + j * RS_THREADS;
+        const int g = tid + j * TH;
         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (RESID) aux[RESID ? j : 0] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (g >= n4) continue;
@@ -96,7 +98,7 @@ __global__ void __launch_bounds__(RS_THREADS, V > 8 ? 4 : 5) row_stage_kernel(co
             const float inv = 1.0f / sqrtf(ss / (float)n + p.eps);
 #pragma unroll
             for (int j = 0; j < V; ++j) {
-                const int g = tid + j * RS_THREADS;
+                const int g = tid + j * TH;
                 const float4 w0 = g < n4 ? ldg4(p.norm0 + 4 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
                 // (multiply, multiply, add: no fused multiply-add, like the shared-memory version)
                 v[j].x = __fadd_rn(__fmul_rn(__fmul_rn(v[j].x, inv), w0.x), aux[j].x);
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(RS_THREADS, V > 8 ? 4 : 5) row_stage_kernel(co
     if (p.mode == VS_OPROJ || p.mode == VS_DOWN || p.mode == VS_EMBED) {
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            const int g = tid + j * RS_THREADS;
+            const int g = tid + j * TH;
             if (g < n4) *reinterpret_cast<float4*>(hdst + ro + 4 * g) = v[j];
         }
     }
@@ -128,7 +130,7 @@ __global__ void __launch_bounds__(RS_THREADS, V > 8 ? 4 : 5) row_stage_kernel(co
         const float inv = 1.0f / sqrtf(ss / (float)n + p.eps);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            const int g = tid + j * RS_THREADS;
+            const int g = tid + j * TH;
             const float4 w = g < n4 ? ldg4(p.norm1 + 4 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
             v[j].x = v[j].x * inv * w.x;
             v[j].y = v[j].y * inv * w.y;
@@ -139,7 +141,7 @@ __global__ void __launch_bounds__(RS_THREADS, V > 8 ? 4 : 5) row_stage_kernel(co
     if (p.y_out) {
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            const int g = tid + j * RS_THREADS;
+            const int g = tid + j * TH;
             if (g < n4) *reinterpret_cast<float4*>(p.y_out + ro + 4 * g) = v[j];
         }
     }
@@ -163,8 +165,10 @@ bool row_stage_supported(const VecStageParams& p, int rows) {
         return false;
     const bool from_acc = p.mode == VS_OPROJ || p.mode == VS_FFN || p.mode == VS_DOWN || p.mode == VS_DEQ;
     if (from_acc && (p.acc.planes != 1 || p.acc.out % 4 || p.terms < 1 || p.terms > 3)) return false;
-    if (p.n % 4 || p.n > 4 * 16 * RS_THREADS) return false;
-    if (p.xq && (p.kpad > 4 * 16 * RS_THREADS || p.terms_out < 1 || p.terms_out > 4)) return false;
+    const bool resid = p.mode == VS_OPROJ || p.mode == VS_DOWN;
+    const int widest = resid ? 4 * 16 * RS_THREADS : 4 * 14 * RS_WIDE_THREADS;  // 8192, or 28672 without a residual row
+    if (p.n % 4 || p.n > widest) return false;
+    if (p.xq && (p.kpad > widest || p.terms_out < 1 || p.terms_out > 4)) return false;
     if (p.ext_sumsq || p.ext_absmax || p.out_sumsq || p.out_absmax) return false;
     return true;
 }
@@ -183,6 +187,10 @@ static void launch_row_stage_v(const VecStageParams& p, int rows, int v, cudaStr
 
 int launch_row_stage(const VecStageParams& p, int rows, cudaStream_t st) {
     const int width = p.xq && p.kpad > p.n ? p.kpad : p.n;   // the quantiser also writes the zero padding
+    if (width > 4 * 16 * RS_THREADS) {  // wide rows without a residual: 512 threads, up to 14 groups each
+        row_stage_kernel<14, false, RS_WIDE_THREADS><<<rows, RS_WIDE_THREADS, 0, st>>>(p);
+        return launch_status();
+    }
     const int v = (width / 4 + RS_THREADS - 1) / RS_THREADS;
     if (p.mode == VS_OPROJ || p.mode == VS_DOWN)
         launch_row_stage_v<true>(p, rows, v, st);

@@ -387,3 +387,27 @@ def test_batched_decode_step(rb, batch):
         _, oc = O.model_forward(om, ids[b:b + 1], O.REFERENCE, use_cache=True)
         want, _ = O.model_forward(om, nxt[b:b + 1], O.REFERENCE, past_kv_cache=oc, use_cache=True)
         assert rel_err(got[b], want[0]) < TOL, (b, rel_err(got[b], want[0]))
+
+
+def test_wide_ffn_many_rows(rb):
+    """70 rows through an FFN whose hidden width (9216) exceeds 8192: the gating / sub-norm / quantise
+    stage takes the 512-thread register-resident kernel."""
+    import torch
+    from rotor_b200 import ops
+    d, ff, rows = 256, 9216, 70
+    rng = np.random.default_rng(77)
+    lw = {"gate": (O.synth_ternary(rng, ff, d), 0.02), "up": (O.synth_ternary(rng, ff, d), 0.018),
+          "down": (O.synth_ternary(rng, d, ff), 0.015),
+          "ffn_sub_norm": (1.0 + 0.1 * rng.standard_normal(ff)).astype(np.float32)}
+    pre_w = (1.0 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    x = rng.standard_normal((rows, d)).astype(np.float32)
+    sem = rb.sem.REFERENCE
+    ffn = rb.tr.GatedFFN(d, ff, semantics=sem)
+    pre = rb.tr.RMSNorm(d, eps=sem.eps)
+    pre.weight = pre_w
+    ffn.ffn_norm.weight = lw["ffn_sub_norm"]
+    for nm, proj in (("gate", ffn.gate_proj), ("up", ffn.up_proj), ("down", ffn.down_proj)):
+        proj.load_from_int8(lw[nm][0], lw[nm][1])
+    got = ffn.forward_device(ops.to_device(x, torch.float32), pre_norm=pre).cpu().numpy()
+    want = O.ffn(O.rmsnorm(x, pre_w, sem.eps), lw, o_sem(sem))
+    assert rel_err(got, want) < TOL, rel_err(got, want)
