@@ -29,7 +29,6 @@
 namespace rb {
 
 constexpr int T5_TOK = 256;                        // tokens per CTA (two MMA M halves)
-constexpr int T5_STAGES = 3;
 constexpr int T5_A_BYTES = T5_TOK * TILE_K;        // token operand per stage
 constexpr int T5_THREADS = 192;                    // warps 0-3 decode + epilogue, 4 TMA + TMEM, 5 MMA
 // Weight rows per CTA (MMA N) is a template argument: 256 for large grids; 64 when 256-row tiles
@@ -38,7 +37,11 @@ template <int ROWS>
 struct T5Cfg {
     static constexpr int B_BYTES = ROWS * TILE_K;                  // weight operand per stage
     static constexpr int STAGE_BYTES = T5_A_BYTES + B_BYTES;
-    static constexpr int SMEM = T5_STAGES * STAGE_BYTES + 1024;    // + slack to align the ring to 1024 bytes
+    // ring depth and decoder look-ahead: with 64-row tiles a stage is only four short MMAs, so the
+    // copy and weight-load latencies need more stages in flight to stay hidden
+    static constexpr int STAGES = ROWS >= 256 ? 3 : 5;
+    static constexpr int PREFETCH = ROWS >= 256 ? 2 : 6;           // K steps of weight tiles requested ahead
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;       // + slack to align the ring to 1024 bytes
     static constexpr int TMEM_COLS = 2 * ROWS < 32 ? 32 : 2 * ROWS;  // two accumulators of ROWS columns
     static constexpr int TILES_PER_WARP = ROWS / TILE_ROWS / 4;    // row tiles each decoder warp handles
 };
@@ -86,6 +89,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Tc5Params p) {
     using Cfg = T5Cfg<ROWS>;
     constexpr int T5_ROWS = ROWS, T5_STAGE_BYTES = Cfg::STAGE_BYTES, TPW = Cfg::TILES_PER_WARP;
+    constexpr int T5_STAGES = Cfg::STAGES, PF = Cfg::PREFETCH;
     extern __shared__ unsigned char t5_raw[];
     __shared__ __align__(8) unsigned long long s_full[T5_STAGES], s_empty[T5_STAGES], s_accf;
     __shared__ uint32_t s_tmem;
@@ -118,9 +122,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     if (warp < 4) {
         // ---------------- weight decoders: warp w owns row tiles TPW w .. TPW w + TPW - 1 of the CTA's
         const int g = lane >> 2, t = lane & 3;
-        // weight tiles are requested two K steps ahead of their decode, so that the L2 / HBM latency
+        // weight tiles are requested PF K steps ahead of their decode, so that the L2 / HBM latency
         // hides behind the decode of the step in between and the wait for a free stage
-        uint4 wv[2][TPW];
+        uint4 wv[PF][TPW];
         auto fetch = [&](int kt, uint4 (&dst)[TPW]) {
 #pragma unroll
             for (int u = 0; u < TPW; ++u) {
@@ -130,11 +134,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                              : make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
             }
         };
-        fetch(0, wv[0]);
-        fetch(1, wv[1]);
-        for (int kt2 = 0; kt2 < p.nkt; kt2 += 2) {
 #pragma unroll
-          for (int par = 0; par < 2; ++par) {
+        for (int par = 0; par < PF; ++par) fetch(par, wv[par]);
+        for (int kt2 = 0; kt2 < p.nkt; kt2 += PF) {
+#pragma unroll
+          for (int par = 0; par < PF; ++par) {
             const int kt = kt2 + par;
             if (kt >= p.nkt) break;
             const int s = kt % T5_STAGES;
@@ -166,7 +170,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s_full[s])) : "memory");
-            fetch(kt + 2, wv[par]);
+            fetch(kt + PF, wv[par]);
           }
         }
         // ---------------- epilogue: lane = token, 32 columns (weight rows) per load
