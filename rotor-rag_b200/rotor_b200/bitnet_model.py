@@ -255,6 +255,38 @@ class BitNetModel:
             out += new
         return out
 
+    def generate_greedy_batch(self, prompt_ids, max_new_tokens: int, use_graph: bool = True):
+        """Device-resident greedy generation for a batch of equal-length prompts [batch, prompt_len]:
+        one prefill, then every step advances all sequences at once.  Returns int64 [batch, max_new_tokens]."""
+        torch = abi.require_cuda()
+        prompts = np.asarray(prompt_ids, dtype=np.int64)
+        if prompts.ndim != 2:
+            raise ValueError("prompt_ids must be [batch, prompt_len]; ragged prompts are not supported")
+        batch, n_prompt = prompts.shape
+        if max_new_tokens <= 0:
+            return np.zeros((batch, 0), dtype=np.int64)
+        h = self._ensure_handle(batch, n_prompt, n_prompt + max_new_tokens)
+        ids_d = ops.to_device(prompts)
+        first = torch.empty(batch, dtype=torch.int64, device="cuda")
+        stream = torch.cuda.current_stream()
+        if use_graph and stream.cuda_stream == 0:
+            stream = self._side_stream()
+        s = stream.cuda_stream
+        out = np.empty((batch, max_new_tokens), dtype=np.int64)
+        with torch.cuda.stream(stream):
+            check(lib.rotor_b200_model_forward(h.h, ptr(ids_d), batch, n_prompt, 0, abi.LOGITS_NONE, None, ptr(first),
+                                               s), "prefill")
+            out[:, 0] = first.cpu().numpy()
+            remaining = max_new_tokens - 1
+            if remaining > 0:
+                check(lib.rotor_b200_model_decode_begin(h.h, ptr(first), batch, n_prompt, s), "decode_begin")
+                check(lib.rotor_b200_model_decode_steps(h.h, remaining, int(use_graph), s), "decode_steps")
+                buf = np.empty((remaining, batch), dtype=np.int64)   # the token log is [step][sequence]
+                check(lib.rotor_b200_model_read_tokens(h.h, 0, remaining, buf.ctypes.data, s), "read_tokens")
+                out[:, 1:] = buf.T
+        abi.device_status()
+        return out
+
     def _side_stream(self):
         torch = abi.require_cuda()
         if getattr(self, "_stream", None) is None:

@@ -411,3 +411,18 @@ def test_wide_ffn_many_rows(rb):
     got = ffn.forward_device(ops.to_device(x, torch.float32), pre_norm=pre).cpu().numpy()
     want = O.ffn(O.rmsnorm(x, pre_w, sem.eps), lw, o_sem(sem))
     assert rel_err(got, want) < TOL, rel_err(got, want)
+
+
+@pytest.mark.parametrize("batch", [3, 6])
+def test_batched_greedy_generation(rb, batch):
+    """Equal-length prompts generated together give, sequence by sequence, the oracle's tokens
+    (three sequences: fused generation step; six: the unfused one)."""
+    om, prompt, model = _tiny(rb, "hd64", rb.sem.REFERENCE, max_batch=batch)
+    rng = np.random.default_rng(60 + batch)
+    prompts = rng.integers(0, om["cfg"]["vocab_size"], size=(batch, 5))
+    got = model.generate_greedy_batch(prompts, 12)
+    assert got.shape == (batch, 12)
+    for b in range(batch):
+        want = O.generate_greedy(om, prompts[b], 12, O.REFERENCE)[5:]
+        assert list(got[b]) == want, b
+    assert np.array_equal(model.generate_greedy_batch(prompts, 12, use_graph=False), got)
