@@ -75,8 +75,72 @@ int launch_rope_table(float2* table, int max_seq, int head_dim, float theta, cud
     return launch_status();
 }
 
+
+// The same for many rows (prefill): 128-bit loads, four rotary pairs per thread, every load of the
+// thread in flight before the first use.  Needs complete accumulators in one plane, out % 4 == 0.
+__device__ __forceinline__ float4 qf_deq4(const QkvFinishParams& p, const float (&sxv)[3], int m, int o, float wscale) {
+    float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+    int4 a[3];
+#pragma unroll
+    for (int t = 0; t < 3; ++t)
+        if (t < p.terms) a[t] = __ldcg(reinterpret_cast<const int4*>(p.acc.acc + ((size_t)m * p.terms + t) * p.acc.out + o));
+#pragma unroll
+    for (int t = 0; t < 3; ++t)
+        if (t < p.terms) {
+            f.x += (float)a[t].x * sxv[t];
+            f.y += (float)a[t].y * sxv[t];
+            f.z += (float)a[t].z * sxv[t];
+            f.w += (float)a[t].w * sxv[t];
+        }
+    return make_float4(f.x * wscale, f.y * wscale, f.z * wscale, f.w * wscale);
+}
+
+__global__ void __launch_bounds__(256) qkv_finish_vec_kernel(const __grid_constant__ QkvFinishParams p) {
+    const int m = blockIdx.x;
+    const int b = m / p.seq, s = m % p.seq;
+    const int pos = *p.past_len + s;
+    const int D = p.head_dim, half = D / 2, h4 = half / 4;
+    const int dq = p.n_heads * D, dkv = p.n_kv_heads * D;
+    if (pos >= p.max_seq) return;
+    float sxv[3] = {0.f, 0.f, 0.f};
+    for (int t = 0; t < p.terms; ++t) sxv[t] = __ldcg(&p.sx[(size_t)m * p.terms + t]);
+    const int q_items = p.n_heads * h4, k_items = p.n_kv_heads * h4, v_items = dkv / 4;
+    for (int w = threadIdx.x; w < q_items + k_items + v_items; w += blockDim.x) {
+        if (w >= q_items + k_items) {  // V: plain dequantise into the cache
+            const int e = (w - q_items - k_items) * 4, head = e / D, i = e % D;
+            *reinterpret_cast<float4*>(p.v_cache + (((size_t)b * p.n_kv_heads + head) * p.max_seq + pos) * D + i) =
+                qf_deq4(p, sxv, m, dq + dkv + e, p.sv);
+            continue;
+        }
+        const bool is_q = w < q_items;
+        const int ww = is_q ? w : w - q_items;
+        const int head = ww / h4, i = (ww % h4) * 4;
+        const int base = (is_q ? 0 : dq) + head * D;
+        const float sc = is_q ? p.sq : p.sk;
+        float4 a = qf_deq4(p, sxv, m, base + i, sc);
+        float4 c = qf_deq4(p, sxv, m, base + i + half, sc);
+        if (p.rope) {
+            const float4 cs0 = *reinterpret_cast<const float4*>(p.rope + (size_t)pos * half + i);      // (cos, sin) x 2
+            const float4 cs1 = *reinterpret_cast<const float4*>(p.rope + (size_t)pos * half + i + 2);
+            const float4 ra = make_float4(a.x * cs0.x - c.x * cs0.y, a.y * cs0.z - c.y * cs0.w,
+                                          a.z * cs1.x - c.z * cs1.y, a.w * cs1.z - c.w * cs1.w);
+            const float4 rc = make_float4(c.x * cs0.x + a.x * cs0.y, c.y * cs0.z + a.y * cs0.w,
+                                          c.z * cs1.x + a.z * cs1.y, c.w * cs1.z + a.w * cs1.w);
+            a = ra;
+            c = rc;
+        }
+        float* dst = is_q ? p.q + (size_t)m * dq + head * D
+                          : p.k_cache + (((size_t)b * p.n_kv_heads + head) * p.max_seq + pos) * D;
+        *reinterpret_cast<float4*>(dst + i) = a;
+        *reinterpret_cast<float4*>(dst + i + half) = c;
+    }
+}
+
 int launch_qkv_finish(const QkvFinishParams& p, int rows, cudaStream_t st) {
-    qkv_finish_kernel<<<rows, 256, 0, st>>>(p);
+    if (rows >= 64 && p.acc.planes == 1 && p.acc.out % 4 == 0 && p.head_dim % 8 == 0 && p.terms >= 1 && p.terms <= 3)
+        qkv_finish_vec_kernel<<<rows, 256, 0, st>>>(p);
+    else
+        qkv_finish_kernel<<<rows, 256, 0, st>>>(p);
     return launch_status();
 }
 
