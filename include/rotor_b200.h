@@ -247,6 +247,20 @@ int rotor_b200_model_decode_steps(void* handle, int nsteps, int use_graph, void*
 int rotor_b200_model_read_tokens(void* handle, int first_step, int count, int64_t* tokens_host, void* stream);
 int rotor_b200_model_position(void* handle);
 
+/* Batched generation over prompts of different lengths -- an extension of the cached loop of
+ * TextGenerator.generate (src/rotor/generation.py:220-279), which takes one prompt per call.
+ * forward_ragged(): ids int64 [batch][seq] hold the prompts right-padded to `seq` tokens with any
+ * valid id; lens (HOST int32 [batch], 1 <= lens[b] <= seq) are the true lengths.  Causal models
+ * only (a position never attends to the padding behind it), past length 0.  logits_mode is
+ * NONE or LAST; logits [batch][vocab] and next_ids [batch] are taken at each prompt's own last
+ * token.  decode_begin_ragged(): like decode_begin, with sequence b continuing at lens[b];
+ * decode_steps / read_tokens follow as usual and rotor_b200_model_position reports the longest
+ * sequence. */
+int rotor_b200_model_forward_ragged(void* handle, const int64_t* ids, int batch, int seq, const int32_t* lens,
+                                    int logits_mode, float* logits, int64_t* next_ids, void* stream);
+int rotor_b200_model_decode_begin_ragged(void* handle, const int64_t* first_ids, int batch, const int32_t* lens,
+                                         void* stream);
+
 /* ---------------------------------------------------------------- sampling
  * TopKSampling.sample / TopPSampling.sample (src/rotor/generation.py:45-145) on the device: logits
  * [rows][vocab] float32 (device) are divided by `temperature`; mode 0 keeps the top_k largest, mode 1

@@ -21,7 +21,7 @@ namespace rb {
 __global__ void __launch_bounds__(256) qkv_finish_kernel(QkvFinishParams p) {
     const int m = blockIdx.x;
     const int b = m / p.seq, s = m % p.seq;
-    const int pos = *p.past_len + s;
+    const int pos = p.past_len[b] + s;
     const int D = p.head_dim, half = D / 2;
     const int dq = p.n_heads * D, dkv = p.n_kv_heads * D;
     if (pos >= p.max_seq) return;  // capacity is checked on the host; never write out of bounds
@@ -98,7 +98,7 @@ __device__ __forceinline__ float4 qf_deq4(const QkvFinishParams& p, const float 
 __global__ void __launch_bounds__(256) qkv_finish_vec_kernel(const __grid_constant__ QkvFinishParams p) {
     const int m = blockIdx.x;
     const int b = m / p.seq, s = m % p.seq;
-    const int pos = *p.past_len + s;
+    const int pos = p.past_len[b] + s;
     const int D = p.head_dim, half = D / 2, h4 = half / 4;
     const int dq = p.n_heads * D, dkv = p.n_kv_heads * D;
     if (pos >= p.max_seq) return;
@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnParams p) {
     __shared__ float s_o[4][D];
     const int h = blockIdx.x, m = blockIdx.y;
     const int b = m / p.seq, s = m % p.seq;
-    const int past = *p.past_len;
+    const int past = p.past_len[b];
     int T = p.causal ? past + s + 1 : past + p.seq;
     if (T > p.max_seq) T = p.max_seq;
     const int hk = h / (p.n_heads / p.n_kv_heads);

@@ -69,7 +69,7 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeParams& p, int 
     float* scratch = sc + G * lcmax;    // [64]
     float* row = scratch + 64;          // [dq]   (tail only)
 
-    const int pos = __ldcg(p.past_len);
+    const int pos = __ldcg(p.past_len + b);
     const int T = min(pos + 1, p.max_seq);
     const int lc = (T + p.nsplit - 1) / p.nsplit;
     const int t0 = sp * lc, t1 = min(T, t0 + lc);

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(const __grid_constant
     const int qt = gridDim.x - 1 - blockIdx.x;  // late query tiles see the most keys: start them first
     const int hk = blockIdx.y, b = blockIdx.z;
     const int s0 = qt * QT;
-    const int past = *p.past_len;
+    const int past = p.past_len[b];
     const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const float scale = 1.0f / sqrtf((float)D);
 

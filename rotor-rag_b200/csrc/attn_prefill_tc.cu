@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(256) kv_split_kernel(const __grid_constant__ A
     if (idx >= per_seq * batch) return;
     const int c4 = (int)(idx % c4n);
     const int t = (int)((idx / c4n) % p.max_seq);
-    int t_all = *p.past_len + p.seq;
+    int t_all = p.past_len[idx / per_seq] + p.seq;
     if (t_all > p.max_seq) t_all = p.max_seq;
     if (t >= t_all) return;
     const size_t e = (idx / c4n) * D + 4 * c4;  // element offset: ((b * n_kv + hk) * max_seq + t) * D + 4 c4
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(256, 1) attn_prefill_tc_kernel(const __grid_co
     const int qt = gridDim.x - 1 - blockIdx.x;  // late query tiles see the most keys: start them first
     const int hk = blockIdx.y, b = blockIdx.z;
     const int s0 = qt * QT;
-    const int past = *p.past_len;
+    const int past = p.past_len[b];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: matrix index and row within it for this lane's address
 

@@ -201,7 +201,7 @@ __device__ __forceinline__ void lmhead_body(const LmHeadParams& p, int row0, flo
         }
     }
     if (p.adv_log && threadIdx.x == 0) {
-        *p.adv_pos += 1;
+        for (int r = 0; r < NROWS; ++r) p.adv_pos[r] += 1;
         *p.adv_step += 1;
     }
 }

@@ -71,6 +71,8 @@ struct Model {
     long long* cur_ids;
     long long* tok_log;
     int* d_step;
+    int* d_lens;                // [max_batch] prompt lengths of a ragged batch
+    const int32_t* last_of;     // host, during a ragged forward: tokens of each sequence (its last row is picked)
     int max_log;
     // host mirror of the generation state
     int pos, step, batch;
@@ -157,7 +159,7 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     const size_t pb2 = (size_t)max_planes(d, ff) * cols * d;
     c.accA = cv.take<int32_t>(pa1 > pa2 ? pa1 : pa2);
     c.accB = cv.take<int32_t>(pb1 > pb2 ? pb1 : pb2);
-    c.d_pos = cv.take<int>(1);
+    c.d_pos = cv.take<int>(c.max_batch > 1 ? c.max_batch : 1);  // cached length of every sequence
     c.rope_buf = cv.take<float2>((size_t)c.max_seq * (c.head_dim / 2));
     c.nsplit = attn_decode_nsplit(c.max_seq);
     const size_t heads = (size_t)c.max_batch * c.n_heads * c.nsplit;
@@ -200,6 +202,7 @@ static void carve(Model& m, unsigned char* base, size_t* total) {
     m.max_log = c.max_seq;
     m.tok_log = cv.take<long long>((size_t)m.max_log * c.max_batch);
     m.d_step = cv.take<int>(1);
+    m.d_lens = cv.take<int>(c.max_batch > 1 ? c.max_batch : 1);
     m.mega_dev = cv.take<unsigned char>(mega_layer_bytes() * (size_t)c.n_layers);
     m.mega_bar = cv.take<unsigned>(2);
     const size_t tp = c.tp_size > 1 ? c.tp_size : 1;
@@ -231,14 +234,18 @@ static int derive(Model& m) {
     return ROTOR_B200_OK;
 }
 
-__global__ void set_int_kernel(int* p, int v) { *p = v; }
+// Cached length of every sequence: one value for all, or lens[b] when given.
+__global__ void set_pos_kernel(int* pos, int n, int v, const int* lens) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) pos[i] = lens ? lens[i] : v;
+}
 
-__global__ void begin_kernel(long long* cur, const long long* first, int batch, int* pos, int past, int* step) {
-    if (threadIdx.x < batch) cur[threadIdx.x] = first[threadIdx.x];
-    if (threadIdx.x == 0) {
-        *pos = past;
-        *step = 0;
+__global__ void begin_kernel(long long* cur, const long long* first, int batch, int* pos, int past, const int* lens,
+                             int* step) {
+    if (threadIdx.x < batch) {
+        cur[threadIdx.x] = first[threadIdx.x];
+        pos[threadIdx.x] = lens ? lens[threadIdx.x] : past;
     }
+    if (threadIdx.x == 0) *step = 0;
 }
 
 // After a generation step: log the picked tokens and move the position on.
@@ -246,10 +253,8 @@ __global__ void advance_kernel(const long long* cur, long long* log, int batch, 
     const int s = *step;
     if (threadIdx.x < batch && s < max_log) log[(size_t)s * batch + threadIdx.x] = cur[threadIdx.x];
     __syncthreads();
-    if (threadIdx.x == 0) {
-        *pos += 1;
-        *step = s + 1;
-    }
+    if (threadIdx.x < batch) pos[threadIdx.x] += 1;
+    if (threadIdx.x == 0) *step = s + 1;
 }
 
 #define RB_TRY(expr)              \
@@ -822,7 +827,7 @@ static int run_layers_tp(Model& m, const long long* ids, int batch, int seq, int
     int lm_rows = rows;
     if (!all && seq > 1) {
         for (int b = 0; b < batch; ++b)
-            RB_CUDA(cudaMemcpyAsync(c.qbuf + (size_t)b * d, c.hn + ((size_t)b * seq + seq - 1) * d, d * sizeof(float),
+            RB_CUDA(cudaMemcpyAsync(c.qbuf + (size_t)b * d, c.hn + ((size_t)b * seq + (m.last_of ? m.last_of[b] : seq) - 1) * d, d * sizeof(float),
                                     cudaMemcpyDeviceToDevice, st));
         x = c.qbuf;
         lm_rows = batch;
@@ -1011,7 +1016,7 @@ static int run_layers(Model& m, const long long* ids, int batch, int seq, int lo
     if (!all && seq > 1) {
         // compact the last rows: hn[b*seq + seq-1] -> qbuf[b] (qbuf is free by now)
         for (int b = 0; b < batch; ++b)
-            RB_CUDA(cudaMemcpyAsync(c.qbuf + (size_t)b * d, c.hn + ((size_t)b * seq + seq - 1) * d, d * sizeof(float),
+            RB_CUDA(cudaMemcpyAsync(c.qbuf + (size_t)b * d, c.hn + ((size_t)b * seq + (m.last_of ? m.last_of[b] : seq) - 1) * d, d * sizeof(float),
                                     cudaMemcpyDeviceToDevice, st));
         x = c.qbuf;
         lm_rows = batch;
@@ -1117,7 +1122,7 @@ int rotor_b200_model_forward(void* handle, const int64_t* ids, int batch, int se
     RB_REQUIRE(logits_mode >= ROTOR_B200_LOGITS_NONE && logits_mode <= ROTOR_B200_LOGITS_ALL);
     RB_REQUIRE(logits_mode == ROTOR_B200_LOGITS_NONE || logits);
     cudaStream_t st = as_stream(stream);
-    set_int_kernel<<<1, 1, 0, st>>>(m->c.d_pos, past_len);
+    set_pos_kernel<<<1, 256, 0, st>>>(m->c.d_pos, m->c.max_batch, past_len, nullptr);
     RB_TRY(run_layers(*m, (const long long*)ids, batch, seq, logits_mode, logits, (long long*)next_ids, st));
     m->pos = past_len + seq;
     return launch_status();
@@ -1129,8 +1134,56 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
     RB_REQUIRE(past_len >= 0 && past_len < m->cfg.max_seq);
     RB_TRY(mega_prepare(*m, batch, as_stream(stream)));
     begin_kernel<<<1, 1024, 0, as_stream(stream)>>>(m->cur_ids, (const long long*)first_ids, batch, m->c.d_pos,
-                                                    past_len, m->d_step);
+                                                    past_len, nullptr, m->d_step);
     m->pos = past_len;
+    m->step = 0;
+    m->batch = batch;
+    return launch_status();
+}
+
+/* Prefill of a ragged batch: `ids` holds `batch` prompts right-padded to `seq` tokens (any valid
+ * id as padding), lens[b] (host) the true length of prompt b, 1 <= lens[b] <= seq.  Causal
+ * models only: a row then never sees the padding behind it, so every position below lens[b]
+ * is what a batch-of-one forward of prompt b alone gives.  Logits / picks are taken at each
+ * prompt's own last token (logits_mode NONE or LAST).  Cache positions lens[b].. hold padding
+ * products; rotor_b200_model_decode_begin_ragged makes the next steps overwrite them in order. */
+int rotor_b200_model_forward_ragged(void* handle, const int64_t* ids, int batch, int seq, const int32_t* lens,
+                                    int logits_mode, float* logits, int64_t* next_ids, void* stream) {
+    Model* m = (Model*)handle;
+    RB_REQUIRE(m && ids && lens && batch > 0 && seq > 0);
+    RB_REQUIRE(m->cfg.causal && m->c.tp_size <= 1);
+    RB_REQUIRE(batch <= m->cfg.max_batch && (long)batch * seq <= m->cfg.max_rows && seq <= m->cfg.max_seq);
+    RB_REQUIRE(logits_mode == ROTOR_B200_LOGITS_NONE || (logits_mode == ROTOR_B200_LOGITS_LAST && logits));
+    for (int b = 0; b < batch; ++b) RB_REQUIRE(lens[b] >= 1 && lens[b] <= seq);
+    cudaStream_t st = as_stream(stream);
+    set_pos_kernel<<<1, 256, 0, st>>>(m->c.d_pos, m->c.max_batch, 0, nullptr);
+    m->last_of = lens;
+    const int rc = run_layers(*m, (const long long*)ids, batch, seq, logits_mode, logits, (long long*)next_ids, st);
+    m->last_of = nullptr;
+    if (rc) return rc;
+    m->pos = seq;
+    return launch_status();
+}
+
+/* rotor_b200_model_decode_begin for sequences of different cached lengths (host lens[b], after
+ * rotor_b200_model_forward_ragged): sequence b appends at position lens[b] + step and attends
+ * to its own lens[b] + step + 1 keys. */
+int rotor_b200_model_decode_begin_ragged(void* handle, const int64_t* first_ids, int batch, const int32_t* lens,
+                                         void* stream) {
+    Model* m = (Model*)handle;
+    RB_REQUIRE(m && first_ids && lens && batch > 0 && batch <= m->cfg.max_batch && batch <= 1024);
+    int longest = 0;
+    for (int b = 0; b < batch; ++b) {
+        RB_REQUIRE(lens[b] >= 0 && lens[b] < m->cfg.max_seq);
+        longest = lens[b] > longest ? lens[b] : longest;
+    }
+    cudaStream_t st = as_stream(stream);
+    RB_TRY(mega_prepare(*m, batch, st));
+    RB_CUDA(cudaMemcpyAsync(m->d_lens, lens, (size_t)batch * sizeof(int), cudaMemcpyHostToDevice, st));
+    begin_kernel<<<1, 1024, 0, st>>>(m->cur_ids, (const long long*)first_ids, batch, m->c.d_pos, 0, m->d_lens,
+                                     m->d_step);
+    RB_CUDA(cudaStreamSynchronize(st));  // `lens` may be pageable host memory the caller reuses
+    m->pos = longest;  // capacity checks follow the longest sequence
     m->step = 0;
     m->batch = batch;
     return launch_status();
@@ -1236,7 +1289,7 @@ int rotor_b200_model_forward_hidden(void* handle, const float* hidden_in, int ba
     cudaStream_t st = as_stream(stream);
     Ctx& c = m->c;
     const int rows = batch * seq;
-    set_int_kernel<<<1, 1, 0, st>>>(c.d_pos, past_len);
+    set_pos_kernel<<<1, 256, 0, st>>>(c.d_pos, c.max_batch, past_len, nullptr);
     RB_CUDA(cudaMemcpyAsync(c.h, hidden_in, (size_t)rows * c.d * sizeof(float), cudaMemcpyDeviceToDevice, st));
     VecStageParams e = {};
     e.mode = VS_PLAIN;
@@ -1378,7 +1431,7 @@ int rotor_b200_attention_forward(const rotor_b200_model_config* cfg, const rotor
     Ctx c;
     cudaStream_t st = as_stream(stream);
     RB_TRY(block_ctx(c, cfg, rows, workspace, workspace_bytes, st));
-    set_int_kernel<<<1, 1, 0, st>>>(c.d_pos, past_len);
+    set_pos_kernel<<<1, 256, 0, st>>>(c.d_pos, c.max_batch, past_len, nullptr);
     VecStageParams e = {};
     e.mode = VS_PLAIN;
     e.n = c.d;

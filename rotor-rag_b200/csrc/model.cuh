@@ -106,7 +106,7 @@ struct QkvFinishParams {
     float sq, sk, sv;
     int n_heads, n_kv_heads, head_dim;
     int seq;              // tokens per sequence in this call
-    const int* past_len;  // device scalar: tokens already cached
+    const int* past_len;  // device [batch]: tokens already cached, per sequence
     int max_seq;          // cache capacity per sequence
     const float2* rope;   // cos/sin table [max_seq][head_dim/2], or null for no rotation
     float* q;             // [rows][n_heads*head_dim]

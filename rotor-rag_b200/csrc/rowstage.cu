@@ -54,7 +54,7 @@ __device__ __forceinline__ float rs_gate(float gate, float up, int act) {
 // row for it; the other modes are compiled without it.
 // TH: threads per row; 128 for rows up to 8192 elements, 512 for wider ones (XL FFN rows).
 template <int V, bool RESID, int TH = RS_THREADS>
-__global__ void __launch_bounds__(TH, TH > 128 ? 1 : (V > 8 ? 4 : 5)) row_stage_kernel(const __grid_constant__ VecStageParams p) {
+__global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 : 5)) row_stage_kernel(const __grid_constant__ VecStageParams p) {
     __shared__ float scratch[64];
     const int m = blockIdx.x, n = p.n, n4 = n >> 2, tid = threadIdx.x;
     const size_t ro = (size_t)m * n, col0 = (size_t)m * p.terms;
@@ -192,6 +192,13 @@ int launch_row_stage(const VecStageParams& p, int rows, cudaStream_t st) {
         return launch_status();
     }
     const int v = (width / 4 + RS_THREADS - 1) / RS_THREADS;
+    static const bool ffn512 = getenv("ROTOR_B200_FFN_STAGE_128") == nullptr;  // comparison aid
+    if (ffn512 && v > 8 && p.mode != VS_OPROJ && p.mode != VS_DOWN) {
+        // 4097..8192 elements without a residual (the 2B FFN row): four groups per thread at 512 threads
+        // keep more warps per SM busy than fourteen groups at 128
+        row_stage_kernel<4, false, RS_WIDE_THREADS><<<rows, RS_WIDE_THREADS, 0, st>>>(p);
+        return launch_status();
+    }
     if (p.mode == VS_OPROJ || p.mode == VS_DOWN)
         launch_row_stage_v<true>(p, rows, v, st);
     else

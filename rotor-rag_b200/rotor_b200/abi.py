@@ -99,6 +99,8 @@ _SIGNATURES.update({
     "rotor_b200_model_decode_steps": (_i, [_p, _i, _i, _p]),
     "rotor_b200_model_read_tokens": (_i, [_p, _i, _i, _p, _p]),
     "rotor_b200_model_position": (_i, [_p]),
+    "rotor_b200_model_forward_ragged": (_i, [_p, _p, _i, _i, _p, _i, _p, _p, _p]),
+    "rotor_b200_model_decode_begin_ragged": (_i, [_p, _p, _i, _p, _p]),
     "rotor_b200_block_workspace_bytes": (_sz, [_cfgp, _i]),
     "rotor_b200_set_pdl": (_i, [_i]),
     "rotor_b200_sample": (_i, [_p, _i, _i, _i, _i, C.c_float, C.c_float, C.c_uint64, C.c_uint64, _p, _p]),

@@ -256,13 +256,27 @@ class BitNetModel:
         return out
 
     def generate_greedy_batch(self, prompt_ids, max_new_tokens: int, use_graph: bool = True):
-        """Device-resident greedy generation for a batch of equal-length prompts [batch, prompt_len]:
-        one prefill, then every step advances all sequences at once.  Returns int64 [batch, max_new_tokens]."""
+        """Device-resident greedy generation for a batch of prompts: one prefill, then every step
+        advances all sequences at once.  ``prompt_ids`` is [batch, prompt_len] or a list of
+        prompts of different lengths; those are right-padded for the prefill (a causal model
+        never attends to the padding behind a token) and every sequence then continues from
+        its own length.  Returns int64 [batch, max_new_tokens], row b holding what a
+        single-prompt generation from prompt b gives."""
         torch = abi.require_cuda()
-        prompts = np.asarray(prompt_ids, dtype=np.int64)
-        if prompts.ndim != 2:
-            raise ValueError("prompt_ids must be [batch, prompt_len]; ragged prompts are not supported")
-        batch, n_prompt = prompts.shape
+        rows = [np.asarray(p, dtype=np.int64).reshape(-1) for p in prompt_ids]
+        batch = len(rows)
+        if batch == 0:
+            return np.zeros((0, max(max_new_tokens, 0)), dtype=np.int64)
+        lens = np.array([len(r) for r in rows], dtype=np.int32)
+        if lens.min() < 1:
+            raise ValueError("every prompt needs at least one token")
+        n_prompt = int(lens.max())
+        ragged = bool((lens != n_prompt).any())
+        if ragged and not self.semantics.causal:
+            raise ValueError("prompts of different lengths need a causal model")
+        prompts = np.zeros((batch, n_prompt), dtype=np.int64)
+        for b, r in enumerate(rows):
+            prompts[b, :len(r)] = r
         if max_new_tokens <= 0:
             return np.zeros((batch, 0), dtype=np.int64)
         h = self._ensure_handle(batch, n_prompt, n_prompt + max_new_tokens)
@@ -274,12 +288,20 @@ class BitNetModel:
         s = stream.cuda_stream
         out = np.empty((batch, max_new_tokens), dtype=np.int64)
         with torch.cuda.stream(stream):
-            check(lib.rotor_b200_model_forward(h.h, ptr(ids_d), batch, n_prompt, 0, abi.LOGITS_NONE, None, ptr(first),
-                                               s), "prefill")
+            if ragged:
+                check(lib.rotor_b200_model_forward_ragged(h.h, ptr(ids_d), batch, n_prompt, lens.ctypes.data,
+                                                          abi.LOGITS_NONE, None, ptr(first), s), "prefill")
+            else:
+                check(lib.rotor_b200_model_forward(h.h, ptr(ids_d), batch, n_prompt, 0, abi.LOGITS_NONE, None,
+                                                   ptr(first), s), "prefill")
             out[:, 0] = first.cpu().numpy()
             remaining = max_new_tokens - 1
             if remaining > 0:
-                check(lib.rotor_b200_model_decode_begin(h.h, ptr(first), batch, n_prompt, s), "decode_begin")
+                if ragged:
+                    check(lib.rotor_b200_model_decode_begin_ragged(h.h, ptr(first), batch, lens.ctypes.data, s),
+                          "decode_begin")
+                else:
+                    check(lib.rotor_b200_model_decode_begin(h.h, ptr(first), batch, n_prompt, s), "decode_begin")
                 check(lib.rotor_b200_model_decode_steps(h.h, remaining, int(use_graph), s), "decode_steps")
                 buf = np.empty((remaining, batch), dtype=np.int64)   # the token log is [step][sequence]
                 check(lib.rotor_b200_model_read_tokens(h.h, 0, remaining, buf.ctypes.data, s), "read_tokens")

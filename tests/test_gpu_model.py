@@ -426,3 +426,25 @@ def test_batched_greedy_generation(rb, batch):
         want = O.generate_greedy(om, prompts[b], 12, O.REFERENCE)[5:]
         assert list(got[b]) == want, b
     assert np.array_equal(model.generate_greedy_batch(prompts, 12, use_graph=False), got)
+
+
+@pytest.mark.parametrize("lens", [[3, 7, 5], [9, 2, 6, 4, 9, 1], [30, 17, 40], list(range(4, 21))])
+def test_batched_greedy_generation_ragged(rb, lens):
+    """Prompts of different lengths generated together: every sequence gives the tokens of its
+    own single-prompt generation by the oracle (3 sequences: fused step; 6: unfused; 30/17/40:
+    tiled prefill attention over padded rows; 17 sequences: tiled attention in the steps)."""
+    import dataclasses
+    batch = len(lens)
+    sem, osem = dataclasses.replace(rb.sem.REFERENCE, causal=True), dataclasses.replace(O.REFERENCE, causal=True)
+    om, prompt, model = _tiny(rb, "hd64", sem, max_batch=batch)
+    rng = np.random.default_rng(70 + batch + lens[0])
+    prompts = [rng.integers(0, om["cfg"]["vocab_size"], size=n) for n in lens]
+    new = 8
+    got = model.generate_greedy_batch(prompts, new)
+    assert got.shape == (batch, new)
+    for b in range(batch):
+        want = O.generate_greedy(om, prompts[b], new, osem)[lens[b]:]
+        assert list(got[b]) == want, b
+    assert np.array_equal(model.generate_greedy_batch(prompts, new, use_graph=False), got)
+    with pytest.raises(ValueError):  # without a causal mask a row would attend to its padding
+        _tiny(rb, "hd64", rb.sem.REFERENCE, max_batch=batch)[2].generate_greedy_batch(prompts, new)
