@@ -48,21 +48,83 @@ __device__ __forceinline__ float rs_gate(float gate, float up, int act) {
     return gate * (c / (1.f + expf(-c)));
 }
 
+__device__ __forceinline__ void rs_cp16(void* smem, const void* gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+
+// The same dequantisation from this thread's staged pieces (PF kernels): piece q of group g is
+// stage[q * n4 + g], q = term * halves + half.
+__device__ __forceinline__ float4 rs_deq_staged(const int4* stage, int n4, int halves, int half, int terms, int g,
+                                                const float (&sxv)[3], float wscale) {
+    float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int t = 0; t < 3; ++t)
+        if (t < terms) {
+            const int4 a = stage[(size_t)(t * halves + half) * n4 + g];
+            f.x += (float)a.x * sxv[t];
+            f.y += (float)a.y * sxv[t];
+            f.z += (float)a.z * sxv[t];
+            f.w += (float)a.w * sxv[t];
+        }
+    return make_float4(f.x * wscale, f.y * wscale, f.z * wscale, f.w * wscale);
+}
+
 // Wide rows (V > 8) are capped at 128 registers so that four CTAs share an SM: with fewer, the
 // reductions and the quantiser of one row leave the memory pipe idle.
 // RESID: the stage adds to the residual stream (VS_OPROJ, VS_DOWN) and keeps a second register
 // row for it; the other modes are compiled without it.
 // TH: threads per row; 128 for rows up to 8192 elements, 512 for wider ones (XL FFN rows).
-template <int V, bool RESID, int TH = RS_THREADS>
-__global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 : 5)) row_stage_kernel(const __grid_constant__ VecStageParams p) {
+// PF: a CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ... and fetches the NEXT row's
+// accumulators and residual with cp.async while it reduces, normalises and quantises the current
+// one.  Every thread stages exactly the 16-byte pieces it will read itself, so the staging area
+// needs no barrier: cp.async.wait_group by the owner is enough, and the next fetch may start
+// as soon as the owner has the pieces in registers.  Accumulator modes only.
+template <int V, bool RESID, int TH, bool PF>
+__global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 : 5))
+    row_stage_kernel(const __grid_constant__ VecStageParams p, int rows) {
     __shared__ float scratch[64];
-    const int m = blockIdx.x, n = p.n, n4 = n >> 2, tid = threadIdx.x;
-    const size_t ro = (size_t)m * n, col0 = (size_t)m * p.terms;
+    extern __shared__ __align__(16) int4 rs_stage[];
+    const int n = p.n, n4 = n >> 2, tid = threadIdx.x;
     const bool from_acc = p.mode == VS_OPROJ || p.mode == VS_FFN || p.mode == VS_DOWN || p.mode == VS_DEQ;
-    float sxv[3] = {0.f, 0.f, 0.f};
-    if (from_acc)
-        for (int t = 0; t < p.terms; ++t) sxv[t] = __ldcg(&p.sx_in[col0 + t]);
+    const int halves = p.mode == VS_FFN ? 2 : 1;
     float* hdst = p.h_out ? p.h_out : p.h;
+    float sxn[3] = {0.f, 0.f, 0.f};
+
+    // PF: start the fetch of `row` (pieces into the staging area, scales into registers)
+    auto fetch = [&](int row) {
+        const size_t c0 = (size_t)row * p.terms;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const int g = tid + j * TH;
+            if (g >= n4) continue;
+            for (int t = 0; t < p.terms; ++t)
+                for (int hf = 0; hf < halves; ++hf)
+                    rs_cp16(rs_stage + (size_t)(t * halves + hf) * n4 + g,
+                            reinterpret_cast<const int4*>(p.acc.acc + (c0 + t) * p.acc.out + (size_t)hf * n) + g);
+            if (RESID)
+                rs_cp16(rs_stage + (size_t)p.terms * halves * n4 + g,
+                        reinterpret_cast<const int4*>(p.h + (size_t)row * n) + g);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+            if (t < p.terms) sxn[t] = __ldcg(&p.sx_in[c0 + t]);
+    };
+    if (PF && (int)blockIdx.x < rows) fetch(blockIdx.x);
+
+    for (int m = blockIdx.x; m < rows; m += gridDim.x) {
+    const size_t ro = (size_t)m * n, col0 = (size_t)m * p.terms;
+    float sxv[3] = {0.f, 0.f, 0.f};
+    if (PF) {
+#pragma unroll
+        for (int t = 0; t < 3; ++t) sxv[t] = sxn[t];
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (from_acc) {
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+            if (t < p.terms) sxv[t] = __ldcg(&p.sx_in[col0 + t]);
+    }
 
     // ---- build the row: every load of the stage in flight together
     float4 v[V], aux[RESID ? V : 1];
@@ -72,7 +134,20 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (RESID) aux[RESID ? j : 0] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (g >= n4) continue;
-        if (p.mode == VS_EMBED) {
+        if (PF) {
+            float4 a = rs_deq_staged(rs_stage, n4, halves, 0, p.terms, g, sxv, p.wscale0);
+            if (p.mode == VS_FFN) {
+                const float4 b = rs_deq_staged(rs_stage, n4, halves, 1, p.terms, g, sxv, p.wscale1);
+                a = make_float4(rs_gate(a.x, b.x, p.ffn_act), rs_gate(a.y, b.y, p.ffn_act),
+                                rs_gate(a.z, b.z, p.ffn_act), rs_gate(a.w, b.w, p.ffn_act));
+            }
+            v[j] = a;
+            if (RESID) {
+                const int4 r = rs_stage[(size_t)p.terms * halves * n4 + g];
+                aux[RESID ? j : 0] = make_float4(__int_as_float(r.x), __int_as_float(r.y), __int_as_float(r.z),
+                                                 __int_as_float(r.w));
+            }
+        } else if (p.mode == VS_EMBED) {
             const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.embed + (size_t)p.ids[m] * n) + g);
             v[j] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
                                __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
@@ -89,6 +164,7 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
             if (RESID) aux[RESID ? j : 0] = ldcg4(p.h + ro + 4 * g);
         }
     }
+    if (PF && m + (int)gridDim.x < rows) fetch(m + gridDim.x);  // the staged pieces are in registers now
     if constexpr (RESID) {
         if (p.mode == VS_OPROJ) {  // h += subnorm(row)
             float ss = 0.f;
@@ -153,6 +229,7 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
         lean_quantize<V>(q, v, scratch, p.xq + (size_t)m * p.terms_out * p.kpad, (size_t)p.kpad,
                          p.sx_out + (size_t)m * p.terms_out, p.xsum_out + (size_t)m * p.terms_out);
     }
+    }  // rows of this CTA
 }
 
 // Whether the register-resident kernel takes this stage: enough rows, complete accumulators in
@@ -173,37 +250,59 @@ bool row_stage_supported(const VecStageParams& p, int rows) {
     return true;
 }
 
+// Launches one instantiation.  Accumulator modes whose staging area fits run the prefetching
+// variant on a grid of resident CTAs; everything else runs one CTA per row.
+template <int V, bool RESID, int TH>
+static int launch_one(const VecStageParams& p, int rows, cudaStream_t st) {
+    static const bool no_pf = getenv("ROTOR_B200_ROWSTAGE_NO_PREFETCH") != nullptr;  // comparison aid
+    const bool from_acc = p.mode == VS_OPROJ || p.mode == VS_FFN || p.mode == VS_DOWN || p.mode == VS_DEQ;
+    const size_t pieces = (size_t)p.terms * (p.mode == VS_FFN ? 2 : 1) + (RESID ? 1 : 0);
+    const size_t smem = pieces * (size_t)p.n * sizeof(int);
+    if (from_acc && !no_pf && smem <= 200 * 1024) {
+        auto* k = row_stage_kernel<V, RESID, TH, true>;
+        static size_t configured = 0;  // per instantiation
+        static int sms = 0;
+        if (smem > configured) {
+            RB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            configured = smem;
+        }
+        if (!sms) {
+            int dev = 0;
+            RB_CUDA(cudaGetDevice(&dev));
+            RB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        }
+        int per_sm = 0;
+        RB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, TH, smem));
+        if (per_sm >= 1) {
+            const int grid = rows < per_sm * sms ? rows : per_sm * sms;
+            k<<<grid, TH, smem, st>>>(p, rows);
+            return launch_status();
+        }
+    }
+    row_stage_kernel<V, RESID, TH, false><<<rows, TH, 0, st>>>(p, rows);
+    return launch_status();
+}
+
 template <bool RESID>
-static void launch_row_stage_v(const VecStageParams& p, int rows, int v, cudaStream_t st) {
-    if (v <= 5)
-        row_stage_kernel<5, RESID><<<rows, RS_THREADS, 0, st>>>(p);
-    else if (v <= 8)
-        row_stage_kernel<8, RESID><<<rows, RS_THREADS, 0, st>>>(p);
-    else if (v <= 14)
-        row_stage_kernel<14, RESID><<<rows, RS_THREADS, 0, st>>>(p);
-    else
-        row_stage_kernel<16, RESID><<<rows, RS_THREADS, 0, st>>>(p);
+static int launch_row_stage_v(const VecStageParams& p, int rows, int v, cudaStream_t st) {
+    if (v <= 5) return launch_one<5, RESID, RS_THREADS>(p, rows, st);
+    if (v <= 8) return launch_one<8, RESID, RS_THREADS>(p, rows, st);
+    if (v <= 14) return launch_one<14, RESID, RS_THREADS>(p, rows, st);
+    return launch_one<16, RESID, RS_THREADS>(p, rows, st);
 }
 
 int launch_row_stage(const VecStageParams& p, int rows, cudaStream_t st) {
     const int width = p.xq && p.kpad > p.n ? p.kpad : p.n;   // the quantiser also writes the zero padding
-    if (width > 4 * 16 * RS_THREADS) {  // wide rows without a residual: 512 threads, up to 14 groups each
-        row_stage_kernel<14, false, RS_WIDE_THREADS><<<rows, RS_WIDE_THREADS, 0, st>>>(p);
-        return launch_status();
-    }
+    if (width > 4 * 16 * RS_THREADS)  // wide rows without a residual: 512 threads, up to 14 groups each
+        return launch_one<14, false, RS_WIDE_THREADS>(p, rows, st);
     const int v = (width / 4 + RS_THREADS - 1) / RS_THREADS;
     static const bool ffn512 = getenv("ROTOR_B200_FFN_STAGE_128") == nullptr;  // comparison aid
-    if (ffn512 && v > 8 && p.mode != VS_OPROJ && p.mode != VS_DOWN) {
+    if (ffn512 && v > 8 && p.mode != VS_OPROJ && p.mode != VS_DOWN)
         // 4097..8192 elements without a residual (the 2B FFN row): four groups per thread at 512 threads
         // keep more warps per SM busy than fourteen groups at 128
-        row_stage_kernel<4, false, RS_WIDE_THREADS><<<rows, RS_WIDE_THREADS, 0, st>>>(p);
-        return launch_status();
-    }
-    if (p.mode == VS_OPROJ || p.mode == VS_DOWN)
-        launch_row_stage_v<true>(p, rows, v, st);
-    else
-        launch_row_stage_v<false>(p, rows, v, st);
-    return launch_status();
+        return launch_one<4, false, RS_WIDE_THREADS>(p, rows, st);
+    if (p.mode == VS_OPROJ || p.mode == VS_DOWN) return launch_row_stage_v<true>(p, rows, v, st);
+    return launch_row_stage_v<false>(p, rows, v, st);
 }
 
 }  // namespace rb
