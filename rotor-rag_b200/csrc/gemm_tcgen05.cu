@@ -28,21 +28,23 @@
 
 namespace rb {
 
-constexpr int T5_TOK = 256;                        // tokens per CTA (two MMA M halves)
-constexpr int T5_A_BYTES = T5_TOK * TILE_K;        // token operand per stage
+// Tokens per CTA is a template argument too: 256 (two MMA M halves, one CTA per SM: all 512
+// tensor-memory columns) or 128 (one half, 256 columns and a two-stage ring, so that TWO CTAs share
+// an SM and the accumulator read-back of one overlaps the MMAs of the other).
 constexpr int T5_THREADS = 192;                    // warps 0-3 decode + epilogue, 4 TMA + TMEM, 5 MMA
 // Weight rows per CTA (MMA N) is a template argument: 256 for large grids; 64 when 256-row tiles
 // would leave most SMs without a CTA (few tokens and a narrow output, e.g. 64 tokens x 8192 rows).
-template <int ROWS>
+template <int ROWS, int TOK = 256>
 struct T5Cfg {
+    static constexpr int A_BYTES = TOK * TILE_K;                   // token operand per stage
     static constexpr int B_BYTES = ROWS * TILE_K;                  // weight operand per stage
-    static constexpr int STAGE_BYTES = T5_A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     // ring depth and decoder look-ahead: with 64-row tiles a stage is only four short MMAs, so the
     // copy and weight-load latencies need more stages in flight to stay hidden
-    static constexpr int STAGES = ROWS >= 256 ? 3 : 5;
+    static constexpr int STAGES = TOK == 128 ? 2 : (ROWS >= 256 ? 3 : 5);
     static constexpr int PREFETCH = ROWS >= 256 ? 2 : 6;           // K steps of weight tiles requested ahead
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;       // + slack to align the ring to 1024 bytes
-    static constexpr int TMEM_COLS = 2 * ROWS < 32 ? 32 : 2 * ROWS;  // two accumulators of ROWS columns
+    static constexpr int TMEM_COLS = (TOK / 128) * ROWS < 32 ? 32 : (TOK / 128) * ROWS;  // one accumulator of ROWS columns per token half
     static constexpr int TILES_PER_WARP = ROWS / TILE_ROWS / 4;    // row tiles each decoder warp handles
 };
 constexpr long long T5_SPIN_CYCLES = 400000000LL;  // about 0.2 s
@@ -84,10 +86,11 @@ __device__ __forceinline__ uint64_t t5_desc(uint32_t smem_addr) {
 // codes {0,1,2} in four bytes -> signed bytes {-1,0,+1}
 __device__ __forceinline__ uint32_t t5_s8(uint32_t codes) { return (codes + 0x7f7f7f7fu) ^ 0x80808080u; }
 
-template <int ROWS>
-__global__ void __launch_bounds__(T5_THREADS, 1)
+template <int ROWS, int T5_TOK = 256>
+__global__ void __launch_bounds__(T5_THREADS, T5_TOK == 128 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Tc5Params p) {
-    using Cfg = T5Cfg<ROWS>;
+    using Cfg = T5Cfg<ROWS, T5_TOK>;
+    constexpr int T5_A_BYTES = Cfg::A_BYTES, A_HALF = 128 * TILE_K;
     constexpr int T5_ROWS = ROWS, T5_STAGE_BYTES = Cfg::STAGE_BYTES, TPW = Cfg::TILES_PER_WARP;
     constexpr int T5_STAGES = Cfg::STAGES, PF = Cfg::PREFETCH;
     extern __shared__ unsigned char t5_raw[];
@@ -97,7 +100,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     const uint32_t ring = (smem_u32(t5_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok0 = blockIdx.x * T5_TOK, rt0 = blockIdx.y * (T5_ROWS / TILE_ROWS);
-    const int nhalf = p.ncols - tok0 > 128 ? 2 : 1;  // token halves of this CTA that hold any token
+    const int nhalf = (T5_TOK > 128 && p.ncols - tok0 > 128) ? 2 : 1;  // token halves of this CTA that hold any token
     volatile int* abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
@@ -222,10 +225,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                 if (!t5_wait(smem_u32(&s_empty[s]), ((kt / T5_STAGES) & 1) ^ 1, abort_flag, p.status, 0x7c000003u)) break;
                 const uint32_t bar = smem_u32(&s_full[s]);
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                             "r"(nhalf * (T5_A_BYTES / 2))
+                             "r"(nhalf * A_HALF)
                              : "memory");
                 for (int half = 0; half < nhalf; ++half) {
-                    const uint32_t dst = ring + s * T5_STAGE_BYTES + half * (T5_A_BYTES / 2);
+                    const uint32_t dst = ring + s * T5_STAGE_BYTES + half * A_HALF;
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
                         "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -249,7 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                 for (int half = 0; half < nhalf; ++half)
 #pragma unroll
                     for (int k4 = 0; k4 < TILE_K / 32; ++k4) {
-                        const uint64_t da = t5_desc(abase + half * (T5_A_BYTES / 2) + k4 * 32);
+                        const uint64_t da = t5_desc(abase + half * A_HALF + k4 * 32);
                         const uint64_t db = t5_desc(bbase + k4 * 32);
                         const uint32_t accumulate = (kt > 0 || k4 > 0) ? 1u : 0u;
                         asm volatile(
@@ -311,6 +314,8 @@ int configure_gemm_tcgen05() {
     g_encode = (EncodeTiledFn)fn;
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<256>::SMEM));
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<64>::SMEM));
+    RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 T5Cfg<256, 128>::SMEM));
     g_tc5_ready = true;
     return ROTOR_B200_OK;
 }
@@ -338,7 +343,8 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return ROTOR_B200_ERR_CUDA;
-    const int tok_tiles = (ncols + T5_TOK - 1) / T5_TOK, rows = p.nrt * TILE_ROWS;
+    const int tok_tiles = (ncols + 255) / 256, rows = p.nrt * TILE_ROWS;
+    static const bool pair = getenv("ROTOR_B200_T5_PAIR") != nullptr;
     static int sms = 0;
     if (!sms) {
         int dev = 0;
@@ -349,6 +355,9 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
     if (tok_tiles * ((rows + 255) / 256) < sms) {  // 256-row tiles would leave SMs idle
         dim3 grid(tok_tiles, (rows + 63) / 64);
         gemm_tcgen05_kernel<64><<<grid, T5_THREADS, T5Cfg<64>::SMEM, st>>>(tmap, p);
+    } else if (pair) {  // 128-token tiles, two CTAs per SM
+        dim3 grid((ncols + 127) / 128, (rows + 255) / 256);
+        gemm_tcgen05_kernel<256, 128><<<grid, T5_THREADS, T5Cfg<256, 128>::SMEM, st>>>(tmap, p);
     } else {
         dim3 grid(tok_tiles, (rows + 255) / 256);
         gemm_tcgen05_kernel<256><<<grid, T5_THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);
