@@ -82,6 +82,11 @@ EXTRA_MODELS = {
     # per-rank FFN slice still wider than 8192 when split two ways
     "wide_tp": dict(cfg=dict(vocab_size=512, d_model=256, n_layers=2, n_heads=4, n_kv_heads=2, d_ff=18432),
                     seed=778, prompt_len=6),
+    # four KV heads: shards four ways.  The seed is one whose one-term quantiser has no value within
+    # float rounding of a .5 tie (checked by perturbing the oracle's norm sums): with one activation
+    # term a single such tie moves the logits by several percent of their RMS.
+    "tp4": dict(cfg=dict(vocab_size=1024, d_model=512, n_layers=2, n_heads=8, n_kv_heads=4, d_ff=2048),
+                seed=9094, prompt_len=7),
 }
 
 

@@ -1,4 +1,4 @@
-"""GPU, two ranks on two GPUs (skipped on a one-GPU box): the tensor-parallel model through
+"""GPU, two ranks on two GPUs and four on four (skipped on a smaller box): the tensor-parallel model through
 the C ABI against the single-device oracle.  Each rank checks its vocabulary slice of the
 logits (tolerance: max-abs error below 1e-3 of the output RMS) and that greedy generation,
 launch by launch and as a replayed CUDA graph, yields the oracle's tokens."""
@@ -12,7 +12,6 @@ import golden_inputs as G
 from oracle import bitlinear_np as O
 
 pytestmark = pytest.mark.gpu
-WORLD = 2
 TOL = 1e-3
 
 
@@ -22,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, port, out_dir, name):
+def _worker(rank, port, out_dir, name, WORLD):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -38,7 +37,7 @@ def _worker(rank, port, out_dir, name):
         om, prompt = G.tiny_model(name)
         model = ShardedBitNetModel(om["cfg"], group, semantics=BASELINE.with_(act_terms=1), max_seq=64)
         model.load_from_params(om)
-        logits = model.forward(prompt[None, :])                      # [1, S, V/2]
+        logits = model.forward(prompt[None, :])                      # [1, S, V/WORLD]
         last = model.forward(prompt[None, :], logits_positions="last")
         from rotor_b200 import abi
         before = abi.lib.rotor_b200_launch_count()
@@ -55,13 +54,13 @@ def _worker(rank, port, out_dir, name):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("name", ["hd128", "wide_tp"])
-def test_two_gpu_model_matches_oracle(tmp_path, name):
+@pytest.mark.parametrize("name,WORLD", [("hd128", 2), ("wide_tp", 2), ("tp4", 4)])
+def test_sharded_model_matches_oracle(tmp_path, name, WORLD):
     import torch
     if torch.cuda.device_count() < WORLD:
-        pytest.skip("needs two GPUs")
+        pytest.skip(f"needs {WORLD} GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(_free_port(), str(tmp_path), name), nprocs=WORLD, join=True)
+    mp.spawn(_worker, args=(_free_port(), str(tmp_path), name, WORLD), nprocs=WORLD, join=True)
     om, prompt = G.tiny_model(name)
     sem = O.with_semantics(O.BASELINE, act_terms=1)
     want, _ = O.model_forward(om, prompt[None, :], sem)

@@ -1,4 +1,4 @@
-"""CPU, two gloo ranks: the tensor-parallel split (row / column shards, shared row maximum,
+"""CPU, two and four gloo ranks: the tensor-parallel split (row / column shards, shared row maximum,
 integer all-reduce, sharded sub-norm, vocabulary-sharded pick) reproduces the single-device
 oracle.  The collectives are torch.distributed over gloo on 127.0.0.1; the arithmetic is the
 NumPy restatement in oracle/tp_np.py fed by rotor_b200.tensor_parallel.shard_layer, the same
@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, port, out_dir):
+def _worker(rank, port, out_dir, name, WORLD):
     import torch
     import torch.distributed as dist
     from oracle import tp_np
@@ -41,7 +41,7 @@ def _worker(rank, port, out_dir):
             dist.all_gather_object(got, pair)
             return got
 
-        om, prompt = G.tiny_model("hd128")
+        om, prompt = G.tiny_model(name)
         cfg = om["cfg"]
         sem = O.with_semantics(O.BASELINE, act_terms=1)
         ld = local_dims(cfg, WORLD)
@@ -58,13 +58,14 @@ def _worker(rank, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_two_rank_split_matches_single_device_oracle(tmp_path):
+@pytest.mark.parametrize("name,world", [("hd128", 2), ("tp4", 4)])
+def test_rank_split_matches_single_device_oracle(tmp_path, name, world):
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(_free_port(), str(tmp_path)), nprocs=WORLD, join=True)
-    om, prompt = G.tiny_model("hd128")
+    mp.spawn(_worker, args=(_free_port(), str(tmp_path), name, world), nprocs=world, join=True)
+    om, prompt = G.tiny_model(name)
     sem = O.with_semantics(O.BASELINE, act_terms=1)
     ids, want = O.generate_greedy(om, prompt, N_NEW, sem, return_logits=True)
-    got = [np.load(tmp_path / f"rank{r}.npz") for r in range(WORLD)]
+    got = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
     full = np.concatenate([g["logits"] for g in got], axis=1)  # vocabulary slices side by side
     for step in range(N_NEW):
         ref = np.asarray(want[step], np.float64)
