@@ -222,10 +222,7 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnParams p) {
 }
 
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st) {
-    if (attn_prefill_supported(p, rows)) {
-        static const bool fp32 = getenv("ROTOR_B200_ATTN_FP32") != nullptr;  // comparison aid: the FP32-pipe kernel
-        return fp32 ? launch_attn_prefill(p, rows, st) : launch_attn_prefill_tc(p, rows, st);
-    }
+    if (attn_prefill_supported(p, rows)) return launch_attn_prefill_tc(p, rows, st);
     dim3 grid(p.n_heads, rows);
     switch (p.head_dim) {
         case 32: attention_kernel<1><<<grid, 128, 0, st>>>(p); break;
@@ -252,8 +249,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     float* row = scratch + 64;                        // [dq]   (tail only)
     TraceRec tr;
     RB_STAMP(tr, 0);
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     RB_STAMP(tr, 2);
     attn_decode_body<D>(p, blockIdx.x, b, sm, threadIdx.x, blockDim.x, [] { __syncthreads(); });
     RB_STAMP(tr, 5);
@@ -325,6 +322,263 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
                                p.sx_out + (size_t)b * p.terms_out, p.xsum_out + (size_t)b * p.terms_out, scratch);
 }
 
+// ---------------------------------------------------------------------------------------
+// The same one-token attention with the slices of one KV head as a thread-block cluster.
+// Grid (n_kv_heads * nsplit, batch), cluster (nsplit, 1, 1), nsplit <= 8, 128 threads.
+//
+// Before the programmatic-launch wait a CTA reads the cached length and copies its slice of the
+// K and V rows (written by earlier steps) into shared memory with cp.async; after the wait only
+// the new q / k / v row has to come from the q/k/v product, and scores and weighted V run out of
+// shared memory.  The slices are then merged through distributed shared memory: every CTA leaves
+// (max, sum, weighted V) for the group's heads in its own shared memory, and after a cluster
+// barrier CTA r combines the r-th share of the group's outputs from all slices and writes
+// finished attention rows -- the output projection reads one float row instead of every CTA of
+// it re-merging nsplit partial rows.  Merge arithmetic and order are those of the consumer-side
+// merge (lean_row, LM_ATTN).
+__device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster(const float* own_smem, unsigned cta) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                 : "=r"(remote)
+                 : "r"((uint32_t)__cvta_generic_to_shared(own_smem)), "r"(cta));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+constexpr int AC_MAX_SPLIT = 8;  // portable cluster size
+
+__host__ __device__ inline int round4(int v) { return (v + 3) & ~3; }
+
+template <int D>
+__global__ void __launch_bounds__(128) attn_decode_cluster_kernel(const __grid_constant__ AttnDecodeParams p) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int half = D / 2, C4 = D / 4, NCH = D / 32;  // 16-byte chunks per row; chunks per lane of a key's 8 lanes
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int G = p.n_heads / p.n_kv_heads, ns = p.nsplit;
+    const int hk = blockIdx.x / ns, sp = blockIdx.x % ns;  // sp is also the rank inside the cluster
+    const int b = blockIdx.y;
+    const int dq = p.n_heads * D, dkv = p.n_kv_heads * D;
+    const int lcmax = (p.max_seq + ns - 1) / ns;
+    float* q_s = sm;                          // [G][D], pre-scaled by 1/sqrt(D)
+    float* k_new = q_s + G * D;               // [D]
+    float* v_new = k_new + D;                 // [D]
+    float* sc = v_new + D;                    // [G][lcmax]
+    float* o_s = sc + round4(G * lcmax);      // [G][D] weighted V of this slice
+    float* ml_s = o_s + G * D;                // [2][G] slice maximum, slice sum
+    float* Ks = ml_s + round4(2 * G);         // [lcmax][D]
+    float* Vs = Ks + (size_t)lcmax * D;       // [lcmax][D]
+    TraceRec tr;
+    RB_STAMP(tr, 0);
+
+    // ---- before the wait: the cached length (advanced by the previous step's last kernel) and
+    // this slice's older cache rows
+    const int pos = __ldcg(p.past_len + b);
+    const int T = min(pos + 1, p.max_seq);
+    const int lc = (T + ns - 1) / ns;
+    const int t0 = sp * lc, t1 = min(T, t0 + lc);
+    float* kc = p.k_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
+    float* vc = p.v_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
+    for (int idx = tid; idx < (t1 - t0) * C4; idx += nthr) {
+        const int r = idx / C4, c4 = idx - r * C4, t = t0 + r;
+        if (t != pos) {  // the new row comes from the q/k/v product
+            cp_async16(Ks + (size_t)r * D + 4 * c4, kc + (size_t)t * D + 4 * c4);
+            cp_async16(Vs + (size_t)r * D + 4 * c4, vc + (size_t)t * D + 4 * c4);
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (p.rope && tid * 16 < half) prefetch_l2(p.rope + (size_t)pos * half + tid * 16);
+    RB_STAMP(tr, 1);
+    pdl_wait();
+    pdl_trigger();
+    RB_STAMP(tr, 2);
+
+    // ---- q of the G heads, and the new k / v of this KV head
+    const float scale = 1.0f / sqrtf((float)D);
+    const float* qf = p.qkv_f + (size_t)b * (dq + 2 * dkv);
+    for (int w = tid; w < (G + 1) * half; w += nthr) {
+        const bool is_q = w < G * half;
+        const int hh = is_q ? w / half : 0, i = w % half;
+        const int base = is_q ? (hk * G + hh) * D : dq + hk * D;
+        float a = __ldcg(qf + base + i), c = __ldcg(qf + base + i + half);
+        if (p.rope) {
+            const float2 cs = p.rope[(size_t)pos * half + i];
+            const float ra = a * cs.x - c * cs.y, rc = c * cs.x + a * cs.y;
+            a = ra;
+            c = rc;
+        }
+        if (is_q) {
+            q_s[hh * D + i] = a * scale;
+            q_s[hh * D + i + half] = c * scale;
+        } else {
+            k_new[i] = a;
+            k_new[i + half] = c;
+        }
+    }
+    for (int i = tid; i < D; i += nthr) v_new[i] = __ldcg(qf + dq + dkv + hk * D + i);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (pos < p.max_seq && pos >= t0 && pos < t1)
+        for (int i = tid; i < D; i += nthr) {
+            kc[(size_t)pos * D + i] = k_new[i];
+            vc[(size_t)pos * D + i] = v_new[i];
+        }
+    RB_STAMP(tr, 3);
+
+    // ---- scores of this slice: 8 lanes per key; lane l8 takes the 16-byte chunks l8, l8 + 8, ...
+    // of the key row (consecutive lanes read consecutive chunks of shared memory)
+    const int l8 = tid & 7;
+    for (int tb = t0; tb < t1; tb += nthr / 8) {  // same trip count for every thread (full-warp shuffles)
+        const int t = tb + (tid >> 3);
+        const bool valid = t < t1;
+        float4 kv[NCH];
+#pragma unroll
+        for (int e = 0; e < NCH; ++e) kv[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (valid) {
+            const float* kp = (t == pos) ? k_new : Ks + (size_t)(t - t0) * D;
+#pragma unroll
+            for (int e = 0; e < NCH; ++e) kv[e] = *reinterpret_cast<const float4*>(kp + 4 * (8 * e + l8));
+        }
+        for (int g = 0; g < G; ++g) {
+            float s = 0.f;
+#pragma unroll
+            for (int e = 0; e < NCH; ++e) {
+                const float4 q4 = *reinterpret_cast<const float4*>(q_s + g * D + 4 * (8 * e + l8));
+                s += q4.x * kv[e].x + q4.y * kv[e].y + q4.z * kv[e].z + q4.w * kv[e].w;
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if (valid && l8 == 0) sc[g * lcmax + (t - t0)] = s;
+        }
+    }
+    __syncthreads();
+
+    // ---- softmax statistics of the slice, one warp per head
+    const int warp = tid >> 5, lane = tid & 31, n = t1 - t0;
+    for (int g = warp; g < G; g += nthr / 32) {
+        float mx = -INFINITY;
+        for (int i = lane; i < n; i += 32) mx = fmaxf(mx, sc[g * lcmax + i]);
+        mx = warp_max(mx);
+        float l = 0.f;
+        for (int i = lane; i < n; i += 32) {
+            const float e = __expf(sc[g * lcmax + i] - mx);
+            sc[g * lcmax + i] = e;
+            l += e;
+        }
+        l = warp_sum(l);
+        if (lane == 0) {
+            ml_s[g] = n > 0 ? mx : -INFINITY;
+            ml_s[G + g] = l;
+        }
+    }
+    __syncthreads();
+
+    // ---- weighted V of the slice: thread d owns one output dimension
+    for (int d = tid; d < D; d += nthr) {
+        for (int g0 = 0; g0 < G; g0 += 4) {
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int t = t0; t < t1; ++t) {
+                const float vv = (t == pos) ? v_new[d] : Vs[(size_t)(t - t0) * D + d];
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    if (g0 + g < G) o[g] += sc[(g0 + g) * lcmax + (t - t0)] * vv;
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+                if (g0 + g < G) o_s[(g0 + g) * D + d] = o[g];
+        }
+    }
+    RB_STAMP(tr, 4);
+    cluster_barrier();  // every slice's (max, sum, weighted V) is in its CTA's shared memory
+
+    // ---- merge across the cluster: this CTA finishes outputs [sp * share, (sp + 1) * share) of the group
+    const int share = G * D / ns;  // G * D is a multiple of 32, ns <= 8
+    for (int idx = tid; idx < share; idx += nthr) {
+        const int oi = sp * share + idx, g = oi / D, d = oi - g * D;
+        float f[AC_MAX_SPLIT];
+        float M = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2) {
+            f[s2] = s2 < ns ? ld_cluster(ml_s + g, s2) : -INFINITY;
+            M = fmaxf(M, f[s2]);
+        }
+        float L = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2) {
+            const float ms = f[s2];
+            const float e = ms == -INFINITY ? 0.f : __expf(ms - M);
+            if (s2 < ns) L += ld_cluster(ml_s + G + g, s2) * e;
+            f[s2] = e;
+        }
+        const float inv = 1.0f / L;
+        float acc = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2)
+            if (s2 < ns) acc += ld_cluster(o_s + g * D + d, s2) * (f[s2] * inv);
+        p.attn_out[(size_t)b * dq + (size_t)(hk * G + g) * D + d] = acc;
+    }
+    cluster_barrier();  // no CTA leaves while its shared memory may still be read
+    RB_STAMP(tr, 5);
+    RB_TRACE_COMMIT(tr, 100);
+}
+
+static size_t attn_cluster_smem(int G, int D, int lcmax) {
+    return ((size_t)2 * G * D + 2 * D + round4(G * lcmax) + round4(2 * G) + 2 * (size_t)lcmax * D) * sizeof(float);
+}
+
+// Whether a generation step of this shape takes the cluster kernel (the slices of one KV head fit a
+// portable cluster and the staged cache slices fit shared memory).
+bool attn_decode_cluster_ok(int n_heads, int n_kv_heads, int head_dim, int max_seq, int nsplit) {
+    if (nsplit < 1 || nsplit > AC_MAX_SPLIT || n_kv_heads < 1 || n_heads % n_kv_heads) return false;
+    if (head_dim != 32 && head_dim != 64 && head_dim != 128) return false;
+    const int G = n_heads / n_kv_heads;
+    if ((G * head_dim) % nsplit) return false;
+    return attn_cluster_smem(G, head_dim, (max_seq + nsplit - 1) / nsplit) <= 200 * 1024;
+}
+
+template <int D>
+static int launch_attn_decode_cluster_d(const AttnDecodeParams& p, int batch, cudaStream_t st) {
+    const int G = p.n_heads / p.n_kv_heads;
+    const size_t smem = attn_cluster_smem(G, D, (p.max_seq + p.nsplit - 1) / p.nsplit);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.n_kv_heads * p.nsplit, batch);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.nsplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 2 : 1;
+    if (cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel<D>, p) != cudaSuccess) {
+        ++g_launch_count;
+        return ROTOR_B200_ERR_CUDA;
+    }
+    return launch_status();
+}
+
+int launch_attn_decode_cluster(const AttnDecodeParams& p, int batch, cudaStream_t st) {
+    if (!p.qkv_f || !p.attn_out || !attn_decode_cluster_ok(p.n_heads, p.n_kv_heads, p.head_dim, p.max_seq, p.nsplit))
+        return ROTOR_B200_ERR_ARG;
+    switch (p.head_dim) {
+        case 32: return launch_attn_decode_cluster_d<32>(p, batch, st);
+        case 64: return launch_attn_decode_cluster_d<64>(p, batch, st);
+        case 128: return launch_attn_decode_cluster_d<128>(p, batch, st);
+    }
+    return ROTOR_B200_ERR_SHAPE;
+}
+
 int attn_decode_nsplit(int max_seq) {
     int n = max_seq / 128;
     return n < 8 ? 8 : (n > 32 ? 32 : n);
@@ -376,8 +630,10 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    int rc = configure_attn_prefill();
-    return rc ? rc : configure_attn_prefill_tc();
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    return configure_attn_prefill_tc();
 }
 
 }  // namespace rb

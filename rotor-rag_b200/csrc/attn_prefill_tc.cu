@@ -1,7 +1,6 @@
 // Softmax attention for prompt prefill on the tensor cores, float32-faithful.
 //
-// Same contract as attn_prefill.cu (reference: MultiHeadAttention.forward,
-// src/rotor/transformer.py:249-283): scores Q K^T / sqrt(head_dim) over the cache, optional
+// Reference: MultiHeadAttention.forward (src/rotor/transformer.py:249-283): scores Q K^T / sqrt(head_dim) over the cache, optional
 // causal mask, softmax, times V, K/V shared by the query heads of a group.
 //
 // Both products run as mma.sync.m16n8k16 (bf16 operands, float32 accumulation).  To stay
@@ -321,6 +320,15 @@ int configure_attn_prefill_tc() {
     RB_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)attn_prefill_tc_smem<128>()));
     return ROTOR_B200_OK;
+}
+
+// Whether the tiled kernel takes this shape (the per-query kernel covers the rest).
+bool attn_prefill_supported(const AttnParams& p, int rows) {
+    if (p.head_dim != 64 && p.head_dim != 128) return false;
+    const int G = p.n_heads / p.n_kv_heads;
+    // long prompts, or many sequences with few new positions each (a CTA then serves one sequence's
+    // group of heads and streams that sequence's cache once)
+    return G >= 1 && G <= TC_BM && TC_BM % G == 0 && (p.seq >= 16 || rows >= 16);
 }
 
 int launch_attn_prefill_tc(const AttnParams& p, int rows, cudaStream_t st) {

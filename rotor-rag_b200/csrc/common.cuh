@@ -90,6 +90,33 @@ __device__ __forceinline__ int block_sum_i(int v, int* scratch) {
     return warp_sum_i(r);
 }
 
+// One-barrier variants for chains of reductions: `scratch` holds 64 floats used as two halves that
+// successive calls alternate between (`k` counts the calls).  A half is rewritten only two calls
+// later, and the barrier of the call in between orders that write after every read of this one.
+// Nothing else may touch `scratch` between calls without a CTA barrier of its own.
+__device__ __forceinline__ float block_sum_alt(float v, float* scratch, int& k) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    float* s = scratch + 32 * (k++ & 1);
+    v = warp_sum(v);
+    if (lane == 0) s[w] = v;
+    __syncthreads();
+    float r = (lane < nw) ? s[lane] : 0.f;
+    return warp_sum(r);
+}
+__device__ __forceinline__ float block_max_alt(float v, float* scratch, int& k) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    float* s = scratch + 32 * (k++ & 1);
+    v = warp_max(v);
+    if (lane == 0) s[w] = v;
+    __syncthreads();
+    float r = (lane < nw) ? s[lane] : -3.4e38f;
+    return warp_max(r);
+}
+
+// L2 prefetch of the 128-byte line that holds `p` (constants a kernel will need after its
+// programmatic-launch wait).
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // Streaming 128-bit load that bypasses L1 (weights are read exactly once).
 __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
     uint4 r;
@@ -103,6 +130,13 @@ __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
 // predecessor in the stream is still running.  pdl_trigger() lets the successor start
 // early; pdl_wait() blocks until every predecessor grid has completed and its writes are
 // visible.  Both are no-ops for a kernel launched without the attribute.
+//
+// Rule followed by every kernel of the generation step: pdl_wait() first, pdl_trigger() right
+// after it.  A successor's code before its own pdl_wait() therefore starts only once the
+// predecessor has passed its wait, i.e. once everything launched before the predecessor is
+// complete: that code may read constants (weights) and anything written two or more kernels
+// earlier (the cached length, older KV-cache rows), never the predecessor's outputs, and
+// writes nothing outside its own CTA.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -1,6 +1,7 @@
 // Generation-step BitLinear product with the vector stage that feeds it fused in.
 //
-// One CTA per SM, FG_THREADS threads.  Every CTA owns whole row tiles (16 output rows each,
+// One CTA per SM, FG_THREADS threads (a second CTA slot per SM stays free for the next kernel of
+// the step, see below).  Every CTA owns whole row tiles (16 output rows each,
 // full K), so no partial sum ever leaves the CTA: the warps split the CTA's tiles -- taken
 // in memory order, one contiguous span of HBM per CTA -- and merge their integer partial
 // sums in shared memory.  Before the tile products the CTA builds the int8 activation
@@ -9,6 +10,12 @@
 // separate single-CTA launch between two products.  After them it dequantises its rows
 // and writes finished float32 outputs; the gate/up product, whose CTAs own matching row
 // tiles of both halves, applies the gating there as well.
+//
+// Programmatic dependent launch: everything a product can do without its input -- tile ranges,
+// clearing the merge slots, the first weight tiles into registers, further tiles and the norm
+// weights into L2 -- happens before griddepcontrol.wait, while the previous kernel of the step is
+// still running on the same SMs; the launch gap and the cold start of the weight stream are
+// hidden behind that kernel.
 #include "product_body.cuh"
 
 RB_TRACE_DEFINE(rotor_b200_trace_read_fused)
@@ -16,20 +23,22 @@ RB_TRACE_DEFINE(rotor_b200_trace_read_fused)
 namespace rb {
 
 template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP, bool TP>
-__global__ void __launch_bounds__(DEEP ? FG_THREADS_DEEP : FG_THREADS, 1) fused_gemv_kernel(const __grid_constant__ FusedGemvParams p) {
+__global__ void __launch_bounds__(FG_THREADS, DEEP ? 1 : 2) fused_gemv_kernel(const __grid_constant__ FusedGemvParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ float s_sx[8];
     __shared__ int s_xsum[8];
     TraceRec tr;
     RB_STAMP(tr, 0);
-    pdl_trigger();
     const ProductCtx c = product_ctx(p, smem_raw);
     uint4 wv[FG_U];
     product_prefetch(p, c, wv);
+    if constexpr (!WIDE) lean_prefetch(p.st);
+    for (int e = threadIdx.x; e < c.slots * 128; e += blockDim.x) c.merge[e] = 0;
     RB_STAMP(tr, 1);
-    pdl_wait();  // the weights above are constants; everything below depends on earlier kernels
+    pdl_wait();     // the weights above are constants; everything below depends on earlier kernels
+    pdl_trigger();  // after the wait: see the rule in common.cuh
     RB_STAMP(tr, 2);
-    product_run<USE_MMA, NCOL, WIDE, DEEP, TP>(p, c, wv, s_sx, s_xsum);
+    product_run<USE_MMA, NCOL, WIDE, DEEP, TP>(p, c, wv, s_sx, s_xsum, tr);
     RB_STAMP(tr, 5);
     RB_TRACE_COMMIT(tr, p.st.mode * 10 + p.halves);
 }
@@ -57,7 +66,7 @@ static int launch_fused_tp(const FusedGemvParams& p, int grid, cudaStream_t st) 
     if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(DEEP ? FG_THREADS_DEEP : FG_THREADS);
+    cfg.blockDim = dim3(FG_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -125,14 +134,15 @@ int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int 
         p.sx_out = tp->sx_out;
     }
     if (grid > p.units) grid = p.units;
-    // large matrices (eight or more weight tiles per warp) stream: they take the pipelined loop
+    // large matrices (sixteen or more weight tiles per warp) stream: they take the pipelined loop,
+    // and so do rows too wide for the shallow variant's register budget
     const long tiles_per_warp = (long)p.units * p.halves * p.nkt / ((long)grid * FG_WARPS);
     if (fused_wide(p.st)) {
         if (p.cols == 1) return launch_fused<false, 1, true, true>(p, grid, st);
         if (p.cols == 2) return launch_fused<false, 2, true, true>(p, grid, st);
         return launch_fused<true, 1, true, true>(p, grid, st);
     }
-    if (tiles_per_warp >= 8) {
+    if (tiles_per_warp >= 16 || !fused_shallow_fits(p.st)) {
         if (p.cols == 1) return launch_fused<false, 1, false, true>(p, grid, st);
         if (p.cols == 2) return launch_fused<false, 2, false, true>(p, grid, st);
         return launch_fused<true, 1, false, true>(p, grid, st);

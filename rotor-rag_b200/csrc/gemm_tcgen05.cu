@@ -314,8 +314,6 @@ int configure_gemm_tcgen05() {
     g_encode = (EncodeTiledFn)fn;
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<256>::SMEM));
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<64>::SMEM));
-    RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 T5Cfg<256, 128>::SMEM));
     g_tc5_ready = true;
     return ROTOR_B200_OK;
 }
@@ -344,7 +342,6 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return ROTOR_B200_ERR_CUDA;
     const int tok_tiles = (ncols + 255) / 256, rows = p.nrt * TILE_ROWS;
-    static const bool pair = getenv("ROTOR_B200_T5_PAIR") != nullptr;
     static int sms = 0;
     if (!sms) {
         int dev = 0;
@@ -355,9 +352,6 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
     if (tok_tiles * ((rows + 255) / 256) < sms) {  // 256-row tiles would leave SMs idle
         dim3 grid(tok_tiles, (rows + 63) / 64);
         gemm_tcgen05_kernel<64><<<grid, T5_THREADS, T5Cfg<64>::SMEM, st>>>(tmap, p);
-    } else if (pair) {  // 128-token tiles, two CTAs per SM
-        dim3 grid((ncols + 127) / 128, (rows + 255) / 256);
-        gemm_tcgen05_kernel<256, 128><<<grid, T5_THREADS, T5Cfg<256, 128>::SMEM, st>>>(tmap, p);
     } else {
         dim3 grid(tok_tiles, (rows + 255) / 256);
         gemm_tcgen05_kernel<256><<<grid, T5_THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);

@@ -51,17 +51,19 @@ __device__ __forceinline__ float amax4(const float4& v) {
 }
 
 // Builds token row m in registers: v[j] holds elements 4*(threadIdx.x + j*blockDim.x) .. +3
-// (groups past n/4 stay zero).  Applies norm1 when given.  `scratch`: 64 shared floats;
+// (groups past n/4 stay zero).  Applies norm1 when given.  `scratch`: 64 shared floats, `rk` the
+// running count of one-barrier reductions over it (block_sum_alt);
 // `aux`: shared floats for the attention merge weights (2 * n_heads * nsplit, LM_ATTN only).
 // All threads of the block must call.
-template <int LEAN_V>
+// PLAIN_ONLY: the caller guarantees p.mode == LM_PLAIN; the other modes' code (and registers) are left out.
+template <int LEAN_V, bool PLAIN_ONLY = false>
 __device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[LEAN_V], float* scratch, float* aux,
-                                         bool writer, const XchScalarDev* x = nullptr) {
+                                         bool writer, int& rk, const XchScalarDev* x = nullptr) {
     const int n4 = p.n >> 2, bd = blockDim.x;
     const size_t ro = (size_t)m * p.n;
 #pragma unroll
     for (int j = 0; j < LEAN_V; ++j) v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (p.mode == LM_ATTN) {
+    if (!PLAIN_ONLY && p.mode == LM_ATTN) {
         const int D = p.head_dim, ns = p.nsplit, nh = p.n_heads;
         float* wf = aux;
         float* wl = aux + nh * ns;
@@ -120,23 +122,23 @@ __device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[
         a[j] = hv[j] = w0[j] = w1[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (g < n4) {
             const int i = g * 4;
-            if (p.mode == LM_EMBED) {
+            if (!PLAIN_ONLY && p.mode == LM_EMBED) {
                 const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.embed + (size_t)__ldcg(p.ids + m) * p.n + i));
                 a[j] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
                                    __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
             } else {
                 a[j] = ldcg4(p.y + ro + i);
-                if (p.mode == LM_ADD || p.mode == LM_SUBNORM_ADD) hv[j] = ldcg4(p.h + ro + i);
-                if (p.mode == LM_SUBNORM_ADD) w0[j] = ldg4(p.norm0 + i);
+                if (!PLAIN_ONLY && (p.mode == LM_ADD || p.mode == LM_SUBNORM_ADD)) hv[j] = ldcg4(p.h + ro + i);
+                if (!PLAIN_ONLY && p.mode == LM_SUBNORM_ADD) w0[j] = ldg4(p.norm0 + i);
             }
             if (p.norm1) w1[j] = ldg4(p.norm1 + i);
         }
     }
-    if (p.mode == LM_SUBNORM_ADD) {  // a <- subnorm(a)
+    if (!PLAIN_ONLY && p.mode == LM_SUBNORM_ADD) {  // a <- subnorm(a)
         float s0 = 0.f;
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) s0 += sq4(a[j]);
-        s0 = block_sum(s0, scratch);
+        s0 = block_sum_alt(s0, scratch, rk);
         const float inv0 = 1.0f / sqrtf(s0 / (float)p.n + p.eps);
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) {
@@ -148,15 +150,15 @@ __device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[
     }
 #pragma unroll
     for (int j = 0; j < LEAN_V; ++j) {
-        v[j] = make_float4(a[j].x + hv[j].x, a[j].y + hv[j].y, a[j].z + hv[j].z, a[j].w + hv[j].w);
+        v[j] = PLAIN_ONLY ? a[j] : make_float4(a[j].x + hv[j].x, a[j].y + hv[j].y, a[j].z + hv[j].z, a[j].w + hv[j].w);
         const int g = threadIdx.x + j * bd;
-        if (writer && p.h_out && g < n4) *reinterpret_cast<float4*>(p.h_out + ro + g * 4) = v[j];
+        if (!PLAIN_ONLY && writer && p.h_out && g < n4) *reinterpret_cast<float4*>(p.h_out + ro + g * 4) = v[j];
     }
     if (p.norm1) {
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) ss += sq4(v[j]);
-        ss = block_sum(ss, scratch);
+        ss = block_sum_alt(ss, scratch, rk);
         if (x && p.xi_sum) ss = xch_scalar(*x, p.xi_sum - 1, m, ss, false, writer, scratch);
         const float inv = 1.0f / sqrtf(ss / (float)(p.norm_n ? p.norm_n : p.n) + p.eps);
 #pragma unroll
@@ -169,21 +171,31 @@ __device__ __forceinline__ void lean_row(const LeanStage& p, int m, float4 (&v)[
     }
 }
 
+// Before the programmatic-launch wait: pulls the norm weights the stage will read into L2 (they
+// are constants, but a step streams ten times the L2 capacity between two uses of them).
+__device__ __forceinline__ void lean_prefetch(const LeanStage& p) {
+    if (threadIdx.x & 7) return;  // one request per 128-byte line
+    for (int i = threadIdx.x * 4; i < p.n; i += blockDim.x * 4) {
+        if (p.norm1) prefetch_l2(p.norm1 + i);
+        if (p.mode == LM_SUBNORM_ADD) prefetch_l2(p.norm0 + i);
+    }
+}
+
 // Absmax int8 quantiser over the register row: term t of the row goes to xq + t*tstride
 // (shared memory, zero padded to kpad), its scale and sum to sx[t] / xsum[t] (shared).
 // Same results as quantize_row_from_smem.  Requires kpad <= 4 * LEAN_V * blockDim.x; sx / xsum are
 // complete after the next CTA barrier.
 template <int LEAN_V>
 __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LEAN_V], float* scratch, int8_t* xq,
-                                              size_t tstride, float* sx, int* xsum, int m = 0, bool writer = false,
-                                              const XchScalarDev* x = nullptr) {
+                                              size_t tstride, float* sx, int* xsum, int& rk, int m = 0,
+                                              bool writer = false, const XchScalarDev* x = nullptr) {
     const int n4 = p.n >> 2, k4 = p.kpad >> 2, bd = blockDim.x;
     for (int t = 0; t < p.terms; ++t) {
         float mx = 0.f;
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) mx = fmaxf(mx, amax4(v[j]));
         if (threadIdx.x == 0) xsum[t] = 0;  // ordered before the atomics below by the reduction's barriers
-        mx = block_max(mx, scratch);
+        mx = block_max_alt(mx, scratch, rk);
         if (x && p.xi_max && t == 0) mx = xch_scalar(*x, p.xi_max - 1, m, mx, true, writer, scratch);
         const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
         const float rs = __fdiv_rn(1.0f, s);

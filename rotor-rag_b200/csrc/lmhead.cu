@@ -18,8 +18,8 @@ int lmhead_parts() { return LM_PARTS; }
 template <int NROWS>
 __global__ void __launch_bounds__(LM_WARPS * 32) lmhead_kernel(const __grid_constant__ LmHeadParams p, int row0) {
     extern __shared__ __align__(16) float xs[];  // [NROWS][d]
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     lmhead_body<NROWS>(p, row0, xs);
 }
 

@@ -79,13 +79,6 @@ struct Model {
     cudaGraphExec_t graph;
     int graph_batch;
     unsigned long long graph_launches;  // kernels inside the captured step
-    // single-launch generation step: per-block plan on host and device, built per batch size
-    void* mega_host;
-    void* mega_dev;
-    unsigned* mega_bar;
-    LmHeadParams mega_lm;
-    int mega_batch;   // batch the plan is valid for (0 = none)
-    int mega_ok;      // the device can run the step kernel for that plan
     // tensor parallel greedy pick: (value, global index) of every rank's best row
     __nv_bfloat16* xsplit;  // LM head over more than four rows: hi / lo bf16 split of its input rows
     float* pick_val;      // [rows]
@@ -203,8 +196,6 @@ static void carve(Model& m, unsigned char* base, size_t* total) {
     m.tok_log = cv.take<long long>((size_t)m.max_log * c.max_batch);
     m.d_step = cv.take<int>(1);
     m.d_lens = cv.take<int>(c.max_batch > 1 ? c.max_batch : 1);
-    m.mega_dev = cv.take<unsigned char>(mega_layer_bytes() * (size_t)c.n_layers);
-    m.mega_bar = cv.take<unsigned>(2);
     const size_t tp = c.tp_size > 1 ? c.tp_size : 1;
     m.pick_val = cv.take<float>(rows);
     m.pick_idx = cv.take<long long>(rows);
@@ -464,17 +455,14 @@ static bool fused_step_ok(const Model& m, int batch, int seq) {
     return shape_ok && q && o && g && dn;
 }
 
-// With record == true nothing is launched: the parameter blocks go to m.mega_host / m.mega_lm.
 static int run_step_fused(Model& m, const long long* ids, int batch, int logits_mode, float* logits,
-                          long long* next_ids, cudaStream_t st, bool advance, bool record = false) {
+                          long long* next_ids, cudaStream_t st, bool advance) {
     Ctx& c = m.c;
     const int d = c.d;
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
-    const int grid = fused_sm_count();
-    FusedGemvParams prod[4];
-    auto product = [&](int i, const void* tiles, size_t out, size_t in, int halves, const LeanStage& stg, float* y,
+    const bool cluster = attn_decode_cluster_ok(c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, c.nsplit);
+    auto product = [&](const void* tiles, size_t out, size_t in, int halves, const LeanStage& stg, float* y,
                        const float* scale, int seg1, int seg2, int act) {
-        if (record) return make_fused_params(prod[i], tiles, out, in, halves, batch, stg, y, scale, seg1, seg2, act, grid);
         return launch_fused_gemv(tiles, out, in, halves, batch, stg, y, scale, seg1, seg2, act, st);
     };
     LeanStage ls;
@@ -501,7 +489,7 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         ls.h_out = c.h;
         ls.norm1 = L.input_norm;
         const float sqkv[3] = {L.q_scale, L.k_scale, L.v_scale};
-        RB_TRY(product(0, L.qkv_tiles, qkv_out, d, 1, ls, c.fy[0], sqkv, c.dq, c.dq + c.dkv, 0));
+        RB_TRY(product(L.qkv_tiles, qkv_out, d, 1, ls, c.fy[0], sqkv, c.dq, c.dq + c.dkv, 0));
 
         AttnDecodeParams dp = {};
         dp.qkv_f = c.fy[0];
@@ -517,18 +505,24 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         dp.part_o = c.part_o;
         dp.part_m = c.part_m;
         dp.part_l = c.part_l;
-        if (!record) RB_TRY(launch_attn_decode(dp, batch, st));  // no counter: the o product merges the partials
-
-        // o <- merged attention
-        stage(LM_ATTN, c.dq);
-        ls.part_o = c.part_o;
-        ls.part_m = c.part_m;
-        ls.part_l = c.part_l;
-        ls.nsplit = c.nsplit;
-        ls.n_heads = c.n_heads;
-        ls.head_dim = c.head_dim;
+        dp.attn_out = c.attn;
+        if (cluster) {
+            // o <- finished attention rows (the cluster merges its slices itself)
+            RB_TRY(launch_attn_decode_cluster(dp, batch, st));
+            stage(LM_PLAIN, c.dq);
+            ls.y = c.attn;
+        } else {
+            RB_TRY(launch_attn_decode(dp, batch, st));  // no counter: the o product merges the partials
+            stage(LM_ATTN, c.dq);
+            ls.part_o = c.part_o;
+            ls.part_m = c.part_m;
+            ls.part_l = c.part_l;
+            ls.nsplit = c.nsplit;
+            ls.n_heads = c.n_heads;
+            ls.head_dim = c.head_dim;
+        }
         const float so[3] = {L.o_scale, L.o_scale, L.o_scale};
-        RB_TRY(product(1, L.o_tiles, d, c.dq, 1, ls, c.fy[1], so, d, d, 0));
+        RB_TRY(product(L.o_tiles, d, c.dq, 1, ls, c.fy[1], so, d, d, 0));
 
         // gate/up <- h + subnorm(o) -> h2, post-attention norm; gating in the epilogue
         stage(LM_SUBNORM_ADD, d);
@@ -538,15 +532,14 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
         ls.norm0 = L.attn_sub_norm;
         ls.norm1 = L.post_attn_norm;
         const float sgu[3] = {L.gate_scale, L.up_scale, 0.f};
-        RB_TRY(product(2, L.gate_up_tiles, c.ff, d, 2, ls, c.fy[2], sgu, 0, 0, c.ffn_act));
+        RB_TRY(product(L.gate_up_tiles, c.ff, d, 2, ls, c.fy[2], sgu, 0, 0, c.ffn_act));
 
         // down <- sub-norm(gated)
         stage(LM_PLAIN, c.ff);
         ls.y = c.fy[2];
         ls.norm1 = L.ffn_sub_norm;
         const float sd[3] = {L.down_scale, L.down_scale, L.down_scale};
-        RB_TRY(product(3, L.down_tiles, d, c.ff, 1, ls, c.fy[3], sd, d, d, 0));
-        if (record) RB_TRY(mega_record_layer(m.mega_host, l, prod, dp));
+        RB_TRY(product(L.down_tiles, d, c.ff, 1, ls, c.fy[3], sd, d, d, 0));
     }
     // LM head: h2 + last down, final norm in its prologue; greedy pick in its last CTA
     LmHeadParams lp = {};
@@ -569,34 +562,7 @@ static int run_step_fused(Model& m, const long long* ids, int batch, int logits_
     lp.pro_h = c.h2;
     lp.pro_norm = m.final_norm;
     lp.pro_eps = c.eps;
-    if (record) {
-        lp.nparts = grid;  // one partial pick per CTA of the step kernel
-        m.mega_lm = lp;
-        return ROTOR_B200_OK;
-    }
     return launch_lmhead(lp, batch, st);
-}
-
-// Builds (once per batch size) the plan of the single-launch generation step and copies it
-// to the device.  Not to be called inside a stream capture.
-static int mega_prepare(Model& m, int batch, cudaStream_t st) {
-    // Measured slower than the five-launch block on B200 (grid barriers of 148 CTAs cost 2.5-5 us
-    // each, more than a kernel boundary), so the single-launch step is opt-in.
-    static const bool off = getenv("ROTOR_B200_MEGA") == nullptr;
-    if (m.mega_batch == batch) return ROTOR_B200_OK;
-    m.mega_batch = batch;
-    m.mega_ok = 0;
-    if (off || m.c.tp_size > 1 || !fused_step_ok(m, batch, 1)) return ROTOR_B200_OK;
-    if (!m.mega_host) m.mega_host = calloc((size_t)m.cfg.n_layers, mega_layer_bytes());
-    if (!m.mega_host) return ROTOR_B200_ERR_ARG;
-    RB_TRY(run_step_fused(m, m.cur_ids, batch, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st, true, true));
-    if (!mega_supported(m.mega_host, m.cfg.n_layers, batch, m.c.d, fused_sm_count())) return ROTOR_B200_OK;
-    RB_CUDA(cudaMemcpyAsync(m.mega_dev, m.mega_host, mega_layer_bytes() * (size_t)m.cfg.n_layers,
-                            cudaMemcpyHostToDevice, st));
-    RB_CUDA(cudaMemsetAsync(m.mega_bar, 0, 2 * sizeof(unsigned), st));
-    RB_CUDA(cudaStreamSynchronize(st));  // the host plan may be rebuilt later; the copy must be done
-    m.mega_ok = 1;
-    return ROTOR_B200_OK;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -879,6 +845,7 @@ static int run_step_fused_tp(Model& m, const long long* ids, int batch, long lon
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
     FusedTpExtra ex = {};
     ex.xs = tp_scalar_dev(c.tp);
+    const bool cluster = attn_decode_cluster_ok(c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, c.nsplit);
     int xi = 0, big = 0;  // exchanges so far in this step; vector exchanges so far (slot parity)
     LeanStage ls;
     auto stage = [&](int mode, int n) {
@@ -920,15 +887,21 @@ static int run_step_fused_tp(Model& m, const long long* ids, int batch, long lon
         dp.part_o = c.part_o;
         dp.part_m = c.part_m;
         dp.part_l = c.part_l;
-        RB_TRY(launch_attn_decode(dp, batch, st));
-
-        stage(LM_ATTN, c.dq);
-        ls.part_o = c.part_o;
-        ls.part_m = c.part_m;
-        ls.part_l = c.part_l;
-        ls.nsplit = c.nsplit;
-        ls.n_heads = c.n_heads;
-        ls.head_dim = c.head_dim;
+        dp.attn_out = c.attn;
+        if (cluster) {
+            RB_TRY(launch_attn_decode_cluster(dp, batch, st));
+            stage(LM_PLAIN, c.dq);
+            ls.y = c.attn;
+        } else {
+            RB_TRY(launch_attn_decode(dp, batch, st));
+            stage(LM_ATTN, c.dq);
+            ls.part_o = c.part_o;
+            ls.part_m = c.part_m;
+            ls.part_l = c.part_l;
+            ls.nsplit = c.nsplit;
+            ls.n_heads = c.n_heads;
+            ls.head_dim = c.head_dim;
+        }
         ls.xi_max = ++xi;  // (index + 1)
         ex.part = c.accB;
         ex.sx_out = c.sx[1];
@@ -1108,7 +1081,6 @@ void rotor_b200_model_destroy(void* handle) {
     Model* m = (Model*)handle;
     if (!m) return;
     if (m->graph) cudaGraphExecDestroy(m->graph);
-    free(m->mega_host);
     free(m->layers);
     delete m;
 }
@@ -1132,7 +1104,6 @@ int rotor_b200_model_decode_begin(void* handle, const int64_t* first_ids, int ba
     Model* m = (Model*)handle;
     RB_REQUIRE(m && first_ids && batch > 0 && batch <= m->cfg.max_batch && batch <= 1024);
     RB_REQUIRE(past_len >= 0 && past_len < m->cfg.max_seq);
-    RB_TRY(mega_prepare(*m, batch, as_stream(stream)));
     begin_kernel<<<1, 1024, 0, as_stream(stream)>>>(m->cur_ids, (const long long*)first_ids, batch, m->c.d_pos,
                                                     past_len, nullptr, m->d_step);
     m->pos = past_len;
@@ -1178,7 +1149,6 @@ int rotor_b200_model_decode_begin_ragged(void* handle, const int64_t* first_ids,
         longest = lens[b] > longest ? lens[b] : longest;
     }
     cudaStream_t st = as_stream(stream);
-    RB_TRY(mega_prepare(*m, batch, st));
     RB_CUDA(cudaMemcpyAsync(m->d_lens, lens, (size_t)batch * sizeof(int), cudaMemcpyHostToDevice, st));
     begin_kernel<<<1, 1024, 0, st>>>(m->cur_ids, (const long long*)first_ids, batch, m->c.d_pos, 0, m->d_lens,
                                      m->d_step);
@@ -1192,9 +1162,6 @@ int rotor_b200_model_decode_begin_ragged(void* handle, const int64_t* first_ids,
 static int one_step(Model& m, cudaStream_t st) {
     if (m.c.tp_size > 1)
         return run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st, true);
-    if (m.mega_ok && m.mega_batch == m.batch)
-        return launch_decode_step_mega(m.mega_dev, m.mega_host, m.cfg.n_layers, m.batch, m.c.head_dim, m.mega_lm,
-                                       m.mega_bar, library_status_word(), fused_sm_count(), st);
     if (m.batch <= 4)  // pick, token log and position advance ride in the LM head's last CTA
         return run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st, true);
     RB_TRY(run_layers(m, m.cur_ids, m.batch, 1, ROTOR_B200_LOGITS_NONE, nullptr, m.cur_ids, st));

@@ -139,6 +139,9 @@ struct AttnDecodeParams {
     int kpad;
 };
 int launch_attn_decode(const AttnDecodeParams& p, int batch, cudaStream_t st);
+// Cluster variant: finished attention rows in p.attn_out (needs p.qkv_f); see attention.cu.
+bool attn_decode_cluster_ok(int n_heads, int n_kv_heads, int head_dim, int max_seq, int nsplit);
+int launch_attn_decode_cluster(const AttnDecodeParams& p, int batch, cudaStream_t st);
 int attn_decode_nsplit(int max_seq);
 size_t attn_decode_part_floats(int batch, int n_heads, int head_dim, int max_seq);
 int configure_attention();
@@ -158,8 +161,6 @@ struct AttnParams {
 };
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st);
 bool attn_prefill_supported(const AttnParams& p, int rows);
-int launch_attn_prefill(const AttnParams& p, int rows, cudaStream_t st);
-int configure_attn_prefill();
 int launch_attn_prefill_tc(const AttnParams& p, int rows, cudaStream_t st);
 int configure_attn_prefill_tc();
 
@@ -196,14 +197,6 @@ int launch_lmhead_mma(const __nv_bfloat16* embed, const float* x, __nv_bfloat16*
 int launch_lmhead(const LmHeadParams& p, int rows, cudaStream_t st);
 int lmhead_parts();
 
-// Single-launch generation step (megastep.cu).
-struct FusedGemvParams;
-size_t mega_layer_bytes();
-int mega_record_layer(void* host_plan, int l, const FusedGemvParams* prod4, const AttnDecodeParams& attn);
-int launch_decode_step_mega(const void* dev_plan, const void* host_plan, int n_layers, int batch, int head_dim,
-                            const LmHeadParams& lm, unsigned* bar, unsigned* status, int grid, cudaStream_t st);
-int configure_mega();
-bool mega_supported(const void* host_plan, int n_layers, int batch, int d, int grid);
 unsigned* library_status_word();
 
 // Tensor-parallel collectives (tp.cu); `comm` is the handle made by rotor_b200_tp_init.

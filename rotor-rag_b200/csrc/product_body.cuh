@@ -1,18 +1,24 @@
-// Device body of the generation-step BitLinear product (see fused.cu), split so that the
-// single-launch generation step can request the next product's first weight tiles before a
-// grid barrier and run the product after it.
+// Device body of the generation-step BitLinear product (see fused.cu): what runs before the
+// programmatic-launch wait (tile ranges, first weight tiles, L2 prefetch) and what runs after it
+// (prologue, tile products, epilogue).
 #pragma once
 #include "gemv_core.cuh"
 #include "leanstage.cuh"
 #include "vecstage.cuh"
+#include <type_traits>
 
 namespace rb {
 
-constexpr int FG_THREADS = 1024;
-constexpr int FG_THREADS_DEEP = 512;  // large matrices: twice the registers per thread for the pipelined tile loop
+// 512 threads per CTA.  The shallow variant (small matrices, a few weight tiles per warp) is held
+// to 64 registers so that two CTAs fit on an SM: the next kernel of the step becomes resident
+// while this one runs and has its first tiles in registers when its wait returns.  The deep
+// variant (large matrices) takes 128 registers for its pipelined tile loop.
+constexpr int FG_THREADS = 512;
 constexpr int FG_WARPS = FG_THREADS / 32;
-constexpr int FG_U = 4;  // weight tiles in flight per warp
-constexpr int FG_V = 2;  // float4 groups per thread in the prologue: input width <= 8192
+constexpr int FG_U = 4;        // weight tiles in flight per warp
+constexpr int FG_L2_AHEAD = 12;  // further tiles per warp pulled into L2 before the wait
+constexpr int FG_V = 4;        // float4 groups per thread in the register prologue: input width <= 8192
+constexpr int FG_V_NARROW = 2; // shallow variant, stages that hold four arrays per group: width <= 4096
 
 struct FusedGemvParams {
     const uint4* tiles;   // tiles of the (stacked) matrix
@@ -39,6 +45,11 @@ struct FusedGemvParams {
 // are staged as float32 in shared memory instead; only the plain mode (optional norm, then
 // quantise: the down projection's prologue) has such rows.
 __host__ __device__ inline bool fused_wide(const LeanStage& st) { return st.n > 4 * FG_V * FG_THREADS; }
+// The shallow variant keeps a plain stage (input and one norm weight per group) in FG_V groups per
+// thread and every other stage in FG_V_NARROW; wider rows of those stages take the deep variant.
+__host__ __device__ inline bool fused_shallow_fits(const LeanStage& st) {
+    return st.n <= 4 * (st.mode == LM_PLAIN ? FG_V : FG_V_NARROW) * FG_THREADS;
+}
 
 // Shared memory one product needs.
 inline size_t fused_smem(const FusedGemvParams& p) {
@@ -120,12 +131,16 @@ __device__ __forceinline__ const uint4* product_tile_ptr(const FusedGemvParams& 
     return p.tiles + (rt * p.nkt + kt) * 32 + lane;
 }
 
-// Requests the warp's first FG_U weight tiles (constants: may run before the activations
-// this product consumes exist).
+// Requests the warp's first FG_U weight tiles and pulls up to FG_L2_AHEAD more into L2
+// (constants: may run before the activations this product consumes exist).
 __device__ __forceinline__ void product_prefetch(const FusedGemvParams& p, const ProductCtx& c, uint4 (&wv)[FG_U]) {
 #pragma unroll
     for (int u = 0; u < FG_U; ++u)
         if (c.w0 + u < c.w1) wv[u] = ld_stream_v4(product_tile_ptr(p, c, c.w0 + u));
+    if ((threadIdx.x & 7) == 0) {  // four 128-byte lines per tile
+        const int end = min(c.w1, c.w0 + FG_U + FG_L2_AHEAD);
+        for (int lt = c.w0 + FG_U; lt < end; ++lt) prefetch_l2(product_tile_ptr(p, c, lt));
+    }
 }
 
 // Prologue, tile products and epilogue.  All threads of the CTA must call; `wv` as left by
@@ -137,17 +152,14 @@ __device__ __forceinline__ void product_prefetch(const FusedGemvParams& p, const
 // TP: tensor-parallel hooks compiled in (scalar exchanges in the prologue, int32 partial output).
 template <bool USE_MMA, int NCOL, bool WIDE = false, bool DEEP = false, bool TP = false>
 __device__ __forceinline__ void product_run(const FusedGemvParams& p, const ProductCtx& c, uint4 (&wv)[FG_U],
-                                            float* s_sx, int* s_xsum) {
+                                            float* s_sx, int* s_xsum, TraceRec& tr) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     int8_t* xs = c.xs;
     int* merge = c.merge;
     float* scratch = c.scratch;
     float* aux = c.aux;
-    const int xs_stride = c.xs_stride, slots = c.slots, u0 = c.u0, u1 = c.u1, w0 = c.w0, w1 = c.w1;
-    for (int e = threadIdx.x; e < slots * 128; e += blockDim.x) merge[e] = 0;
+    const int xs_stride = c.xs_stride, u0 = c.u0, u1 = c.u1, w0 = c.w0, w1 = c.w1;
     auto tile_ptr = [&](int lt) { return product_tile_ptr(p, c, lt); };
-    TraceRec tr;
-    (void)tr;
 
     // ---- prologue: activation rows -> int8 in shared memory
     const bool writer = blockIdx.x == 0;
@@ -188,16 +200,29 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
                                    s_sx + m * p.st.terms, s_xsum + m * p.st.terms, scratch, (size_t)xs_stride, given);
         }
     } else {
-        constexpr int V = DEEP ? 2 * FG_V : FG_V;  // the deep variant runs half as many threads
-        for (int m = 0; m < p.rows; ++m) {
-            float4 v[V];
-            const XchScalarDev* x = (TP && p.xs.size) ? &p.xs : nullptr;
-            lean_row<V>(p.st, m, v, scratch, aux, writer, x);
-            lean_quantize<V>(p.st, v, scratch, xs + (size_t)m * p.st.terms * xs_stride, (size_t)xs_stride,
-                             s_sx + m * p.st.terms, s_xsum + m * p.st.terms, m, writer, x);
+        const XchScalarDev* x = (TP && p.xs.size) ? &p.xs : nullptr;
+        int rk = 0;
+        auto rows = [&](auto vtag, auto plain_tag) {
+            constexpr int V = decltype(vtag)::value;
+            constexpr bool PLAIN = decltype(plain_tag)::value;
+            for (int m = 0; m < p.rows; ++m) {
+                float4 v[V];
+                lean_row<V, PLAIN>(p.st, m, v, scratch, aux, writer, rk, x);
+                lean_quantize<V>(p.st, v, scratch, xs + (size_t)m * p.st.terms * xs_stride, (size_t)xs_stride,
+                                 s_sx + m * p.st.terms, s_xsum + m * p.st.terms, rk, m, writer, x);
+            }
+        };
+        if constexpr (DEEP) {
+            rows(std::integral_constant<int, FG_V>(), std::false_type());
+        } else {
+            if (p.st.mode == LM_PLAIN)
+                rows(std::integral_constant<int, FG_V>(), std::true_type());
+            else
+                rows(std::integral_constant<int, FG_V_NARROW>(), std::false_type());
         }
     }
     __syncthreads();
+    RB_STAMP(tr, 3);
 
     // ---- integer tile products over the warp's range
     int accm[4][4];
@@ -335,6 +360,7 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
     }
     if (cur >= 0) flush(cur);
     __syncthreads();
+    RB_STAMP(tr, 4);
 
     // ---- epilogue: the CTA's rows are complete: remove the +1 code offset, dequantise, write
     const int T = p.st.terms;

@@ -226,8 +226,10 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
         q.n = n;
         q.kpad = p.kpad;
         q.terms = p.terms_out;
+        int rk = 0;
+        __syncthreads();  // readers of `scratch` in the reductions above are done
         lean_quantize<V>(q, v, scratch, p.xq + (size_t)m * p.terms_out * p.kpad, (size_t)p.kpad,
-                         p.sx_out + (size_t)m * p.terms_out, p.xsum_out + (size_t)m * p.terms_out);
+                         p.sx_out + (size_t)m * p.terms_out, p.xsum_out + (size_t)m * p.terms_out, rk);
     }
     }  // rows of this CTA
 }
