@@ -149,7 +149,9 @@ int rotor_b200_bitlinear_forward(const void* tiles, size_t out, size_t in, const
  *    any stream capture begins.
  *  - Calls share the array and it keeps the last call's contents (what must start at zero
  *    is cleared inside); calls that overlap on the GPU race on it, so keep them ordered.
- *  - Calls no cudaMalloc / cudaFree or other allocating routine. */
+ *  - Calls no cudaMalloc / cudaFree or other allocating routine.
+ *  - A bounded wait that runs out on this path is recorded in a status word at the start of the
+ *    array; rotor_b200_device_status() reads and clears it together with the library's own word. */
 #define ROTOR_B200_STATIC_SCRATCH_BYTES (4u << 20)
 int rotor_b200_bitlinear_static_fits(size_t out, size_t in, size_t m, int terms);
 int rotor_b200_bitlinear_forward_static(const void* tiles, size_t out, size_t in, const float* x,

@@ -43,6 +43,11 @@ class Semantics:
     rope_theta: Optional[float] = None
     causal: bool = False
     eps: float = 1e-6
+    # With int8 activations the glue between the products (norms, residual adds, LM head) is
+    # float32, the dtype the embeddings arrive in.  glue64 runs that glue in float64 instead: a
+    # second, equally valid evaluation of the same model, used by tests to find positions whose
+    # logits hinge on a rounding tie of the quantiser (the two evaluations then disagree).
+    glue64: bool = False
 
 
 REFERENCE = Semantics()
@@ -182,6 +187,17 @@ def bitlinear_float(x, w_int8, scale):
     return y.reshape(*lead, w_int8.shape[0])
 
 
+def int_matmul(q, w_int8):
+    """acc[m, t, o] = sum_k q[m, t, k] * w[o, k], exact int32.  Every partial sum is an integer of
+    magnitude at most 128 * K; below 2^24 all of them are exact in float32 whatever the summation
+    order, so the product can go through BLAS.  Wider layers take the integer einsum."""
+    m, terms, k = q.shape
+    if 128 * k < (1 << 24):
+        accf = q.reshape(m * terms, k).astype(np.float32) @ w_int8.astype(np.float32).T
+        return accf.astype(np.int32).reshape(m, terms, w_int8.shape[0])
+    return np.einsum("mtk,ok->mto", q.astype(np.int32), w_int8.astype(np.int32), optimize=True).astype(np.int32)
+
+
 def bitlinear_int(x, w_int8, scale, terms=1):
     """Quantised BitLinear: per-row n-term int8 activations, exact int32 accumulation
     against the cached int8 weights, then y = (sum_t s_t * acc_t) * scale in float32.
@@ -189,8 +205,7 @@ def bitlinear_int(x, w_int8, scale, terms=1):
     lead = x.shape[:-1]
     flat = np.ascontiguousarray(x.reshape(-1, x.shape[-1]), dtype=np.float32)
     q, s = quantize_rows(flat, terms)
-    w32 = w_int8.astype(np.int32)
-    acc = np.einsum("mtk,ok->mto", q.astype(np.int32), w32, optimize=True).astype(np.int32)
+    acc = int_matmul(q, w_int8)
     y = np.zeros((flat.shape[0], w_int8.shape[0]), dtype=np.float32)
     for t in range(terms):
         y = (y + acc[:, t, :].astype(np.float32) * s[:, t:t + 1]).astype(np.float32)
@@ -310,6 +325,8 @@ def model_forward(model, input_ids, sem: Semantics = REFERENCE, past_kv_cache=No
     if squeeze:
         ids = ids[None, :]
     hcur = model["embed"][ids]
+    if sem.glue64:
+        hcur = hcur.astype(np.float64)
     caches = [] if use_cache else None
     for li, lw in enumerate(model["layers"]):
         past = None if past_kv_cache is None else past_kv_cache[li]

@@ -324,58 +324,65 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
 
 // ---------------------------------------------------------------------------------------
 // The same one-token attention with the slices of one KV head as a thread-block cluster.
-// Grid (n_kv_heads * nsplit, batch), cluster (nsplit, 1, 1), nsplit <= 8, 128 threads.
+// Grid (n_kv_heads * nsplit, batch), cluster (nsplit, 1, 1), nsplit <= 8; one warp per query
+// head of the group (G <= 8 warps), head_dim 64 or 128.
 //
 // Before the programmatic-launch wait a CTA reads the cached length and copies its slice of the
-// K and V rows (written by earlier steps) into shared memory with cp.async; after the wait only
-// the new q / k / v row has to come from the q/k/v product, and scores and weighted V run out of
-// shared memory.  The slices are then merged through distributed shared memory: every CTA leaves
-// (max, sum, weighted V) for the group's heads in its own shared memory, and after a cluster
-// barrier CTA r combines the r-th share of the group's outputs from all slices and writes
-// finished attention rows -- the output projection reads one float row instead of every CTA of
-// it re-merging nsplit partial rows.  Merge arithmetic and order are those of the consumer-side
-// merge (lean_row, LM_ATTN).
+// K and V rows (written by earlier steps) into shared memory with cp.async.  After the wait the
+// CTA whose slice holds the new position rotates the new k, appends k / v to the cache and to
+// the staged rows; every warp fetches and rotates its head's q into registers.  From there a
+// warp works alone: scores with 8 lanes per key (4 keys per pass, q held as four 16-byte pieces
+// per lane), an online softmax over chunks of 32 keys (lane j keeps key j's score), weighted V
+// with 4 output dimensions per lane.  No CTA barrier separates these phases.
+//
+// The slices are merged through distributed shared memory by pushing: every warp stores its
+// (max, sum) to all CTAs of the cluster and its weighted V to the CTA that owns those outputs;
+// after one cluster barrier CTA r combines the r-th share of the group's outputs from its own
+// shared memory and writes finished attention rows -- the output projection reads one float row
+// instead of every CTA of it re-merging nsplit partial rows.
 __device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src)
                  : "memory");
 }
-__device__ __forceinline__ void cluster_barrier() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster(const float* own_smem, unsigned cta) {
+__device__ __forceinline__ uint32_t cluster_addr(const void* own_smem, unsigned cta) {
     uint32_t remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
                  : "=r"(remote)
                  : "r"((uint32_t)__cvta_generic_to_shared(own_smem)), "r"(cta));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
 }
 
 constexpr int AC_MAX_SPLIT = 8;  // portable cluster size
+constexpr int AC_MAX_GROUP = 8;  // query heads per KV head = warps per CTA
 
 __host__ __device__ inline int round4(int v) { return (v + 3) & ~3; }
 
 template <int D>
-__global__ void __launch_bounds__(128) attn_decode_cluster_kernel(const __grid_constant__ AttnDecodeParams p) {
+__global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(const __grid_constant__ AttnDecodeParams p) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int half = D / 2, C4 = D / 4, NCH = D / 32;  // 16-byte chunks per row; chunks per lane of a key's 8 lanes
-    const int tid = threadIdx.x, nthr = blockDim.x;
-    const int G = p.n_heads / p.n_kv_heads, ns = p.nsplit;
-    const int hk = blockIdx.x / ns, sp = blockIdx.x % ns;  // sp is also the rank inside the cluster
+    constexpr int half = D / 2, C4 = D / 4, NCH = D / 32;  // 16-byte pieces per row; pieces per lane of a key's 8 lanes
+    const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
+    const int G = p.n_heads / p.n_kv_heads, ns = p.nsplit;  // blockDim.x == 32 * G
+    const int hk = blockIdx.x / ns, sp = blockIdx.x % ns;   // sp is also the rank inside the cluster
     const int b = blockIdx.y;
     const int dq = p.n_heads * D, dkv = p.n_kv_heads * D;
     const int lcmax = (p.max_seq + ns - 1) / ns;
-    float* q_s = sm;                          // [G][D], pre-scaled by 1/sqrt(D)
-    float* k_new = q_s + G * D;               // [D]
-    float* v_new = k_new + D;                 // [D]
-    float* sc = v_new + D;                    // [G][lcmax]
-    float* o_s = sc + round4(G * lcmax);      // [G][D] weighted V of this slice
-    float* ml_s = o_s + G * D;                // [2][G] slice maximum, slice sum
-    float* Ks = ml_s + round4(2 * G);         // [lcmax][D]
+    const int share = G * D / ns;             // outputs of the group this CTA finishes (a multiple of 4)
+    float* recv_o = sm;                       // [ns][share] weighted V of every slice for this CTA's outputs
+    float* recv_ml = recv_o + ns * share;     // [ns][2 G]   (max, sum) of every slice and head
+    float* Ks = recv_ml + round4(ns * 2 * G); // [lcmax][D]
     float* Vs = Ks + (size_t)lcmax * D;       // [lcmax][D]
     TraceRec tr;
     RB_STAMP(tr, 0);
+    // every CTA of the cluster has started (its shared memory may be written) once this phase completes
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     // ---- before the wait: the cached length (advanced by the previous step's last kernel) and
     // this slice's older cache rows
@@ -399,157 +406,183 @@ __global__ void __launch_bounds__(128) attn_decode_cluster_kernel(const __grid_c
     pdl_trigger();
     RB_STAMP(tr, 2);
 
-    // ---- q of the G heads, and the new k / v of this KV head
-    const float scale = 1.0f / sqrtf((float)D);
     const float* qf = p.qkv_f + (size_t)b * (dq + 2 * dkv);
-    for (int w = tid; w < (G + 1) * half; w += nthr) {
-        const bool is_q = w < G * half;
-        const int hh = is_q ? w / half : 0, i = w % half;
-        const int base = is_q ? (hk * G + hh) * D : dq + hk * D;
-        float a = __ldcg(qf + base + i), c = __ldcg(qf + base + i + half);
-        if (p.rope) {
-            const float2 cs = p.rope[(size_t)pos * half + i];
-            const float ra = a * cs.x - c * cs.y, rc = c * cs.x + a * cs.y;
-            a = ra;
-            c = rc;
+    // ---- the new k / v row: rotate, append to the cache and to the staged rows (owning slice only)
+    if (pos >= t0 && pos < t1) {
+        float* ks_row = Ks + (size_t)(pos - t0) * D;
+        float* vs_row = Vs + (size_t)(pos - t0) * D;
+        const bool keep = pos < p.max_seq;
+        for (int i = tid; i < half; i += nthr) {
+            float a = __ldcg(qf + dq + hk * D + i), c = __ldcg(qf + dq + hk * D + i + half);
+            if (p.rope) {
+                const float2 cs = p.rope[(size_t)pos * half + i];
+                const float ra = a * cs.x - c * cs.y, rc = c * cs.x + a * cs.y;
+                a = ra;
+                c = rc;
+            }
+            ks_row[i] = a;
+            ks_row[i + half] = c;
+            if (keep) {
+                kc[(size_t)pos * D + i] = a;
+                kc[(size_t)pos * D + i + half] = c;
+            }
         }
-        if (is_q) {
-            q_s[hh * D + i] = a * scale;
-            q_s[hh * D + i + half] = c * scale;
-        } else {
-            k_new[i] = a;
-            k_new[i + half] = c;
+        for (int i = tid; i < D; i += nthr) {
+            const float v = __ldcg(qf + dq + dkv + hk * D + i);
+            vs_row[i] = v;
+            if (keep) vc[(size_t)pos * D + i] = v;
         }
     }
-    for (int i = tid; i < D; i += nthr) v_new[i] = __ldcg(qf + dq + dkv + hk * D + i);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    if (pos < p.max_seq && pos >= t0 && pos < t1)
-        for (int i = tid; i < D; i += nthr) {
-            kc[(size_t)pos * D + i] = k_new[i];
-            vc[(size_t)pos * D + i] = v_new[i];
+    // ---- q of this warp's head: lane l8 = lane & 7 holds pieces l8, l8 + 8, ... (four floats each),
+    // pre-scaled by 1/sqrt(D); piece c < C4/2 rotates with piece c + C4/2, both in the same lane
+    const int l8 = lane & 7;
+    float4 q4[NCH];
+    {
+        const float* qh = qf + (size_t)(hk * G + warp) * D;
+#pragma unroll
+        for (int e = 0; e < NCH; ++e) q4[e] = __ldcg(reinterpret_cast<const float4*>(qh) + (8 * e + l8));
+        if (p.rope) {
+#pragma unroll
+            for (int e = 0; e < NCH / 2; ++e) {
+                const float4* cs4 = reinterpret_cast<const float4*>(p.rope + (size_t)pos * half + 4 * (8 * e + l8));
+                const float4 c01 = __ldg(cs4), c23 = __ldg(cs4 + 1);  // (cos, sin) of four consecutive pairs
+                float4& a = q4[e];
+                float4& c = q4[e + NCH / 2];
+                const float4 ra = make_float4(a.x * c01.x - c.x * c01.y, a.y * c01.z - c.y * c01.w,
+                                              a.z * c23.x - c.z * c23.y, a.w * c23.z - c.w * c23.w);
+                const float4 rc = make_float4(c.x * c01.x + a.x * c01.y, c.y * c01.z + a.y * c01.w,
+                                              c.z * c23.x + a.z * c23.y, c.w * c23.z + a.w * c23.w);
+                a = ra;
+                c = rc;
+            }
         }
+        const float scale = 1.0f / sqrtf((float)D);
+#pragma unroll
+        for (int e = 0; e < NCH; ++e) q4[e] = make_float4(q4[e].x * scale, q4[e].y * scale, q4[e].z * scale, q4[e].w * scale);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // staged rows and the new row are visible to every warp
     RB_STAMP(tr, 3);
 
-    // ---- scores of this slice: 8 lanes per key; lane l8 takes the 16-byte chunks l8, l8 + 8, ...
-    // of the key row (consecutive lanes read consecutive chunks of shared memory)
-    const int l8 = tid & 7;
-    for (int tb = t0; tb < t1; tb += nthr / 8) {  // same trip count for every thread (full-warp shuffles)
-        const int t = tb + (tid >> 3);
-        const bool valid = t < t1;
-        float4 kv[NCH];
-#pragma unroll
-        for (int e = 0; e < NCH; ++e) kv[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (valid) {
-            const float* kp = (t == pos) ? k_new : Ks + (size_t)(t - t0) * D;
-#pragma unroll
-            for (int e = 0; e < NCH; ++e) kv[e] = *reinterpret_cast<const float4*>(kp + 4 * (8 * e + l8));
-        }
-        for (int g = 0; g < G; ++g) {
+    // ---- this warp's head over the slice, 32 keys at a time
+    float m_run = -INFINITY, l_run = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);  // output dimensions 4 lane .. 4 lane + 3 (D = 128) or 2 lanes per pair (D = 64)
+    constexpr int OPL = D / 32;                  // output floats per lane
+    for (int c0 = t0; c0 < t1; c0 += 32) {
+        const int nk = min(32, t1 - c0);
+        float my_s = -INFINITY;
+        for (int i = 0; i * 4 < nk; ++i) {  // four keys per pass: key c0 + 4 i + (lane >> 3)
+            const int j = 4 * i + (lane >> 3);
             float s = 0.f;
+            if (j < nk) {
+                const float4* kr = reinterpret_cast<const float4*>(Ks + (size_t)(c0 + j - t0) * D);
 #pragma unroll
-            for (int e = 0; e < NCH; ++e) {
-                const float4 q4 = *reinterpret_cast<const float4*>(q_s + g * D + 4 * (8 * e + l8));
-                s += q4.x * kv[e].x + q4.y * kv[e].y + q4.z * kv[e].z + q4.w * kv[e].w;
+                for (int e = 0; e < NCH; ++e) {
+                    const float4 k4 = kr[8 * e + l8];
+                    s += q4[e].x * k4.x + q4[e].y * k4.y + q4[e].z * k4.z + q4[e].w * k4.w;
+                }
             }
             s += __shfl_xor_sync(0xffffffffu, s, 1);
             s += __shfl_xor_sync(0xffffffffu, s, 2);
             s += __shfl_xor_sync(0xffffffffu, s, 4);
-            if (valid && l8 == 0) sc[g * lcmax + (t - t0)] = s;
+            const float mine = __shfl_sync(0xffffffffu, s, (lane & 3) * 8);  // key 4 i + (lane & 3)
+            if ((lane >> 2) == i) my_s = mine;                               // lane j keeps key j
         }
-    }
-    __syncthreads();
-
-    // ---- softmax statistics of the slice, one warp per head
-    const int warp = tid >> 5, lane = tid & 31, n = t1 - t0;
-    for (int g = warp; g < G; g += nthr / 32) {
-        float mx = -INFINITY;
-        for (int i = lane; i < n; i += 32) mx = fmaxf(mx, sc[g * lcmax + i]);
-        mx = warp_max(mx);
-        float l = 0.f;
-        for (int i = lane; i < n; i += 32) {
-            const float e = __expf(sc[g * lcmax + i] - mx);
-            sc[g * lcmax + i] = e;
-            l += e;
-        }
-        l = warp_sum(l);
-        if (lane == 0) {
-            ml_s[g] = n > 0 ? mx : -INFINITY;
-            ml_s[G + g] = l;
-        }
-    }
-    __syncthreads();
-
-    // ---- weighted V of the slice: thread d owns one output dimension
-    for (int d = tid; d < D; d += nthr) {
-        for (int g0 = 0; g0 < G; g0 += 4) {
-            float o[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int t = t0; t < t1; ++t) {
-                const float vv = (t == pos) ? v_new[d] : Vs[(size_t)(t - t0) * D + d];
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    if (g0 + g < G) o[g] += sc[(g0 + g) * lcmax + (t - t0)] * vv;
+        if (lane >= nk) my_s = -INFINITY;
+        const float m_new = fmaxf(m_run, warp_max(my_s));
+        const float keep = m_run == -INFINITY ? 0.f : __expf(m_run - m_new);
+        const float pr = lane < nk ? __expf(my_s - m_new) : 0.f;
+        l_run = l_run * keep + warp_sum(pr);
+        o = make_float4(o.x * keep, o.y * keep, o.z * keep, o.w * keep);
+        const float* vr = Vs + (size_t)(c0 - t0) * D + OPL * lane;
+#pragma unroll 4
+        for (int j = 0; j < nk; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, pr, j);
+            if constexpr (OPL == 4) {
+                const float4 v4 = *reinterpret_cast<const float4*>(vr + (size_t)j * D);
+                o.x += pj * v4.x;
+                o.y += pj * v4.y;
+                o.z += pj * v4.z;
+                o.w += pj * v4.w;
+            } else {
+                const float2 v2 = *reinterpret_cast<const float2*>(vr + (size_t)j * D);
+                o.x += pj * v2.x;
+                o.y += pj * v2.y;
             }
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-                if (g0 + g < G) o_s[(g0 + g) * D + d] = o[g];
         }
+        m_run = m_new;
     }
     RB_STAMP(tr, 4);
-    cluster_barrier();  // every slice's (max, sum, weighted V) is in its CTA's shared memory
 
-    // ---- merge across the cluster: this CTA finishes outputs [sp * share, (sp + 1) * share) of the group
-    const int share = G * D / ns;  // G * D is a multiple of 32, ns <= 8
+    // ---- push this slice's results to the CTAs that merge them
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // (phase opened at the top of the kernel)
+    {
+        const int oi = warp * D + OPL * lane;      // first output of this lane within the group
+        const int dst = oi / share, off = oi - dst * share;
+        const uint32_t ra = cluster_addr(recv_o + sp * share + off, (unsigned)dst);
+        if constexpr (OPL == 4) {
+            st_cluster_v4(ra, o);
+        } else {
+            st_cluster_f32(ra, o.x);
+            st_cluster_f32(ra + 4, o.y);
+        }
+        if (lane < ns) {
+            const uint32_t rm = cluster_addr(recv_ml + sp * 2 * G + warp, (unsigned)lane);
+            st_cluster_f32(rm, m_run);
+            st_cluster_f32(rm + 4 * G, l_run);
+        }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+
+    // ---- merge: outputs [sp * share, (sp + 1) * share) of the group, from this CTA's own shared memory
     for (int idx = tid; idx < share; idx += nthr) {
         const int oi = sp * share + idx, g = oi / D, d = oi - g * D;
         float f[AC_MAX_SPLIT];
         float M = -INFINITY;
 #pragma unroll
         for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2) {
-            f[s2] = s2 < ns ? ld_cluster(ml_s + g, s2) : -INFINITY;
+            f[s2] = s2 < ns ? recv_ml[s2 * 2 * G + g] : -INFINITY;
             M = fmaxf(M, f[s2]);
         }
         float L = 0.f;
 #pragma unroll
         for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2) {
-            const float ms = f[s2];
-            const float e = ms == -INFINITY ? 0.f : __expf(ms - M);
-            if (s2 < ns) L += ld_cluster(ml_s + G + g, s2) * e;
+            const float e = f[s2] == -INFINITY ? 0.f : __expf(f[s2] - M);
+            if (s2 < ns) L += recv_ml[s2 * 2 * G + G + g] * e;
             f[s2] = e;
         }
         const float inv = 1.0f / L;
         float acc = 0.f;
 #pragma unroll
         for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2)
-            if (s2 < ns) acc += ld_cluster(o_s + g * D + d, s2) * (f[s2] * inv);
+            if (s2 < ns) acc += recv_o[s2 * share + idx] * (f[s2] * inv);
         p.attn_out[(size_t)b * dq + (size_t)(hk * G + g) * D + d] = acc;
     }
-    cluster_barrier();  // no CTA leaves while its shared memory may still be read
     RB_STAMP(tr, 5);
     RB_TRACE_COMMIT(tr, 100);
 }
 
-static size_t attn_cluster_smem(int G, int D, int lcmax) {
-    return ((size_t)2 * G * D + 2 * D + round4(G * lcmax) + round4(2 * G) + 2 * (size_t)lcmax * D) * sizeof(float);
+static size_t attn_cluster_smem(int G, int D, int lcmax, int ns) {
+    return ((size_t)G * D + round4(ns * 2 * G) + 2 * (size_t)lcmax * D) * sizeof(float);
 }
 
 // Whether a generation step of this shape takes the cluster kernel (the slices of one KV head fit a
 // portable cluster and the staged cache slices fit shared memory).
 bool attn_decode_cluster_ok(int n_heads, int n_kv_heads, int head_dim, int max_seq, int nsplit) {
     if (nsplit < 1 || nsplit > AC_MAX_SPLIT || n_kv_heads < 1 || n_heads % n_kv_heads) return false;
-    if (head_dim != 32 && head_dim != 64 && head_dim != 128) return false;
+    if (head_dim != 64 && head_dim != 128) return false;
     const int G = n_heads / n_kv_heads;
-    if ((G * head_dim) % nsplit) return false;
-    return attn_cluster_smem(G, head_dim, (max_seq + nsplit - 1) / nsplit) <= 200 * 1024;
+    if (G > AC_MAX_GROUP || (G * head_dim) % (4 * nsplit)) return false;
+    return attn_cluster_smem(G, head_dim, (max_seq + nsplit - 1) / nsplit, nsplit) <= 200 * 1024;
 }
 
 template <int D>
 static int launch_attn_decode_cluster_d(const AttnDecodeParams& p, int batch, cudaStream_t st) {
     const int G = p.n_heads / p.n_kv_heads;
-    const size_t smem = attn_cluster_smem(G, D, (p.max_seq + p.nsplit - 1) / p.nsplit);
+    const size_t smem = attn_cluster_smem(G, D, (p.max_seq + p.nsplit - 1) / p.nsplit, p.nsplit);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.n_kv_heads * p.nsplit, batch);
-    cfg.blockDim = dim3(128);
+    cfg.blockDim = dim3(32 * G);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -572,7 +605,6 @@ int launch_attn_decode_cluster(const AttnDecodeParams& p, int batch, cudaStream_
     if (!p.qkv_f || !p.attn_out || !attn_decode_cluster_ok(p.n_heads, p.n_kv_heads, p.head_dim, p.max_seq, p.nsplit))
         return ROTOR_B200_ERR_ARG;
     switch (p.head_dim) {
-        case 32: return launch_attn_decode_cluster_d<32>(p, batch, st);
         case 64: return launch_attn_decode_cluster_d<64>(p, batch, st);
         case 128: return launch_attn_decode_cluster_d<128>(p, batch, st);
     }
@@ -595,8 +627,9 @@ static int launch_attn_decode_d(const AttnDecodeParams& p, int batch, cudaStream
     const size_t smem = ((size_t)G * D + 2 * D + (size_t)G * lcmax + 64 + (size_t)p.n_heads * D +
                          2 * (size_t)p.n_heads * p.nsplit) * sizeof(float);
     if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
-    static size_t configured = 48 * 1024;
-    if (smem > configured) {
+    static PerDevice<size_t> once;
+    size_t& configured = once.here();
+    if (smem > 48 * 1024 && smem > configured) {
         RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         configured = 200 * 1024;
     }
@@ -630,9 +663,12 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
     return configure_attn_prefill_tc();
 }
 

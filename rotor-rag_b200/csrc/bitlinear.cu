@@ -184,18 +184,19 @@ __global__ void dequant_kernel(const int32_t* __restrict__ acc, const float* __r
     }
 }
 
-// Device status word shared by every launch of the library in this process.
-static unsigned* g_status = nullptr;
+// Device status word shared by every launch of the library on one device (one word per device).
+static PerDevice<unsigned*> g_status_words;
 static int ensure_status() {
-    if (g_status) return ROTOR_B200_OK;
-    RB_CUDA(cudaMalloc(&g_status, sizeof(unsigned)));
-    RB_CUDA(cudaMemset(g_status, 0, sizeof(unsigned)));
+    unsigned*& w = g_status_words.here();
+    if (w) return ROTOR_B200_OK;
+    RB_CUDA(cudaMalloc(&w, sizeof(unsigned)));
+    RB_CUDA(cudaMemset(w, 0, sizeof(unsigned)));
     return ROTOR_B200_OK;
 }
 
-int g_use_pdl = 0;  // programmatic dependent launch for the kernels that call pdl_wait()
+int g_use_pdl = 1;  // programmatic dependent launch for the kernels that call pdl_wait()
 
-unsigned* library_status_word() { return ensure_status() ? nullptr : g_status; }
+unsigned* library_status_word() { return ensure_status() ? nullptr : g_status_words.here(); }
 
 template <int WARPS, int UMAX, bool USE_MMA, int NCOL>
 static int launch_acc(const AccParams& p, int nrt, int ksplit, cudaStream_t st) {
@@ -203,7 +204,8 @@ static int launch_acc(const AccParams& p, int nrt, int ksplit, cudaStream_t st) 
     const size_t smem = 16 + WARPS * 128 * 4 + (size_t)p.ncols * (p.kt_per_split * TILE_K + XS_PAD);
     if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     if (smem > 48 * 1024) {
-        static size_t configured = 0;
+        static PerDevice<size_t> once;  // per instantiation and device
+        size_t& configured = once.here();
         if (smem > configured) {
             RB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             configured = 200 * 1024;
@@ -309,7 +311,7 @@ int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* x
         p.xq = xq + (size_t)c0 * kpad;
         p.xsum = xsum + c0;
         p.acc = acc + (size_t)c0 * out;
-        p.status = g_status;
+        p.status = g_status_words.here();
         p.out = (int)out;
         p.nkt = nkt;
         p.kt_per_split = plan.kt_per_split;
@@ -354,7 +356,7 @@ int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int
         p.xq = xq + c0 * kpad;
         p.xsum = xsum + c0;
         p.acc = acc + c0 * out;
-        p.status = g_status;
+        p.status = g_status_words.here();
         p.out = (int)out;
         p.nkt = nkt;
         p.kt_per_split = (nkt + ksplit - 1) / ksplit;
@@ -432,18 +434,20 @@ int rotor_b200_bitlinear_forward(const void* tiles, size_t out, size_t in, const
  *  - No cudaMalloc, cudaFree or other allocating routine is called on this path. */
 static __device__ __align__(256) unsigned char g_static_scratch[ROTOR_B200_STATIC_SCRATCH_BYTES];
 
+static PerDevice<unsigned char*> g_static_addr;  // device address of the array, once looked up on that device
+
 static int static_scratch_address(unsigned char** out) {
-    static unsigned char* addr[64] = {nullptr};
     int dev = -1;
     RB_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return ROTOR_B200_ERR_ARG;
-    if (!addr[dev]) {
+    if (dev < 0 || dev >= RB_MAX_DEVICES) return ROTOR_B200_ERR_ARG;
+    unsigned char*& addr = g_static_addr.v[dev];
+    if (!addr) {
         // g_static_scratch names the array in device code only; host code must ask for its address
         void* p = nullptr;
         RB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-        addr[dev] = static_cast<unsigned char*>(p);
+        addr = static_cast<unsigned char*>(p);
     }
-    *out = addr[dev];
+    *out = addr;
     return ROTOR_B200_OK;
 }
 
@@ -479,7 +483,8 @@ int rotor_b200_bitlinear_forward_static(const void* tiles, size_t out, size_t in
     int32_t* xsum = (int32_t*)w;
     w += al256(nc * 4);
     int32_t* acc = (int32_t*)w;
-    RB_CUDA(cudaMemsetAsync(status, 0, sizeof(unsigned), st));  // left over from whoever used the array last
+    // the status word starts at zero (the array is zero-initialised when the library is loaded) and is
+    // cleared only by rotor_b200_device_status(), which reads it: a timed-out wait is never lost
     rc = rotor_b200_quantize_rows(x, m, in, terms, xq, sx, xsum, stream);
     if (rc) return rc;
     const int nkt = (int)(kpad / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
@@ -537,13 +542,21 @@ int rotor_b200_ternary_matmul_host(const void* tiles, const float* scales_host, 
     return ROTOR_B200_OK;
 }
 
-/* Reads and clears the device status word that bounded waits write to. */
+/* Reads and clears the status words of the current device that bounded waits write to: the
+ * library's own word and the one at the start of the fixed scratch array of
+ * rotor_b200_bitlinear_forward_static (once that entry point has run on this device).  Allocates
+ * nothing. */
 int rotor_b200_device_status(void) {
-    if (!g_status) return ROTOR_B200_OK;
-    unsigned v = 0;
-    RB_CUDA(cudaMemcpy(&v, g_status, sizeof(v), cudaMemcpyDeviceToHost));
-    if (v) RB_CUDA(cudaMemset(g_status, 0, sizeof(v)));
-    return (int)v;
+    unsigned v = 0, vs = 0;
+    if (unsigned* w = g_status_words.here()) {
+        RB_CUDA(cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost));
+        if (v) RB_CUDA(cudaMemset(w, 0, sizeof(v)));
+    }
+    if (unsigned char* a = g_static_addr.here()) {
+        RB_CUDA(cudaMemcpy(&vs, a, sizeof(vs), cudaMemcpyDeviceToHost));
+        if (vs) RB_CUDA(cudaMemset(a, 0, sizeof(vs)));
+    }
+    return (int)(v ? v : vs);
 }
 
 }  // extern "C"

@@ -19,6 +19,20 @@ __host__ __device__ inline size_t opad_of(size_t out) { return round_up(out, TIL
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// State kept once per device: a process may drive several GPUs, and function attributes
+// (shared-memory opt-in), the status word and device properties belong to one of them.
+constexpr int RB_MAX_DEVICES = 64;
+inline int current_device() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= RB_MAX_DEVICES) d = 0;
+    return d;
+}
+template <typename T>
+struct PerDevice {
+    T v[RB_MAX_DEVICES] = {};
+    T& here() { return v[current_device()]; }
+};
+
 // Kernel launches issued by this library in this process (graph replays add the launches
 // the graph holds).  Defined in format.cu.
 extern unsigned long long g_launch_count;

@@ -31,7 +31,10 @@ __global__ void __launch_bounds__(FG_THREADS, DEEP ? 1 : 2) fused_gemv_kernel(co
     RB_STAMP(tr, 0);
     const ProductCtx c = product_ctx(p, smem_raw);
     uint4 wv[FG_U];
-    product_prefetch(p, c, wv);
+    if constexpr (DEEP)
+        product_prefetch(p, c, wv);
+    else
+        product_stage(p, c);
     if constexpr (!WIDE) lean_prefetch(p.st);
     for (int e = threadIdx.x; e < c.slots * 128; e += blockDim.x) c.merge[e] = 0;
     RB_STAMP(tr, 1);
@@ -43,26 +46,30 @@ __global__ void __launch_bounds__(FG_THREADS, DEEP ? 1 : 2) fused_gemv_kernel(co
     RB_TRACE_COMMIT(tr, p.st.mode * 10 + p.halves);
 }
 
-static int g_sm_count = 0;
+static PerDevice<int> g_sm_counts;
 static int sm_count() {
-    if (!g_sm_count) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count <= 0)
-            g_sm_count = 148;
+    int& n = g_sm_counts.here();
+    if (!n) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, current_device()) != cudaSuccess || n <= 0)
+            n = 148;
     }
-    return g_sm_count;
+    return n;
 }
 
 template <bool USE_MMA, int NCOL, bool WIDE, bool DEEP, bool TP>
 static int launch_fused_tp(const FusedGemvParams& p, int grid, cudaStream_t st) {
-    static bool configured = false;  // each variant raises its own shared-memory limit once
+    static PerDevice<bool> once;  // each variant raises its own shared-memory limit once per device
+    bool& configured = once.here();
     if (!configured) {
         RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<USE_MMA, NCOL, WIDE, DEEP, TP>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        // the largest shared-memory split for every variant: kernels of a step share SMs, and a CTA
+        // whose request does not fit the split left by its neighbour waits for the SM to drain
+        RB_CUDA(cudaFuncSetAttribute(fused_gemv_kernel<USE_MMA, NCOL, WIDE, DEEP, TP>,
+                                     cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured = true;
     }
-    const size_t smem = fused_smem(p);
+    const size_t smem = fused_smem(p, !DEEP);
     if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -118,7 +125,7 @@ bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int halves
     p.st.mode = merge_weights ? LM_ATTN : LM_ADD;
     p.st.n_heads = merge_weights;
     p.st.nsplit = 1;
-    return fused_smem(p) <= 160 * 1024;
+    return fused_smem(p, false) <= 160 * 1024;
 }
 
 int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int rows, const LeanStage& stage, float* y,
@@ -142,7 +149,7 @@ int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int 
         if (p.cols == 2) return launch_fused<false, 2, true, true>(p, grid, st);
         return launch_fused<true, 1, true, true>(p, grid, st);
     }
-    if (tiles_per_warp >= 16 || !fused_shallow_fits(p.st)) {
+    if (tiles_per_warp >= 16 || !fused_shallow_fits(p.st) || fused_stage_bytes(p) > FG_STAGE_MAX) {
         if (p.cols == 1) return launch_fused<false, 1, false, true>(p, grid, st);
         if (p.cols == 2) return launch_fused<false, 2, false, true>(p, grid, st);
         return launch_fused<true, 1, false, true>(p, grid, st);

@@ -122,7 +122,8 @@ int configure_gemm_mma() {
 
 int launch_gemm_mma(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
                     int32_t* acc, cudaStream_t st) {
-    static bool configured = false;
+    static PerDevice<bool> once;
+    bool& configured = once.here();
     if (!configured) {
         int rc = configure_gemm_mma();
         if (rc) return rc;

@@ -294,7 +294,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode = nullptr;
-static bool g_tc5_ready = false;
+static PerDevice<bool> g_tc5_ready;
 
 // Shapes this kernel takes: enough tokens to be worth its tile, 16-byte aligned operands.
 bool gemm_tcgen05_supported(size_t out, size_t in, int ncols, const void* xq) {
@@ -306,7 +306,7 @@ bool gemm_tcgen05_supported(size_t out, size_t in, int ncols, const void* xq) {
 }
 
 int configure_gemm_tcgen05() {
-    if (g_tc5_ready) return ROTOR_B200_OK;
+    if (g_tc5_ready.here()) return ROTOR_B200_OK;
     cudaDriverEntryPointQueryResult q;
     void* fn = nullptr;
     RB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
@@ -314,7 +314,7 @@ int configure_gemm_tcgen05() {
     g_encode = (EncodeTiledFn)fn;
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<256>::SMEM));
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<64>::SMEM));
-    g_tc5_ready = true;
+    g_tc5_ready.here() = true;
     return ROTOR_B200_OK;
 }
 
@@ -342,11 +342,10 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return ROTOR_B200_ERR_CUDA;
     const int tok_tiles = (ncols + 255) / 256, rows = p.nrt * TILE_ROWS;
-    static int sms = 0;
+    static PerDevice<int> sm_counts;
+    int& sms = sm_counts.here();
     if (!sms) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, current_device()) != cudaSuccess || sms <= 0)
             sms = 148;
     }
     if (tok_tiles * ((rows + 255) / 256) < sms) {  // 256-row tiles would leave SMs idle

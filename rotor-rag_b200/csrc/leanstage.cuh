@@ -181,20 +181,55 @@ __device__ __forceinline__ void lean_prefetch(const LeanStage& p) {
     }
 }
 
+// Four values -> four int8 in one word: q = clip(rint(v / s), -128, 127) with the exact IEEE quotient
+// (v * (1/s) is within 2e-5 of v / s for |v / s| <= 127, so the multiply decides unless it lands
+// within 1e-4 of a tie), packed with
+// the saturating pack instruction.  `lsum` gains the four integers (one dp4a).  With RESIDUAL the
+// values are replaced by v - q * s (float32, one rounding per operation) for the next term.
+template <bool RESIDUAL>
+__device__ __forceinline__ int quant4_pack(float4& v, float s, float rs, int& lsum) {
+    const float r0 = v.x * rs, r1 = v.y * rs, r2 = v.z * rs, r3 = v.w * rs;
+    float q0 = rintf(r0), q1 = rintf(r1), q2 = rintf(r2), q3 = rintf(r3);
+    const float dm = fmaxf(fmaxf(fabsf(r0 - q0), fabsf(r1 - q1)), fmaxf(fabsf(r2 - q2), fabsf(r3 - q3)));
+    if (dm > 0.4999f) {  // rare: some product is close to a tie, take the true quotients
+        q0 = rintf(__fdiv_rn(v.x, s));
+        q1 = rintf(__fdiv_rn(v.y, s));
+        q2 = rintf(__fdiv_rn(v.z, s));
+        q3 = rintf(__fdiv_rn(v.w, s));
+    }
+    if (RESIDUAL) {
+        q0 = fminf(fmaxf(q0, -128.f), 127.f);
+        q1 = fminf(fmaxf(q1, -128.f), 127.f);
+        q2 = fminf(fmaxf(q2, -128.f), 127.f);
+        q3 = fminf(fmaxf(q3, -128.f), 127.f);
+        v.x = __fsub_rn(v.x, __fmul_rn(q0, s));
+        v.y = __fsub_rn(v.y, __fmul_rn(q1, s));
+        v.z = __fsub_rn(v.z, __fmul_rn(q2, s));
+        v.w = __fsub_rn(v.w, __fmul_rn(q3, s));
+    }
+    const int i0 = __float2int_rn(q0), i1 = __float2int_rn(q1), i2 = __float2int_rn(q2), i3 = __float2int_rn(q3);
+    int hi, packed;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(i3), "r"(i2), "r"(0));       // bytes: i2, i3
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed) : "r"(i1), "r"(i0), "r"(hi));  // i0, i1, i2, i3
+    lsum = __dp4a(packed, 0x01010101, lsum);
+    return packed;
+}
+
 // Absmax int8 quantiser over the register row: term t of the row goes to xq + t*tstride
 // (shared memory, zero padded to kpad), its scale and sum to sx[t] / xsum[t] (shared).
 // Same results as quantize_row_from_smem.  Requires kpad <= 4 * LEAN_V * blockDim.x; sx / xsum are
-// complete after the next CTA barrier.
-template <int LEAN_V>
+// complete after the next CTA barrier.  ONE_TERM: p.terms is 1 (the loop and the residual drop out).
+template <int LEAN_V, bool ONE_TERM = false>
 __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LEAN_V], float* scratch, int8_t* xq,
                                               size_t tstride, float* sx, int* xsum, int& rk, int m = 0,
                                               bool writer = false, const XchScalarDev* x = nullptr) {
     const int n4 = p.n >> 2, k4 = p.kpad >> 2, bd = blockDim.x;
-    for (int t = 0; t < p.terms; ++t) {
+    const int terms = ONE_TERM ? 1 : p.terms;
+    for (int t = 0; t < terms; ++t) {
         float mx = 0.f;
 #pragma unroll
         for (int j = 0; j < LEAN_V; ++j) mx = fmaxf(mx, amax4(v[j]));
-        if (threadIdx.x == 0) xsum[t] = 0;  // ordered before the atomics below by the reduction's barriers
+        if (threadIdx.x == 0) xsum[t] = 0;  // ordered before the atomics below by the reduction's barrier
         mx = block_max_alt(mx, scratch, rk);
         if (x && p.xi_max && t == 0) mx = xch_scalar(*x, p.xi_max - 1, m, mx, true, writer, scratch);
         const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
@@ -205,19 +240,8 @@ __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LE
             const int g = threadIdx.x + j * bd;
             if (g < k4) {
                 int packed = 0;
-                if (g < n4) {
-                    const float q0 = exact_quant(v[j].x, s, rs), q1 = exact_quant(v[j].y, s, rs);
-                    const float q2 = exact_quant(v[j].z, s, rs), q3 = exact_quant(v[j].w, s, rs);
-                    const int i0 = (int)q0, i1 = (int)q1, i2 = (int)q2, i3 = (int)q3;
-                    packed = (i0 & 0xff) | ((i1 & 0xff) << 8) | ((i2 & 0xff) << 16) | ((i3 & 0xff) << 24);
-                    lsum += i0 + i1 + i2 + i3;
-                    if (t + 1 < p.terms) {
-                        v[j].x = __fsub_rn(v[j].x, __fmul_rn(q0, s));
-                        v[j].y = __fsub_rn(v[j].y, __fmul_rn(q1, s));
-                        v[j].z = __fsub_rn(v[j].z, __fmul_rn(q2, s));
-                        v[j].w = __fsub_rn(v[j].w, __fmul_rn(q3, s));
-                    }
-                }
+                if (g < n4) packed = (!ONE_TERM && t + 1 < terms) ? quant4_pack<true>(v[j], s, rs, lsum)
+                                                                  : quant4_pack<false>(v[j], s, rs, lsum);
                 *reinterpret_cast<int*>(xq + (size_t)t * tstride + (size_t)g * 4) = packed;
             }
         }

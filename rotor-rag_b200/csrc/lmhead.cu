@@ -67,7 +67,8 @@ template <int NROWS>
 static int launch_lm(const LmHeadParams& p, int row0, cudaStream_t st) {
     const size_t smem = (size_t)NROWS * p.d * sizeof(float);
     if (smem > 48 * 1024) {
-        static bool configured = false;
+        static PerDevice<bool> once;
+        bool& configured = once.here();
         if (!configured) {
             RB_CUDA(cudaFuncSetAttribute(lmhead_kernel<NROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          200 * 1024));

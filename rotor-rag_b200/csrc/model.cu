@@ -1336,7 +1336,8 @@ int rotor_b200_ffn_forward(const rotor_b200_model_config* cfg, const rotor_b200_
             Carve cv{(unsigned char*)workspace, 0};
             carve_ctx(c, cv, (size_t)rows);
             if (cv.off > workspace_bytes) return ROTOR_B200_ERR_WORKSPACE;
-            static bool configured = false;
+            static PerDevice<bool> once;
+            bool& configured = once.here();
             if (!configured) {
                 RB_TRY(configure_fused_gemv());
                 configured = true;

@@ -1,6 +1,6 @@
 // Device body of the generation-step BitLinear product (see fused.cu): what runs before the
-// programmatic-launch wait (tile ranges, first weight tiles, L2 prefetch) and what runs after it
-// (prologue, tile products, epilogue).
+// programmatic-launch wait (tile ranges, the weight tiles on their way into shared memory or
+// registers) and what runs after it (prologue, tile products, epilogue).
 #pragma once
 #include "gemv_core.cuh"
 #include "leanstage.cuh"
@@ -9,14 +9,17 @@
 
 namespace rb {
 
-// 512 threads per CTA.  The shallow variant (small matrices, a few weight tiles per warp) is held
-// to 64 registers so that two CTAs fit on an SM: the next kernel of the step becomes resident
-// while this one runs and has its first tiles in registers when its wait returns.  The deep
-// variant (large matrices) takes 128 registers for its pipelined tile loop.
+// 512 threads per CTA.  The shallow variant (small matrices: the CTA's whole share of the weights
+// fits in shared memory) is held to 64 registers and FG_STAGE_MAX bytes of staged tiles so that two
+// CTAs fit on an SM: the next kernel of the step becomes resident while this one runs and copies
+// its tiles into shared memory (cp.async) before its wait returns, so the weight stream of a step
+// overlaps the prologues and epilogues of the kernels before it.  The deep variant (large
+// matrices) takes 128 registers and streams its tiles through a register pipeline.
 constexpr int FG_THREADS = 512;
 constexpr int FG_WARPS = FG_THREADS / 32;
 constexpr int FG_U = 4;        // weight tiles in flight per warp
-constexpr int FG_L2_AHEAD = 12;  // further tiles per warp pulled into L2 before the wait
+constexpr int FG_L2_AHEAD = 12;  // deep variant: further tiles per warp pulled into L2 before the wait
+constexpr size_t FG_STAGE_MAX = 96 * 1024;  // shallow variant: most tile bytes a CTA stages
 constexpr int FG_V = 4;        // float4 groups per thread in the register prologue: input width <= 8192
 constexpr int FG_V_NARROW = 2; // shallow variant, stages that hold four arrays per group: width <= 4096
 
@@ -51,12 +54,18 @@ __host__ __device__ inline bool fused_shallow_fits(const LeanStage& st) {
     return st.n <= 4 * (st.mode == LM_PLAIN ? FG_V : FG_V_NARROW) * FG_THREADS;
 }
 
-// Shared memory one product needs.
-inline size_t fused_smem(const FusedGemvParams& p) {
-    const size_t xs = (size_t)p.cols * (p.nkt * TILE_K + XS_PAD);
+// Bytes of weight tiles the largest CTA share holds (what the shallow variant stages).
+inline size_t fused_stage_bytes(const FusedGemvParams& p) {
+    return (size_t)p.upc * p.halves * p.nkt * TILE_BYTES;
+}
+
+// Shared memory one product needs; `staged`: the shallow variant, which keeps its tiles there.
+inline size_t fused_smem(const FusedGemvParams& p, bool staged) {
+    const size_t xs = round_up((size_t)p.cols * (p.nkt * TILE_K + XS_PAD), 16);
     const size_t aux = p.st.mode == LM_ATTN ? 2 * (size_t)p.st.n_heads * p.st.nsplit : 0;
     const size_t wide = fused_wide(p.st) ? (size_t)p.st.n : 0;
-    return xs + (size_t)p.upc * p.halves * 512 + (64 + aux + wide) * sizeof(float);
+    const size_t fixed = xs + (size_t)p.upc * p.halves * 512 + round_up((64 + aux + wide) * sizeof(float), 16);
+    return fixed + (staged ? fused_stage_bytes(p) : 0);
 }
 
 // Fills the parameter block of one product for a grid of `grid` CTAs.  out: output rows per
@@ -98,6 +107,7 @@ struct ProductCtx {
     int* merge;
     float* scratch;
     float* aux;
+    uint4* wt;  // staged tiles (shallow variant): [half][unit - u0][kt][32]
     int xs_stride, slots, u0, u1, w0, w1;
 };
 
@@ -108,18 +118,21 @@ __device__ __forceinline__ ProductCtx product_ctx(const FusedGemvParams& p, unsi
     c.xs_stride = kpad + XS_PAD;
     c.slots = p.upc * p.halves;
     c.xs = reinterpret_cast<int8_t*>(smem_raw);                                      // [cols][xs_stride]
-    c.merge = reinterpret_cast<int*>(smem_raw + (size_t)p.cols * c.xs_stride);       // [slots][128]
+    c.merge = reinterpret_cast<int*>(smem_raw + round_up((size_t)p.cols * c.xs_stride, 16));  // [slots][128]
     c.scratch = reinterpret_cast<float*>(c.merge + c.slots * 128);                   // [64]
     c.aux = c.scratch + 64;                                                          // attention merge weights,
                                                                                      // or the staged wide row
+    const size_t auxn = p.st.mode == LM_ATTN ? 2 * (size_t)p.st.n_heads * p.st.nsplit : 0;
+    c.wt = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(c.scratch) +
+                                    round_up((64 + auxn) * sizeof(float), 16));
     // units (row tiles / row-tile pairs) of this CTA, and the warp's share of their tiles
     // (32-bit arithmetic: units * gridDim.x stays far below 2^31)
     c.u0 = (int)((unsigned)p.units * blockIdx.x / gridDim.x);
     c.u1 = (int)((unsigned)p.units * (blockIdx.x + 1) / gridDim.x);
-    const int ntile = (c.u1 - c.u0) * p.halves * p.nkt;  // local tile index = ((u-u0)*halves + half)*nkt + kt
-    const int nw = blockDim.x >> 5;
-    c.w0 = (int)((unsigned)ntile * (unsigned)warp / (unsigned)nw);
-    c.w1 = (int)((unsigned)ntile * (unsigned)(warp + 1) / (unsigned)nw);
+    // local tile index: deep variant ((u-u0)*halves + half)*nkt + kt, shallow (half*(u1-u0) + u-u0)*nkt + kt
+    const int ntile = (c.u1 - c.u0) * p.halves * p.nkt;
+    c.w0 = ntile * warp / FG_WARPS;
+    c.w1 = ntile * (warp + 1) / FG_WARPS;
     return c;
 }
 
@@ -131,7 +144,21 @@ __device__ __forceinline__ const uint4* product_tile_ptr(const FusedGemvParams& 
     return p.tiles + (rt * p.nkt + kt) * 32 + lane;
 }
 
-// Requests the warp's first FG_U weight tiles and pulls up to FG_L2_AHEAD more into L2
+// Shallow variant: copies the CTA's tiles into shared memory, one contiguous span per half
+// (constants: may run before the activations this product consumes exist).  Completion:
+// cp.async.wait_group 0 by every thread, then a CTA barrier.
+__device__ __forceinline__ void product_stage(const FusedGemvParams& p, const ProductCtx& c) {
+    const int count = (c.u1 - c.u0) * p.nkt * 32;  // 16-byte pieces per half
+    for (int h = 0; h < p.halves; ++h) {
+        const uint4* src = p.tiles + ((size_t)h * p.units + c.u0) * p.nkt * 32;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(c.wt + (size_t)h * count);
+        for (int i = threadIdx.x; i < count; i += FG_THREADS)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + i) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// Deep variant: requests the warp's first FG_U weight tiles and pulls up to FG_L2_AHEAD more into L2
 // (constants: may run before the activations this product consumes exist).
 __device__ __forceinline__ void product_prefetch(const FusedGemvParams& p, const ProductCtx& c, uint4 (&wv)[FG_U]) {
 #pragma unroll
@@ -159,7 +186,6 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
     float* scratch = c.scratch;
     float* aux = c.aux;
     const int xs_stride = c.xs_stride, u0 = c.u0, u1 = c.u1, w0 = c.w0, w1 = c.w1;
-    auto tile_ptr = [&](int lt) { return product_tile_ptr(p, c, lt); };
 
     // ---- prologue: activation rows -> int8 in shared memory
     const bool writer = blockIdx.x == 0;
@@ -205,11 +231,14 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         auto rows = [&](auto vtag, auto plain_tag) {
             constexpr int V = decltype(vtag)::value;
             constexpr bool PLAIN = decltype(plain_tag)::value;
-            for (int m = 0; m < p.rows; ++m) {
+            constexpr bool ONE = NCOL == 1 && !USE_MMA;  // one activation column: one row of one term
+            const int nrows = ONE ? 1 : p.rows, terms = ONE ? 1 : p.st.terms;
+            for (int m = 0; m < nrows; ++m) {
                 float4 v[V];
                 lean_row<V, PLAIN>(p.st, m, v, scratch, aux, writer, rk, x);
-                lean_quantize<V>(p.st, v, scratch, xs + (size_t)m * p.st.terms * xs_stride, (size_t)xs_stride,
-                                 s_sx + m * p.st.terms, s_xsum + m * p.st.terms, rk, m, writer, x);
+                RB_STAMP(tr, 6);
+                lean_quantize<V, ONE>(p.st, v, scratch, xs + (size_t)m * terms * xs_stride, (size_t)xs_stride,
+                                      s_sx + m * terms, s_xsum + m * terms, rk, m, writer, x);
             }
         };
         if constexpr (DEEP) {
@@ -221,6 +250,7 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
                 rows(std::integral_constant<int, FG_V_NARROW>(), std::false_type());
         }
     }
+    if constexpr (!DEEP) asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's staged tiles
     __syncthreads();
     RB_STAMP(tr, 3);
 
@@ -338,43 +368,50 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
             }
         }
     } else {
-        for (int base = w0; base < w1; base += FG_U) {
-#pragma unroll
-            for (int u = 0; u < FG_U; ++u) {
-                const int lt = base + u;
-                if (lt < w1) {
-                    const int slot = lt / p.nkt, kt = lt - slot * p.nkt;
-                    if (slot != cur) {  // warp-uniform
-                        if (cur >= 0) flush(cur);
-                        clear();
-                        cur = slot;
-                    }
-                    const uint32_t pw[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-                    tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, kt * TILE_K + 32 * t, g, p.cols, accm, accd);
-                }
+        // tiles come out of shared memory in local order; (slot, kt) advance by counting
+        int slot = w0 / p.nkt, kt = w0 - slot * p.nkt;
+        const uint4* wp = c.wt + (size_t)w0 * 32 + lane;
+#pragma unroll 2
+        for (int lt = w0; lt < w1; ++lt) {
+            const uint4 w4 = *wp;
+            wp += 32;
+            const uint32_t pw[4] = {w4.x, w4.y, w4.z, w4.w};
+            tile_mac<USE_MMA, NCOL>(pw, xs, xs_stride, kt * TILE_K + 32 * t, g, p.cols, accm, accd);
+            cur = slot;
+            if (++kt == p.nkt) {  // warp-uniform: the row tile is complete
+                flush(slot);
+                clear();
+                kt = 0;
+                ++slot;
+                cur = -1;
             }
-#pragma unroll
-            for (int u = 0; u < FG_U; ++u)
-                if (base + FG_U + u < w1) wv[u] = ld_stream_v4(tile_ptr(base + FG_U + u));
         }
     }
+    RB_STAMP(tr, 7);
     if (cur >= 0) flush(cur);
     __syncthreads();
     RB_STAMP(tr, 4);
 
     // ---- epilogue: the CTA's rows are complete: remove the +1 code offset, dequantise, write
-    const int T = p.st.terms;
-    for (int e = threadIdx.x; e < (u1 - u0) * 16 * p.rows; e += blockDim.x) {
-        const int m = e % p.rows, rl = (e / p.rows) & 15, lu = e / (p.rows * 16);
+    constexpr bool ONE = NCOL == 1 && !USE_MMA;
+    const int T = ONE ? 1 : p.st.terms, nrows = ONE ? 1 : p.rows;
+    for (int e = threadIdx.x; e < (u1 - u0) * 16 * nrows; e += blockDim.x) {
+        int m = 0, q = e;
+        if (!ONE) {
+            q = e / nrows;
+            m = e - q * nrows;
+        }
+        const int rl = q & 15, lu = q >> 4;
         const int orow = (u0 + lu) * TILE_ROWS + rl;
         if (orow >= p.out) continue;
         if (TP && p.part) {  // exact partial sum of this rank's columns; summed across ranks and dequantised later
-            p.part[(size_t)m * p.out + orow] = merge[lu * 128 + rl * 8 + m] - s_xsum[m];
+            p.part[(size_t)m * p.out + orow] = merge[lu * 128 + rl * 8 + m] - s_xsum[m];  // halves == 1
             continue;
         }
         float val[2] = {0.f, 0.f};
         for (int half = 0; half < p.halves; ++half) {
-            const int* src = merge + (lu * p.halves + half) * 128 + rl * 8 + m * T;
+            const int slot = DEEP ? lu * p.halves + half : half * (u1 - u0) + lu;
+            const int* src = merge + slot * 128 + rl * 8 + m * T;
             float f = 0.f;
             for (int tt = 0; tt < T; ++tt) f += (float)(src[tt] - s_xsum[m * T + tt]) * s_sx[m * T + tt];
             val[half] = f;
@@ -383,11 +420,11 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         if (p.halves == 2) {
             const float gt = val[0] * p.scale[0], up = val[1] * p.scale[1];
             if (p.ffn_act == ROTOR_B200_FFN_RELU2) {
-                const float q = fmaxf(gt, 0.f);
-                r = q * q * up;
+                const float q2 = fmaxf(gt, 0.f);
+                r = q2 * q2 * up;
             } else {
-                const float c = fminf(fmaxf(up, -20.f), 20.f);
-                r = gt * (c / (1.f + expf(-c)));
+                const float c2 = fminf(fmaxf(up, -20.f), 20.f);
+                r = gt * (c2 / (1.f + expf(-c2)));
             }
         } else {
             r = val[0] * (orow < p.seg1 ? p.scale[0] : (orow < p.seg2 ? p.scale[1] : p.scale[2]));

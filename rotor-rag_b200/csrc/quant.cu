@@ -27,7 +27,8 @@ extern "C" int rotor_b200_quantize_rows(const float* x, size_t m, size_t k, int 
     RB_REQUIRE(((uintptr_t)xq & 3) == 0);
     const size_t smem = 64 * 4 + k * 4;
     if (smem > 48 * 1024) {
-        static bool configured = false;
+        static PerDevice<bool> once;
+        bool& configured = once.here();
         if (!configured) {
             RB_CUDA(cudaFuncSetAttribute(quantize_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          64 * 4 + 49152 * 4));

@@ -262,8 +262,10 @@ static int launch_one(const VecStageParams& p, int rows, cudaStream_t st) {
     const size_t smem = pieces * (size_t)p.n * sizeof(int);
     if (from_acc && !no_pf && smem <= 200 * 1024) {
         auto* k = row_stage_kernel<V, RESID, TH, true>;
-        static size_t configured = 0;  // per instantiation
-        static int sms = 0;
+        static PerDevice<size_t> once;  // per instantiation and device
+        static PerDevice<int> sm_counts;
+        size_t& configured = once.here();
+        int& sms = sm_counts.here();
         if (smem > configured) {
             RB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             configured = smem;

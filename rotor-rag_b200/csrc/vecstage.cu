@@ -29,8 +29,9 @@ int launch_vec_stage(const VecStageParams& p, int rows, cudaStream_t st) {
     if (row_stage_supported(p, rows)) return launch_row_stage(p, rows, st);  // many rows: register-resident kernel
     const size_t smem = 64 * 4 + (size_t)p.n * 4 +
                         (p.mode == VS_ATTN ? 2 * (size_t)p.n_heads * p.nsplit * 4 : 0);  // merge weights behind the row
-    static size_t configured = 48 * 1024;
-    if (smem > configured) {
+    static PerDevice<size_t> once;
+    size_t& configured = once.here();
+    if (smem > 48 * 1024 && smem > configured) {
         if (smem > 200 * 1024) return ROTOR_B200_ERR_SHAPE;
         RB_CUDA(cudaFuncSetAttribute(vec_stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         configured = 200 * 1024;

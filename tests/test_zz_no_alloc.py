@@ -9,6 +9,10 @@ results as the workspace-taking entry point, on two calls in a row that reuse th
 with different shapes, plus the size limit.  This file sorts last on purpose, so that a
 run that stops at the first failure has already run every other test.
 """
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 
@@ -53,6 +57,47 @@ def test_static_scratch_matches_workspace_entry_point_twice():
     want, got = _forward_both(abi, ops, torch, w1, x1, 1, 0.016, abi.VARIANT_AUTO)
     assert np.array_equal(got, want)
     abi.device_status()
+
+
+_FRESH = r"""
+import sys
+import numpy as np, torch
+from oracle import bitlinear_np as O
+from rotor_b200 import abi, ops
+rng = np.random.default_rng(7)
+w = O.synth_ternary(rng, 6912, 2560)
+x = rng.standard_normal((1, 2560)).astype(np.float32)
+tiles = ops.int8_to_tiles(w)                      # load-time repack; no layer forward has run yet
+xd = ops.to_device(x, torch.float32)
+y = torch.empty((1, 6912), dtype=torch.float32, device="cuda")
+def call():
+    st = abi.lib.rotor_b200_bitlinear_forward_static(tiles.data_ptr(), 6912, 2560, xd.data_ptr(), 1, 1, 0.016, None,
+                                                     y.data_ptr(), abi.VARIANT_DP4A, abi.stream())
+    assert st == 0, st
+    torch.cuda.synchronize()
+call()                                            # first forward of the process: looks the array up, loads kernels
+assert np.array_equal(y.cpu().numpy(), O.bitlinear_int(x, w, 0.016, 1)[0])
+free0 = torch.cuda.mem_get_info()[0]
+torch_bytes0 = torch.cuda.memory_allocated()
+y.zero_()
+call()
+call()
+assert torch.cuda.mem_get_info()[0] == free0, "device memory in use changed across static calls"
+assert torch.cuda.memory_allocated() == torch_bytes0
+assert np.array_equal(y.cpu().numpy(), O.bitlinear_int(x, w, 0.016, 1)[0])
+assert abi.lib.rotor_b200_device_status() == 0    # also reads the status word kept in the fixed array
+print("FRESH_OK")
+"""
+
+
+def test_static_call_first_in_a_fresh_process_allocates_nothing():
+    """The static entry point as the first layer forward of a new process (its set-up path), then two more
+    calls across which neither the driver's free-memory figure nor torch's allocator moves."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join([root, os.path.join(root, "rotor-rag_b200"), env.get("PYTHONPATH", "")])
+    r = subprocess.run([sys.executable, "-c", _FRESH], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "FRESH_OK" in r.stdout, r.stdout + r.stderr
 
 
 def test_static_scratch_size_limit_is_reported():
