@@ -76,15 +76,18 @@ def call():
     assert st == 0, st
     torch.cuda.synchronize()
 call()                                            # first forward of the process: looks the array up, loads kernels
-assert np.array_equal(y.cpu().numpy(), O.bitlinear_int(x, w, 0.016, 1)[0])
+want = O.bitlinear_int(x, w, 0.016, 1)[0]
+assert np.array_equal(y.cpu().numpy(), want)
+y.zero_()                                         # (torch's own fill kernel is loaded now, not inside the window)
+torch.cuda.synchronize()
 free0 = torch.cuda.mem_get_info()[0]
 torch_bytes0 = torch.cuda.memory_allocated()
-y.zero_()
 call()
 call()
-assert torch.cuda.mem_get_info()[0] == free0, "device memory in use changed across static calls"
+free1 = torch.cuda.mem_get_info()[0]
+assert free1 == free0, f"device memory in use changed across static calls: {free0} -> {free1}"
 assert torch.cuda.memory_allocated() == torch_bytes0
-assert np.array_equal(y.cpu().numpy(), O.bitlinear_int(x, w, 0.016, 1)[0])
+assert np.array_equal(y.cpu().numpy(), want)
 assert abi.lib.rotor_b200_device_status() == 0    # also reads the status word kept in the fixed array
 print("FRESH_OK")
 """
