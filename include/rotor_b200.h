@@ -64,6 +64,10 @@ const char* rotor_b200_status_string(int status);
 int rotor_b200_device_status(void);
 /* Number of kernels this library has launched in this process, graph replays included. */
 unsigned long long rotor_b200_launch_count(void);
+/* Measurement aid (no counterpart in the reference): launches a kernel that does nothing, with the
+ * launch attributes of the decode chain.  Timing a chain of these gives the per-launch floor of a
+ * chain of dependent kernels on this device. */
+int rotor_b200_launch_empty(void* stream);
 
 /* ---------------------------------------------------------------- format (a1-a3)
  * Device twins of the reference's format primitives.

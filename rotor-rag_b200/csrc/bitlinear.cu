@@ -194,6 +194,11 @@ static int ensure_status() {
     return ROTOR_B200_OK;
 }
 
+__global__ void empty_kernel() {
+    pdl_wait();
+    pdl_trigger();
+}
+
 int g_use_pdl = 1;  // programmatic dependent launch for the kernels that call pdl_wait()
 
 unsigned* library_status_word() { return ensure_status() ? nullptr : g_status_words.here(); }
@@ -540,6 +545,26 @@ int rotor_b200_ternary_matmul_host(const void* tiles, const float* scales_host, 
     if (rc) return rc;
     RB_CUDA(cudaMemcpy(y_host, dy, out * 4, cudaMemcpyDeviceToHost));
     return ROTOR_B200_OK;
+}
+
+/* Measurement aid: one launch of a kernel that does nothing, with the same launch attributes
+ * (programmatic dependent launch when enabled) as the kernels of the decode chain.  A chain of
+ * these in a CUDA graph gives the floor that any chain of dependent launches pays per launch. */
+int rotor_b200_launch_empty(void* stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(148);
+    cfg.blockDim = dim3(128);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, rb::empty_kernel) != cudaSuccess) {
+        ++g_launch_count;
+        return ROTOR_B200_ERR_CUDA;
+    }
+    return launch_status();
 }
 
 /* Reads and clears the status words of the current device that bounded waits write to: the
