@@ -68,6 +68,13 @@ unsigned long long rotor_b200_launch_count(void);
  * launch attributes of the decode chain.  Timing a chain of these gives the per-launch floor of a
  * chain of dependent kernels on this device. */
 int rotor_b200_launch_empty(void* stream);
+/* Self-test of the bounded device-side waits (no counterpart in the reference, whose plug-in call
+ * swallows every failure and recomputes on the CPU, src/rotor/transformer.py:145-147): runs the
+ * peer-memory all-reduce on ONE GPU against a "peer" buffer nothing writes, with a wait limit of
+ * spin_cycles SM cycles.  The first launch must give up and set the status word (returned in
+ * *status_out: 0x7e000000 | source rank); a second launch must then return at once (*second_ms,
+ * device time).  The word stays set for rotor_b200_device_status() to read and clear. */
+int rotor_b200_selftest_exchange_timeout(long long spin_cycles, unsigned* status_out, float* second_ms);
 
 /* ---------------------------------------------------------------- format (a1-a3)
  * Device twins of the reference's format primitives.

@@ -351,6 +351,10 @@ int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int
             return launch_gemm_tcgen05(tiles, out, in, xq, (int)ncols, acc, st);
         return launch_gemm_mma(tiles, out, in, xq, xsum, (int)ncols, acc, st);
     }
+    // small matrices, up to eight columns: the staged kernel (every CTA's share of the tiles sits in shared
+    // memory before the activations are needed, which a chain of dependent launches can overlap)
+    if (ncols <= 8 && staged_acc_supported(out, in, (int)ncols, variant))
+        return launch_staged_acc(tiles, out, in, xq, xsum, (int)ncols, acc, variant, st);
     variant = pick_variant(variant, (int)(ncols < 8 ? ncols : 8));
     const size_t chunk = variant == ROTOR_B200_VARIANT_MMA ? 8 : 4;
     for (size_t c0 = 0; c0 < ncols; c0 += chunk) {

@@ -161,4 +161,45 @@ int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int 
 
 int fused_sm_count() { return sm_count(); }
 
+// Stand-alone integer product through the staged kernel: the matrix is small enough for every
+// CTA's share of the tiles to sit in shared memory, and the activations are quantised already.
+bool staged_acc_supported(size_t out, size_t in, int ncols, int variant) {
+    if (ncols < 1 || ncols > 8 || in % 4) return false;
+    if (variant == ROTOR_B200_VARIANT_DP4A && ncols > 2) return false;  // the staged kernel multiplies 1 or 2 columns with dp4a
+    FusedGemvParams p = {};
+    p.cols = ncols;
+    p.nkt = (int)(kpad_of(in) / TILE_K);
+    p.halves = 1;
+    p.units = (int)(opad_of(out) / TILE_ROWS);
+    const int grid = sm_count() < p.units ? sm_count() : p.units;
+    p.upc = (p.units + grid - 1) / grid;
+    p.st.mode = LM_PLAIN;
+    p.st.n = (int)in;
+    const long tiles_per_warp = (long)p.units * p.nkt / ((long)grid * FG_WARPS);
+    return tiles_per_warp < 16 && fused_stage_bytes(p) <= FG_STAGE_MAX && fused_smem(p, true) <= 200 * 1024;
+}
+
+int launch_staged_acc(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
+                      int32_t* acc, int variant, cudaStream_t st) {
+    if (!staged_acc_supported(out, in, ncols, variant)) return ROTOR_B200_ERR_SHAPE;
+    LeanStage stage = {};
+    stage.mode = LM_PLAIN;
+    stage.n = (int)in;
+    stage.terms = 1;
+    stage.kpad = (int)kpad_of(in);
+    FusedGemvParams p;
+    int grid = sm_count();
+    const float one[3] = {1.f, 1.f, 1.f};
+    int rc = make_fused_params(p, tiles, out, in, 1, ncols, stage, nullptr, one, (int)out, (int)out, 0, grid);
+    if (rc) return rc;
+    p.xq_in = xq;
+    p.xsum_in = xsum;
+    p.acc_out = acc;
+    if (grid > p.units) grid = p.units;
+    const bool mma = variant == ROTOR_B200_VARIANT_MMA || ncols > 2;
+    if (mma) return launch_fused_tp<true, 1, false, false, false>(p, grid, st);
+    if (ncols == 1) return launch_fused_tp<false, 1, false, false, false>(p, grid, st);
+    return launch_fused_tp<false, 2, false, false, false>(p, grid, st);
+}
+
 }  // namespace rb

@@ -95,6 +95,10 @@ int launch_fused_gemv(const void* tiles, size_t out, size_t in, int halves, int 
                       const FusedTpExtra* tp = nullptr);
 bool fused_gemv_supported(size_t out, size_t in, int rows, int terms, int halves, int merge_weights);
 int configure_fused_gemv();
+// Stand-alone int8 x ternary product of a small matrix through the staged generation-step kernel.
+bool staged_acc_supported(size_t out, size_t in, int ncols, int variant);
+int launch_staged_acc(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
+                      int32_t* acc, int variant, cudaStream_t st);
 int fused_sm_count();
 
 extern int g_use_pdl;

@@ -42,6 +42,11 @@ struct FusedGemvParams {
     XchScalarDev xs;
     int32_t* part;
     float* sx_out;
+    // stand-alone product on activations that are quantised already (no vector stage): int8 columns
+    // [cols][kpad] and their sums in, exact int32 sums [cols][out] out
+    const int8_t* xq_in;
+    const int32_t* xsum_in;
+    int32_t* acc_out;
 };
 
 // Input rows wider than the register-resident prologue holds (4 * FG_V * FG_THREADS elements)
@@ -189,7 +194,16 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
 
     // ---- prologue: activation rows -> int8 in shared memory
     const bool writer = blockIdx.x == 0;
-    if constexpr (WIDE) {
+    if (!WIDE && !TP && p.xq_in) {
+        // already quantised: the columns are copied as they are
+        const int k16 = p.nkt * (TILE_K / 16);  // 16-byte pieces per column
+        for (int i = threadIdx.x; i < p.cols * k16; i += blockDim.x) {
+            const int col = i / k16, o = i - col * k16;
+            *reinterpret_cast<uint4*>(xs + (size_t)col * xs_stride + 16 * o) =
+                __ldcg(reinterpret_cast<const uint4*>(p.xq_in + (size_t)col * p.nkt * TILE_K) + o);
+        }
+        if ((int)threadIdx.x < p.cols) s_xsum[threadIdx.x] = __ldcg(p.xsum_in + threadIdx.x);
+    } else if constexpr (WIDE) {
         float* row = aux;  // [n] float32
         const int n = p.st.n;
         for (int m = 0; m < p.rows; ++m) {
@@ -393,6 +407,15 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
     RB_STAMP(tr, 4);
 
     // ---- epilogue: the CTA's rows are complete: remove the +1 code offset, dequantise, write
+    if (!WIDE && !TP && p.acc_out) {  // stand-alone product: exact integer sums, column major
+        for (int e = threadIdx.x; e < (u1 - u0) * 16 * p.cols; e += blockDim.x) {
+            const int q = e / p.cols, col = e - q * p.cols;
+            const int rl = q & 15, lu = q >> 4;
+            const int orow = (u0 + lu) * TILE_ROWS + rl;
+            if (orow < p.out) p.acc_out[(size_t)col * p.out + orow] = merge[lu * 128 + rl * 8 + col] - s_xsum[col];
+        }
+        return;
+    }
     constexpr bool ONE = NCOL == 1 && !USE_MMA;
     const int T = ONE ? 1 : p.st.terms, nrows = ONE ? 1 : p.rows;
     for (int e = threadIdx.x; e < (u1 - u0) * 16 * nrows; e += blockDim.x) {
@@ -408,17 +431,19 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
             p.part[(size_t)m * p.out + orow] = merge[lu * 128 + rl * 8 + m] - s_xsum[m];  // halves == 1
             continue;
         }
-        float val[2] = {0.f, 0.f};
-        for (int half = 0; half < p.halves; ++half) {
+        // (two named values, not an array indexed by the loop: that would live in local memory, whose
+        // first touch costs an L2 round trip at the very end of the kernel)
+        auto deq = [&](int half) {
             const int slot = DEEP ? lu * p.halves + half : half * (u1 - u0) + lu;
             const int* src = merge + slot * 128 + rl * 8 + m * T;
             float f = 0.f;
             for (int tt = 0; tt < T; ++tt) f += (float)(src[tt] - s_xsum[m * T + tt]) * s_sx[m * T + tt];
-            val[half] = f;
-        }
+            return f;
+        };
+        const float val0 = deq(0), val1 = p.halves == 2 ? deq(1) : 0.f;
         float r;
         if (p.halves == 2) {
-            const float gt = val[0] * p.scale[0], up = val[1] * p.scale[1];
+            const float gt = val0 * p.scale[0], up = val1 * p.scale[1];
             if (p.ffn_act == ROTOR_B200_FFN_RELU2) {
                 const float q2 = fmaxf(gt, 0.f);
                 r = q2 * q2 * up;
@@ -427,7 +452,7 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
                 r = gt * (c2 / (1.f + expf(-c2)));
             }
         } else {
-            r = val[0] * (orow < p.seg1 ? p.scale[0] : (orow < p.seg2 ? p.scale[1] : p.scale[2]));
+            r = val0 * (orow < p.seg1 ? p.scale[0] : (orow < p.seg2 ? p.scale[1] : p.scale[2]));
         }
         p.y[(size_t)m * p.out + orow] = r;
     }

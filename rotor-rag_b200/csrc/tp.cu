@@ -59,6 +59,7 @@ struct XchDev {
     unsigned* seq;              // collectives completed so far (device memory: graph replays advance it)
     unsigned* done;             // CTAs of the running collective that have finished
     unsigned* status;           // library status word
+    long long spin;             // SM cycles a poll may wait before it gives up
     int rank, size;
 };
 
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(256) oneshot_allreduce_kernel(const __grid_con
                 if (got.y != gen && !failed) {
                     const long long t0 = clock64();
                     while ((got = ld_pair(w)).y != gen) {
-                        if (clock64() - t0 > XCH_SPIN_CYCLES) {
+                        if (clock64() - t0 > t.spin) {
                             failed = true;
                             atomicExch(t.status, 0x7e000000u | (unsigned)src);
                             break;
@@ -154,7 +155,7 @@ __global__ void __launch_bounds__(256) oneshot_allreduce_dequant_kernel(const __
             if (p != t.rank) st_pair(t.buf[p] + (slot + t.rank) * XCH_CAP + i, (unsigned)v, gen);
         int acc = 0;
         for (int src = 0; src < t.size; ++src)
-            acc += src == t.rank ? v : (int)xch_poll(t.buf[t.rank] + (slot + src) * XCH_CAP + i, gen, t.status, src);
+            acc += src == t.rank ? v : (int)xch_poll(t.buf[t.rank] + (slot + src) * XCH_CAP + i, gen, t.status, src, t.spin);
         y[i] = __fmul_rn(__fmul_rn((float)acc, sx[i / n]), scale);
     }
 }
@@ -211,6 +212,7 @@ static int setup_oneshot(TpComm* t) {
     t->x.seq = t->ctr;
     t->x.done = t->ctr + 1;
     t->x.status = library_status_word();
+    t->x.spin = XCH_SPIN_CYCLES;
     t->x.rank = t->rank;
     t->x.size = t->size;
     if (!t->x.status) return ROTOR_B200_ERR_CUDA;
@@ -219,6 +221,7 @@ static int setup_oneshot(TpComm* t) {
     t->fused.done = nullptr;
     t->scalar.seq = t->ctr + 2;
     t->scalar.status = t->x.status;
+    t->scalar.spin = XCH_SPIN_CYCLES;
     t->scalar.rank = t->rank;
     t->scalar.size = t->size;
     for (int p = 0; p < t->size; ++p) {
@@ -303,6 +306,60 @@ int rotor_b200_tp_init(int rank, int size, const void* unique_id128, void** comm
     }
     *comm = t;
     return ROTOR_B200_OK;
+}
+
+/* Self-test of the bounded waits of the peer-memory exchange, on ONE GPU: a two-rank exchange whose
+ * "peer" buffer is a second allocation on this device that nothing ever writes, so the poll for
+ * the peer's words must run out after `spin_cycles` SM cycles.  Runs the all-reduce twice: the
+ * first launch has to give up and set the status word; the second (with a limit of about a
+ * second) has to see the word and return at once.  status_out receives the word after the first
+ * launch, second_ms the device time of the second launch.  The status word stays set: the caller
+ * reads and clears it with rotor_b200_device_status(). */
+int rotor_b200_selftest_exchange_timeout(long long spin_cycles, unsigned* status_out, float* second_ms) {
+    RB_REQUIRE(spin_cycles > 0 && spin_cycles <= XCH_SPIN_CYCLES && status_out && second_ms);
+    const size_t words = 2 * 2 * (size_t)XCH_CAP;  // two slots, two ranks
+    uint2 *own = nullptr, *peer = nullptr;
+    unsigned* ctr = nullptr;
+    int* data = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = ROTOR_B200_ERR_CUDA;
+    const int n = 1024;
+    do {
+        if (cudaMalloc(&own, words * sizeof(uint2)) != cudaSuccess || cudaMalloc(&peer, words * sizeof(uint2)) != cudaSuccess ||
+            cudaMalloc(&ctr, 2 * sizeof(unsigned)) != cudaSuccess || cudaMalloc(&data, 2 * n * sizeof(int)) != cudaSuccess)
+            break;
+        if (cudaMemset(own, 0, words * sizeof(uint2)) != cudaSuccess || cudaMemset(peer, 0, words * sizeof(uint2)) != cudaSuccess ||
+            cudaMemset(ctr, 0, 2 * sizeof(unsigned)) != cudaSuccess || cudaMemset(data, 0, 2 * n * sizeof(int)) != cudaSuccess)
+            break;
+        XchDev x = {};
+        x.buf[0] = own;
+        x.buf[1] = peer;
+        x.seq = ctr;
+        x.done = ctr + 1;
+        x.status = library_status_word();
+        x.spin = spin_cycles;
+        x.rank = 0;
+        x.size = 2;
+        if (!x.status) break;
+        if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
+        oneshot_allreduce_kernel<XOP_SUM_I32><<<4, 256>>>(x, (const unsigned*)data, (unsigned*)data + n, n);
+        if (launch_status() || cudaDeviceSynchronize() != cudaSuccess) break;
+        if (cudaMemcpy(status_out, x.status, sizeof(unsigned), cudaMemcpyDeviceToHost) != cudaSuccess) break;
+        x.spin = XCH_SPIN_CYCLES;  // would take about a second per source if the set status word were ignored
+        cudaEventRecord(e0);
+        oneshot_allreduce_kernel<XOP_SUM_I32><<<4, 256>>>(x, (const unsigned*)data, (unsigned*)data + n, n);
+        cudaEventRecord(e1);
+        if (launch_status() || cudaDeviceSynchronize() != cudaSuccess) break;
+        if (cudaEventElapsedTime(second_ms, e0, e1) != cudaSuccess) break;
+        rc = ROTOR_B200_OK;
+    } while (0);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(own);
+    cudaFree(peer);
+    cudaFree(ctr);
+    cudaFree(data);
+    return rc;
 }
 
 void rotor_b200_tp_destroy(void* comm) {

@@ -15,13 +15,14 @@ constexpr int XCH_MAX_RANKS = 8;
 constexpr int XCH_CAP = 1 << 16;   // 32-bit elements per one-shot vector exchange
 constexpr int XS_RING = 16;        // scalar exchange slots; a rank is never more than two kernels ahead of a peer
 constexpr int XS_ROWS = 8;         // token rows per scalar exchange
-constexpr long long XCH_SPIN_CYCLES = 2000000000LL;  // about one second
+constexpr long long XCH_SPIN_CYCLES = 2000000000LL;  // default limit of a wait: about one second
 
 // One float per token row, exchanged by every CTA of a kernel.
 struct XchScalarDev {
     uint2* buf[XCH_MAX_RANKS];  // this process's mapping of every rank's ring: uint2 [XS_RING][size][XS_ROWS]
     const unsigned* seq;        // exchanges completed before this step
     unsigned* status;
+    long long spin;             // SM cycles a poll may wait before it gives up
     int rank, size;             // size == 0: no exchange (single GPU)
 };
 
@@ -35,12 +36,12 @@ __device__ __forceinline__ uint2 ld_pair(const uint2* p) {
 }
 
 // Polls a local exchange word for generation `gen`; `src` only labels the status code.
-__device__ __forceinline__ unsigned xch_poll(const uint2* w, unsigned gen, unsigned* status, int src) {
+__device__ __forceinline__ unsigned xch_poll(const uint2* w, unsigned gen, unsigned* status, int src, long long spin) {
     uint2 got = ld_pair(w);
     if (got.y != gen && *reinterpret_cast<volatile unsigned*>(status) == 0) {
         const long long t0 = clock64();
         while ((got = ld_pair(w)).y != gen) {
-            if (clock64() - t0 > XCH_SPIN_CYCLES || *reinterpret_cast<volatile unsigned*>(status) != 0) {
+            if (clock64() - t0 > spin || *reinterpret_cast<volatile unsigned*>(status) != 0) {
                 atomicCAS(status, 0u, 0x7e000000u | (unsigned)src);
                 break;
             }
@@ -64,7 +65,7 @@ __device__ __forceinline__ float xch_scalar(const XchScalarDev& x, int idx, int 
         float val = v;
         if (peer != x.rank) {
             if (writer) st_pair(x.buf[peer] + (slot + x.rank) * XS_ROWS + row, __float_as_uint(v), gen);
-            val = __uint_as_float(xch_poll(x.buf[x.rank] + (slot + peer) * XS_ROWS + row, gen, x.status, peer));
+            val = __uint_as_float(xch_poll(x.buf[x.rank] + (slot + peer) * XS_ROWS + row, gen, x.status, peer, x.spin));
         }
         scratch[peer] = val;
     }

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "rotor_b200_device_status": (_i, []),
     "rotor_b200_launch_count": (C.c_ulonglong, []),
     "rotor_b200_launch_empty": (_i, [_p]),
+    "rotor_b200_selftest_exchange_timeout": (_i, [C.c_longlong, _p, _p]),
     "rotor_b200_encode": (_i, [_p, _sz, _p, _p, _p]),
     "rotor_b200_decode": (_i, [_p, _p, _sz, _p, _p]),
     "rotor_b200_pack": (_i, [_p, _p, _sz, _p, _p]),

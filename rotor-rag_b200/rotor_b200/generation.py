@@ -4,11 +4,13 @@
 With a rotor_b200 BitNetModel, greedy generation with the cache stays on the device:
 the prompt is prefilled once, every later step is a replay of one CUDA graph whose
 greedy pick feeds the next step, and token ids come back to the host only to test for
-EOS and to feed the per-token callback.  Top-k / top-p strategies constructed with ``device=True`` keep the logits on the device as
-well and draw there (rotor_b200_sample: the reference's distribution from a seeded
+EOS and to feed the per-token callback.  Top-k / top-p strategies keep the logits on the
+device as well and draw there (rotor_b200_sample: the reference's distribution from a seeded
 counter-based stream instead of NumPy's global generator); only the drawn token id comes
-back.  Otherwise (or with ``use_cache=False``) the logits of the last position go to the
-host each step and are sampled with the reference's NumPy procedure.
+back.  That is the default whenever the model can do it; a strategy built with
+``device=False`` (or ``use_cache=False``) sends the logits of the last position to the host
+each step and samples them with the reference's NumPy procedure, drawing from NumPy's global
+stream as the reference does.
 """
 from __future__ import annotations
 
@@ -40,7 +42,7 @@ class _DeviceDraw:
     k, p = 50, 0.9
 
     def _init_device(self, device, seed):
-        self.device = bool(device)
+        self.device = None if device is None else bool(device)  # None: on the device when the model can
         self.seed = int(np.random.randint(0, 2 ** 31 - 1)) if seed is None else int(seed)
         self.counter = 0
 
@@ -54,10 +56,11 @@ class _DeviceDraw:
 
 
 class TopKSampling(SamplingStrategy, _DeviceDraw):
-    """Sample among the k largest logits (reference :45-88).  ``device=True``: draw on the GPU."""
+    """Sample among the k largest logits (reference :45-88).  ``device=False``: draw on the host from
+    NumPy's global stream (the reference's behaviour) instead of on the GPU."""
     mode = 0
 
-    def __init__(self, k: int = 50, *, device: bool = False, seed: Optional[int] = None):
+    def __init__(self, k: int = 50, *, device: Optional[bool] = None, seed: Optional[int] = None):
         self.k = k
         self._init_device(device, seed)
 
@@ -71,10 +74,10 @@ class TopKSampling(SamplingStrategy, _DeviceDraw):
 
 class TopPSampling(SamplingStrategy, _DeviceDraw):
     """Sample from the smallest set whose probability mass reaches p (reference :91-145).
-    ``device=True``: draw on the GPU."""
+    ``device=False``: draw on the host from NumPy's global stream instead of on the GPU."""
     mode = 1
 
-    def __init__(self, p: float = 0.9, *, device: bool = False, seed: Optional[int] = None):
+    def __init__(self, p: float = 0.9, *, device: Optional[bool] = None, seed: Optional[int] = None):
         self.p = p
         self._init_device(device, seed)
 
@@ -135,8 +138,8 @@ class TextGenerator:
             return
         self.kv_cache = None
         seq = list(ids)
-        if self.use_cache and getattr(self.sampling_strategy, "device", False) and \
-                hasattr(self.model, "forward_last_logits_device"):
+        on_device = isinstance(self.sampling_strategy, _DeviceDraw) and self.sampling_strategy.device is not False
+        if self.use_cache and on_device and hasattr(self.model, "forward_last_logits_device"):
             # logits stay on the device; one token id per step comes back
             for step in range(n):
                 feed = np.asarray(seq if step == 0 else seq[-1:], dtype=np.int64).reshape(1, -1)

@@ -48,12 +48,10 @@ class B200TernaryOps:
         if scales.size != out_dim or x.size != in_dim:
             raise ValueError("scales / input length mismatch")
         y = np.empty(out_dim, dtype=np.float32)
-        f32 = C.POINTER(C.c_float)
         check(lib.rotor_b200_ternary_matmul_host(packed_weights.tiles.data_ptr(),
                                                  scales.ctypes.data_as(C.c_void_p), x.ctypes.data_as(C.c_void_p),
                                                  in_dim, out_dim, self.act_terms, y.ctypes.data_as(C.c_void_p)),
               "ternary_matmul")
-        del f32
         return y
 
 

@@ -98,7 +98,8 @@ class PassTokenizer:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("ROTOR_RAG_REF"), required="ROTOR_RAG_REF" not in os.environ,
+                    help="checkout of the reference (default: $ROTOR_RAG_REF)")
     ap.add_argument("--check-only", action="store_true", help="run every oracle-vs-reference check, write nothing")
     args = ap.parse_args()
     if args.check_only:

@@ -9,7 +9,7 @@ import pytest
 from gguf_writer import synthetic_tensors, write_gguf
 from oracle import bitlinear_np as O
 
-REF_SRC = "/root/reference/src"
+REF_SRC = os.path.join(os.environ.get("ROTOR_RAG_REF", ""), "src")  # set ROTOR_RAG_REF to the reference checkout
 
 
 def _check(reader, tensors):

@@ -256,9 +256,12 @@ def test_generation_loop_rules(rb):
     pieces = list(rb.gen.TextGenerator(model, tok, max_length=64).generate_streaming(text, max_new_tokens=5,
                                                                                    stop_on_eos=False))
     assert pieces[0] == text and [int(p) for p in pieces[1:]] == full[:5]
-    # top-k / top-p run on host logits and return valid ids
+    # top-k / top-p return valid ids on both routes: drawn on the device (the default with this model) and,
+    # with device=False, from host logits with NumPy's global stream as in the reference
     np.random.seed(0)
-    for strat in (rb.gen.TopKSampling(k=5), rb.gen.TopPSampling(p=0.8)):
+    assert rb.gen.TopKSampling(k=5).device is None and rb.gen.TopPSampling(p=0.8, device=False).device is False
+    for strat in (rb.gen.TopKSampling(k=5), rb.gen.TopPSampling(p=0.8), rb.gen.TopKSampling(k=5, device=False),
+                  rb.gen.TopPSampling(p=0.8, device=False)):
         tgs = rb.gen.TextGenerator(model, tok, sampling_strategy=strat, temperature=0.7, max_length=64)
         ids = [int(t) for t in tgs.generate(text, max_new_tokens=4, stop_on_eos=False).split()]
         assert len(ids) == len(prompt) + 4 and all(0 <= t < om["cfg"]["vocab_size"] for t in ids)

@@ -186,7 +186,8 @@ def test_backend_code_matvec():
     assert rel_err(y, O.bitlinear_float(x[None, :], w, 0.37)[0]) < 1e-5
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/src/rotor"), reason="reference checkout not present")
+@pytest.mark.skipif(not os.path.isdir(os.path.join(os.environ.get("ROTOR_RAG_REF", ""), "src", "rotor")),
+                    reason="set ROTOR_RAG_REF to a checkout of the reference to run this")
 def test_oracle_against_live_reference(tmp_path):
     """Where the reference checkout exists, re-run the generator: it asserts oracle == reference."""
     env = dict(os.environ)
