@@ -221,7 +221,11 @@ __global__ void __launch_bounds__(128) attention_kernel(AttnParams p) {
     }
 }
 
+static bool attn_decode_stream_ok(const AttnParams& p, int rows);
+static int launch_attn_decode_stream(const AttnParams& p, int rows, cudaStream_t st);
+
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st) {
+    if (attn_decode_stream_ok(p, rows)) return launch_attn_decode_stream(p, rows, st);  // batched generation steps
     if (attn_prefill_supported(p, rows)) return launch_attn_prefill_tc(p, rows, st);
     dim3 grid(p.n_heads, rows);
     switch (p.head_dim) {
@@ -364,6 +368,58 @@ constexpr int AC_MAX_GROUP = 8;  // query heads per KV head = warps per CTA
 
 __host__ __device__ inline int round4(int v) { return (v + 3) & ~3; }
 
+// One warp, one query head, up to 32 keys whose K and V rows lie in shared memory (row stride D):
+// scores with 8 lanes per key (lane l8 = lane & 7 holds the 16-byte pieces l8, l8 + 8, ... of q,
+// pre-scaled), online softmax across chunks (lane j keeps key j's score), weighted V with D / 32
+// output dimensions per lane.  Updates the running maximum, sum and output.
+template <int D>
+__device__ __forceinline__ void attn_warp_chunk(const float4 (&q4)[D / 32], const float* Kc, const float* Vc, int nk,
+                                                int lane, float& m_run, float& l_run, float4& o) {
+    constexpr int NCH = D / 32, OPL = D / 32;
+    const int l8 = lane & 7;
+    float my_s = -INFINITY;
+    for (int i = 0; i * 4 < nk; ++i) {  // four keys per pass: key 4 i + (lane >> 3)
+        const int j = 4 * i + (lane >> 3);
+        float s = 0.f;
+        if (j < nk) {
+            const float4* kr = reinterpret_cast<const float4*>(Kc + (size_t)j * D);
+#pragma unroll
+            for (int e = 0; e < NCH; ++e) {
+                const float4 k4 = kr[8 * e + l8];
+                s += q4[e].x * k4.x + q4[e].y * k4.y + q4[e].z * k4.z + q4[e].w * k4.w;
+            }
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        const float mine = __shfl_sync(0xffffffffu, s, (lane & 3) * 8);  // key 4 i + (lane & 3)
+        if ((lane >> 2) == i) my_s = mine;                               // lane j keeps key j
+    }
+    if (lane >= nk) my_s = -INFINITY;
+    const float m_new = fmaxf(m_run, warp_max(my_s));
+    const float keep = m_run == -INFINITY ? 0.f : __expf(m_run - m_new);
+    const float pr = lane < nk ? __expf(my_s - m_new) : 0.f;
+    l_run = l_run * keep + warp_sum(pr);
+    o = make_float4(o.x * keep, o.y * keep, o.z * keep, o.w * keep);
+    const float* vr = Vc + OPL * lane;
+#pragma unroll 4
+    for (int j = 0; j < nk; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, pr, j);
+        if constexpr (OPL == 4) {
+            const float4 v4 = *reinterpret_cast<const float4*>(vr + (size_t)j * D);
+            o.x += pj * v4.x;
+            o.y += pj * v4.y;
+            o.z += pj * v4.z;
+            o.w += pj * v4.w;
+        } else {
+            const float2 v2 = *reinterpret_cast<const float2*>(vr + (size_t)j * D);
+            o.x += pj * v2.x;
+            o.y += pj * v2.y;
+        }
+    }
+    m_run = m_new;
+}
+
 template <int D>
 __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(const __grid_constant__ AttnDecodeParams p) {
     extern __shared__ __align__(16) float sm[];
@@ -466,52 +522,11 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(
 
     // ---- this warp's head over the slice, 32 keys at a time
     float m_run = -INFINITY, l_run = 0.f;
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);  // output dimensions 4 lane .. 4 lane + 3 (D = 128) or 2 lanes per pair (D = 64)
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);  // output dimensions OPL * lane .. + OPL - 1
     constexpr int OPL = D / 32;                  // output floats per lane
-    for (int c0 = t0; c0 < t1; c0 += 32) {
-        const int nk = min(32, t1 - c0);
-        float my_s = -INFINITY;
-        for (int i = 0; i * 4 < nk; ++i) {  // four keys per pass: key c0 + 4 i + (lane >> 3)
-            const int j = 4 * i + (lane >> 3);
-            float s = 0.f;
-            if (j < nk) {
-                const float4* kr = reinterpret_cast<const float4*>(Ks + (size_t)(c0 + j - t0) * D);
-#pragma unroll
-                for (int e = 0; e < NCH; ++e) {
-                    const float4 k4 = kr[8 * e + l8];
-                    s += q4[e].x * k4.x + q4[e].y * k4.y + q4[e].z * k4.z + q4[e].w * k4.w;
-                }
-            }
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            s += __shfl_xor_sync(0xffffffffu, s, 4);
-            const float mine = __shfl_sync(0xffffffffu, s, (lane & 3) * 8);  // key 4 i + (lane & 3)
-            if ((lane >> 2) == i) my_s = mine;                               // lane j keeps key j
-        }
-        if (lane >= nk) my_s = -INFINITY;
-        const float m_new = fmaxf(m_run, warp_max(my_s));
-        const float keep = m_run == -INFINITY ? 0.f : __expf(m_run - m_new);
-        const float pr = lane < nk ? __expf(my_s - m_new) : 0.f;
-        l_run = l_run * keep + warp_sum(pr);
-        o = make_float4(o.x * keep, o.y * keep, o.z * keep, o.w * keep);
-        const float* vr = Vs + (size_t)(c0 - t0) * D + OPL * lane;
-#pragma unroll 4
-        for (int j = 0; j < nk; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, pr, j);
-            if constexpr (OPL == 4) {
-                const float4 v4 = *reinterpret_cast<const float4*>(vr + (size_t)j * D);
-                o.x += pj * v4.x;
-                o.y += pj * v4.y;
-                o.z += pj * v4.z;
-                o.w += pj * v4.w;
-            } else {
-                const float2 v2 = *reinterpret_cast<const float2*>(vr + (size_t)j * D);
-                o.x += pj * v2.x;
-                o.y += pj * v2.y;
-            }
-        }
-        m_run = m_new;
-    }
+    for (int c0 = t0; c0 < t1; c0 += 32)
+        attn_warp_chunk<D>(q4, Ks + (size_t)(c0 - t0) * D, Vs + (size_t)(c0 - t0) * D, min(32, t1 - c0), lane, m_run,
+                           l_run, o);
     RB_STAMP(tr, 4);
 
     // ---- push this slice's results to the CTAs that merge them
@@ -560,6 +575,91 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(
     }
     RB_STAMP(tr, 5);
     RB_TRACE_COMMIT(tr, 100);
+}
+
+// ---------------------------------------------------------------------------------------
+// One-token attention for many sequences at once (batched generation steps): grid
+// (n_kv_heads, batch), one warp per query head of the group.  q is finished (rotated), the new
+// k / v row is in the cache already.  The CTA streams its sequence's K and V rows through shared
+// memory 32 keys at a time, double buffered with cp.async, and every warp runs the same
+// per-head chunk routine as the cluster kernel; no partials, no merge: one pass over the cache
+// per group of heads, written as finished attention rows.
+constexpr int AS_KEYS = 32;
+
+template <int D>
+__global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(const __grid_constant__ AttnParams p) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int C4 = D / 4, NCH = D / 32, OPL = D / 32;
+    const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
+    const int G = p.n_heads / p.n_kv_heads;  // blockDim.x == 32 * G
+    const int hk = blockIdx.x, b = blockIdx.y;
+    const int dq = p.n_heads * D;
+    const int T = min(p.past_len[b] + 1, p.max_seq);
+    const float* kc = p.k_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
+    const float* vc = p.v_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
+    float* Ks = sm;                         // [2][AS_KEYS][D]
+    float* Vs = sm + 2 * AS_KEYS * D;       // [2][AS_KEYS][D]
+    auto fetch = [&](int chunk, int stage) {
+        const int t0 = chunk * AS_KEYS, n = min(AS_KEYS, T - t0);
+        for (int idx = tid; idx < n * C4; idx += nthr) {
+            const int r = idx / C4, c4 = idx - r * C4;
+            cp_async16(Ks + ((size_t)stage * AS_KEYS + r) * D + 4 * c4, kc + (size_t)(t0 + r) * D + 4 * c4);
+            cp_async16(Vs + ((size_t)stage * AS_KEYS + r) * D + 4 * c4, vc + (size_t)(t0 + r) * D + 4 * c4);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int nchunk = (T + AS_KEYS - 1) / AS_KEYS;
+    fetch(0, 0);
+    const int l8 = lane & 7;
+    float4 q4[NCH];
+    {
+        const float* qh = p.q + (size_t)b * dq + (size_t)(hk * G + warp) * D;
+        const float scale = 1.0f / sqrtf((float)D);
+#pragma unroll
+        for (int e = 0; e < NCH; ++e) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(qh) + (8 * e + l8));
+            q4[e] = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+        }
+    }
+    float m_run = -INFINITY, l_run = 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 0; c < nchunk; ++c) {
+        if (c + 1 < nchunk) {
+            fetch(c + 1, (c + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // chunk c has landed for every thread
+        const int st = c & 1;
+        attn_warp_chunk<D>(q4, Ks + (size_t)st * AS_KEYS * D, Vs + (size_t)st * AS_KEYS * D, min(AS_KEYS, T - c * AS_KEYS),
+                           lane, m_run, l_run, o);
+        __syncthreads();  // every warp is done with this stage before chunk c + 2 overwrites it
+    }
+    const float inv = 1.0f / l_run;
+    float* dst = p.out + (size_t)b * dq + (size_t)(hk * G + warp) * D + OPL * lane;
+    if constexpr (OPL == 4) {
+        *reinterpret_cast<float4*>(dst) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    } else {
+        *reinterpret_cast<float2*>(dst) = make_float2(o.x * inv, o.y * inv);
+    }
+}
+
+static bool attn_decode_stream_ok(const AttnParams& p, int rows) {
+    if (p.seq != 1 || rows < 16 || (p.head_dim != 64 && p.head_dim != 128)) return false;
+    const int G = p.n_heads / p.n_kv_heads;
+    return G >= 1 && G <= AC_MAX_GROUP;
+}
+
+static int launch_attn_decode_stream(const AttnParams& p, int rows, cudaStream_t st) {
+    const int G = p.n_heads / p.n_kv_heads, D = p.head_dim;
+    const size_t smem = (size_t)4 * AS_KEYS * D * sizeof(float);
+    dim3 grid(p.n_kv_heads, rows);
+    if (D == 64)
+        attn_decode_stream_kernel<64><<<grid, 32 * G, smem, st>>>(p);
+    else
+        attn_decode_stream_kernel<128><<<grid, 32 * G, smem, st>>>(p);
+    return launch_status();
 }
 
 static size_t attn_cluster_smem(int G, int D, int lcmax, int ns) {
@@ -665,6 +765,8 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
