@@ -226,6 +226,7 @@ static int launch_attn_decode_stream(const AttnParams& p, int rows, cudaStream_t
 
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st) {
     if (attn_decode_stream_ok(p, rows)) return launch_attn_decode_stream(p, rows, st);  // batched generation steps
+    if (attn_prefill_t5_supported(p, rows)) return launch_attn_prefill_t5(p, rows, st);  // head_dim 128 prompts
     if (attn_prefill_supported(p, rows)) return launch_attn_prefill_tc(p, rows, st);
     dim3 grid(p.n_heads, rows);
     switch (p.head_dim) {
@@ -771,6 +772,7 @@ int configure_attention() {
                                  cudaSharedmemCarveoutMaxShared));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
+    if (int rc = configure_attn_prefill_t5()) return rc;
     return configure_attn_prefill_tc();
 }
 

@@ -160,7 +160,8 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     c.part_m = cv.take<float>(heads);
     c.part_l = cv.take<float>(heads);
     c.counters = cv.take<unsigned>(8 + (size_t)c.max_batch);
-    c.kvsplit_plane = (size_t)c.max_batch * c.n_kv_heads * c.max_seq * c.head_dim;
+    // (positions rounded up to whole 64-key tiles: the tensor-memory attention kernel reads whole tiles)
+    c.kvsplit_plane = (size_t)c.max_batch * c.n_kv_heads * ((c.max_seq + 63) / 64 * 64) * c.head_dim;
     c.kvsplit = rows >= 64 ? cv.take<__nv_bfloat16>(4 * c.kvsplit_plane) : nullptr;  // prompts long enough to tile
     c.stat[0] = cv.take<float>(rows);
     c.stat[1] = cv.take<float>(rows);

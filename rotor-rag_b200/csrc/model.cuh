@@ -166,6 +166,11 @@ struct AttnParams {
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st);
 bool attn_prefill_supported(const AttnParams& p, int rows);
 int launch_attn_prefill_tc(const AttnParams& p, int rows, cudaStream_t st);
+// head_dim 128 on tcgen05 / tensor memory (attn_prefill_t5.cu); needs the split planes sized for
+// max_seq rounded up to 64 positions
+bool attn_prefill_t5_supported(const AttnParams& p, int rows);
+int launch_attn_prefill_t5(const AttnParams& p, int rows, cudaStream_t st);
+int configure_attn_prefill_t5();
 int configure_attn_prefill_tc();
 
 struct LmHeadParams {
