@@ -36,7 +36,24 @@
 
 #include "model.cuh"
 
+RB_TRACE_DEFINE(rotor_b200_trace_read_attn5)
+
 namespace rb {
+
+// Phase timing of the softmax loop (compiled in with -DRB_TRACE): thread 0 of CTA (0, 0, 0) adds up
+// the time between the marks of every key tile and commits the sums once.
+#ifdef RB_TRACE
+#define A5_MARK(i)                                                                     \
+    do {                                                                               \
+        if (a5_traced) {                                                               \
+            const unsigned long long now_ = gtime();                                   \
+            tr.t[i] += now_ - a5_last;                                                 \
+            a5_last = now_;                                                            \
+        }                                                                              \
+    } while (0)
+#else
+#define A5_MARK(i) do {} while (0)
+#endif
 
 constexpr int A5_BM = 128, A5_BN = 64, A5_D = 128;
 constexpr int A5_THREADS = 352;  // 8 softmax / output warps, two TMA warps, MMA warp
@@ -87,24 +104,27 @@ __device__ __forceinline__ uint64_t a5_desc(uint32_t smem_addr) {
            (2ull << 61);
 }
 
-__device__ __forceinline__ void a5_mma_ss(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+// ACC == 0: the accumulator is overwritten (first MMA of a tile), 1: accumulated into.
+template <int ACC>
+__device__ __forceinline__ void a5_mma_ss(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
         "}\n" ::"r"(d_tmem),
-        "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+        "l"(da), "l"(db), "r"(idesc), "n"(ACC), "r"(0u)
         : "memory");
 }
-__device__ __forceinline__ void a5_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+template <int ACC>
+__device__ __forceinline__ void a5_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
         "}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+        "r"(a_tmem), "l"(db), "r"(idesc), "n"(ACC), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void a5_commit(uint32_t bar) {
@@ -259,17 +279,38 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
+#ifdef RB_TRACE
+    TraceRec tr2 = {};
+    RB_STAMP(tr2, 0);
+#endif
     if (warp < 8) {
         // ---------------- Q tile: scaled, split into hi / lo bf16, K-major panels of 64 columns, 128-byte swizzle
         {
             const float scale = 1.4426950408889634f / sqrtf((float)A5_D);  // scores come out in units of log2: p = 2^(s - m)
-            for (int idx = threadIdx.x; idx < A5_BM * (A5_D / 4); idx += A5_SOFT) {
+            // all sixteen loads of a thread are issued before the first conversion (one round trip to memory
+            // instead of sixteen: the MMA warp waits for this tile before it can start)
+            constexpr int QN = A5_BM * (A5_D / 4) / A5_SOFT;
+            float4 qv[QN];
+#pragma unroll
+            for (int u = 0; u < QN; ++u) {
+                const int idx = threadIdx.x + u * A5_SOFT;
                 const int r = idx / (A5_D / 4), c4 = idx - r * (A5_D / 4);
                 const int s = s0 + r / G, gi = r - (r / G) * G;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                qv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (s < p.seq)
-                    v = *reinterpret_cast<const float4*>(p.q + ((size_t)b * p.seq + s) * p.n_heads * A5_D +
-                                                         (size_t)(hk * G + gi) * A5_D + 4 * c4);
+                    qv[u] = __ldg(reinterpret_cast<const float4*>(p.q + ((size_t)b * p.seq + s) * p.n_heads * A5_D +
+                                                                  (size_t)(hk * G + gi) * A5_D + 4 * c4));
+            }
+#ifdef RB_TRACE
+#pragma unroll
+            for (int u = 0; u < QN; ++u) asm volatile("" ::"f"(qv[u].w));
+            RB_STAMP(tr2, 4);
+#endif
+#pragma unroll
+            for (int u = 0; u < QN; ++u) {
+                const int idx = threadIdx.x + u * A5_SOFT;
+                const int r = idx / (A5_D / 4), c4 = idx - r * (A5_D / 4);
+                const float4 v = qv[u];
                 uint32_t h0, l0, h1, l1;
                 a5_split2(v.x * scale, v.y * scale, h0, l0);
                 a5_split2(v.z * scale, v.w * scale, h1, l1);
@@ -283,6 +324,9 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a5_smem(&s_qready)) : "memory");
         }
+#ifdef RB_TRACE
+        RB_STAMP(tr2, 1);
+#endif
         // ---------------- softmax and output: this thread owns keys [32 half, 32 half + 32) of a tile and output
         // columns [64 half, 64 half + 64) of query row r
         const int half = warp >> 2, wq = warp & 3;
@@ -296,10 +340,16 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
 #pragma unroll
         for (int i = 0; i < A5_D / 2; ++i) o[i] = 0.f;
         bool ok = true;
+#ifdef RB_TRACE
+        TraceRec tr = {};
+        const bool a5_traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+        unsigned long long a5_last = gtime();
+#endif
         // O = O * alpha + P V of key tile j (its accumulator buffer j & 1), this thread's 64 columns
         auto accumulate = [&](int j, float alpha) {
             bool good = a5_wait(a5_smem(&s_ofull[j & 1]), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, 0x7b000002u);
             if (!__all_sync(0xffffffffu, good)) return false;
+            A5_MARK(5);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t ov0[32], ov1[32];
             const uint32_t ob = lane_base + 128u + (uint32_t)(j & 1) * 128u + (uint32_t)half * 64u;
@@ -313,6 +363,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a5_smem(&s_oempty[j & 1])) : "memory");
+            A5_MARK(6);
             return true;
         };
         // (the eight warps leave this loop together: whether to go on is decided by one thread between the
@@ -321,6 +372,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
             const uint32_t sbuf = lane_base + (uint32_t)(j & 1) * 64u;
             ok = ok && a5_wait(a5_smem(&s_sfull[j & 1]), (uint32_t)(j >> 1) & 1u, abort_flag, p.status, 0x7b000001u);
             ok = __all_sync(0xffffffffu, ok);
+            A5_MARK(0);
             uint32_t sa[32];
             float tmax = -INFINITY;
             if (ok) {
@@ -339,6 +391,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
             // the two threads of a row exchange their maxima; past this barrier both have finished reading
             // the S buffer, which the P stores below overwrite (every softmax warp takes part, also after a
             // failed wait, so that the barrier count stays whole)
+            A5_MARK(1);
             s_xch[half][r] = tmax;
             asm volatile("bar.sync 1, %0;" ::"n"(A5_SOFT) : "memory");
             tmax = fmaxf(tmax, s_xch[half ^ 1][r]);
@@ -348,6 +401,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
                 ok = false;
                 break;
             }
+            A5_MARK(2);
             const float m_new = fmaxf(m_run, tmax);  // finite from the first tile on: key 0 is visible to every row
             const float alpha = a5_exp2(m_run - m_new);
             float sum = 0.f;
@@ -358,6 +412,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
                 sum += e0 + e1;
                 a5_split2(e0, e1, ph[c], pl[c]);  // keys 32 half + 2 c, + 1 -> column 16 half + c
             }
+            A5_MARK(3);
             a5_st16(sbuf + (uint32_t)half * 16u, ph);        // P hi: 64 bf16 in columns [0, 32) of the S buffer
             a5_st16(sbuf + 32u + (uint32_t)half * 16u, pl);  // P lo: columns [32, 64)
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -365,11 +420,19 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a5_smem(&s_pfull[j & 1])) : "memory");
             l_run = l_run * alpha + sum;
             m_run = m_new;
+            A5_MARK(4);
             // the previous tile's P V has been running meanwhile: fold it in now
             if (j > 0) ok = accumulate(j - 1, alpha_prev);
             alpha_prev = alpha;
         }
         if (ok && ntiles > 0) ok = accumulate(ntiles - 1, alpha_prev);
+#ifdef RB_TRACE
+        if (a5_traced) {
+            tr.t[7] = (unsigned long long)ntiles;
+            RB_TRACE_COMMIT(tr, 500);
+        }
+        RB_STAMP(tr2, 2);
+#endif
         // the row's sum is the sum of its two halves (same running maximum in both)
         s_xch[half][r] = l_run;
         asm volatile("bar.sync 1, %0;" ::"n"(A5_SOFT) : "memory");
@@ -435,35 +498,39 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
             // kind::f16: float32 accumulate (bit 4), A and B bf16 (bits 7, 10), both K-major, N >> 3 at 17, M >> 4 at 24
             const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(A5_BN >> 3) << 17) | ((128u >> 4) << 24);
             const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(A5_D >> 3) << 17) | ((128u >> 4) << 24);
+            // One thread issues every MMA of the CTA, so its instruction count per MMA bounds the tensor pipe:
+            // the descriptors of a tile are its base descriptor plus compile-time constants (the address field
+            // counts 16-byte units and no operand crosses the field's range), nothing is recomputed per MMA.
+            const uint64_t dq_hi = a5_desc(q_hi), dq_lo = a5_desc(q_lo);
             auto issue_s = [&](int j) {
-                const uint32_t st = kring + (uint32_t)(j & 1) * A5_K_BYTES;
+                const uint64_t dk_hi = a5_desc(kring + (uint32_t)(j & 1) * A5_K_BYTES), dk_lo = dk_hi + (16384u >> 4);
                 const uint32_t d = tmem + (uint32_t)(j & 1) * 64u;
-                const uint32_t qa[3] = {q_hi, q_hi, q_lo};
-                const uint32_t kb[3] = {st, st + 16384u, st};
-                uint32_t acc = 0;
 #pragma unroll
                 for (int term = 0; term < 3; ++term)
 #pragma unroll
                     for (int k16 = 0; k16 < A5_D / 16; ++k16) {
-                        const uint32_t ko = (uint32_t)(k16 & 3) * 32u;
-                        a5_mma_ss(d, a5_desc(qa[term] + (uint32_t)(k16 >> 2) * 16384u + ko),
-                                  a5_desc(kb[term] + (uint32_t)(k16 >> 2) * 8192u + ko), idesc_s, acc);
-                        acc = 1;
+                        const uint64_t qo = (uint64_t)(((k16 >> 2) * 16384 + (k16 & 3) * 32) >> 4);
+                        const uint64_t ko = (uint64_t)(((k16 >> 2) * 8192 + (k16 & 3) * 32) >> 4);
+                        const uint64_t da = (term == 2 ? dq_lo : dq_hi) + qo, db = (term == 1 ? dk_lo : dk_hi) + ko;
+                        if (term == 0 && k16 == 0)
+                            a5_mma_ss<0>(d, da, db, idesc_s);
+                        else
+                            a5_mma_ss<1>(d, da, db, idesc_s);
                     }
             };
             auto issue_pv = [&](int j) {
-                const uint32_t st = vring + (uint32_t)(j & 1) * A5_V_BYTES;
-                const uint32_t pbase = tmem + (uint32_t)(j & 1) * 64u;
-                const uint32_t pa[3] = {pbase, pbase, pbase + 32u};
-                const uint32_t vb[3] = {st, st + 16384u, st};
-                uint32_t acc = 0;
+                const uint64_t dv_hi = a5_desc(vring + (uint32_t)(j & 1) * A5_V_BYTES), dv_lo = dv_hi + (16384u >> 4);
+                const uint32_t pbase = tmem + (uint32_t)(j & 1) * 64u, d = tmem + 128u + (uint32_t)(j & 1) * 128u;
 #pragma unroll
                 for (int term = 0; term < 3; ++term)
 #pragma unroll
                     for (int k16 = 0; k16 < A5_BN / 16; ++k16) {
-                        a5_mma_ts(tmem + 128u + (uint32_t)(j & 1) * 128u, pa[term] + (uint32_t)k16 * 8u,
-                                  a5_desc(vb[term] + (uint32_t)k16 * 32u), idesc_o, acc);
-                        acc = 1;
+                        const uint32_t pa = pbase + (term == 2 ? 32u : 0u) + (uint32_t)k16 * 8u;
+                        const uint64_t db = (term == 1 ? dv_lo : dv_hi) + (uint64_t)((k16 * 32) >> 4);
+                        if (term == 0 && k16 == 0)
+                            a5_mma_ts<0>(d, pa, db, idesc_o);
+                        else
+                            a5_mma_ts<1>(d, pa, db, idesc_o);
                     }
             };
             bool ok = a5_wait(a5_smem(&s_qready), 0, abort_flag, p.status, 0x7b000004u);
@@ -497,6 +564,12 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
         }
     }
 
+#ifdef RB_TRACE
+    if (warp < 8) {
+        RB_STAMP(tr2, 3);
+        RB_TRACE_COMMIT(tr2, 501);
+    }
+#endif
     // ---------------- common exit: nothing of this CTA may still be in flight when it returns
     if (*abort_flag && threadIdx.x == 0) {
         const long long t0 = clock64();
