@@ -26,12 +26,17 @@
 #include "gemv_core.cuh"
 #include "model.cuh"
 
+RB_TRACE_DEFINE(rotor_b200_trace_read_gemm5)
+
 namespace rb {
 
 // Tokens per CTA is a template argument too: 256 (two MMA M halves, one CTA per SM: all 512
 // tensor-memory columns) or 128 (one half, 256 columns and a two-stage ring, so that TWO CTAs share
 // an SM and the accumulator read-back of one overlaps the MMAs of the other).
-constexpr int T5_THREADS = 192;                    // warps 0-3 decode + epilogue, 4 TMA + TMEM, 5 MMA
+// Decoder warps (they also read the accumulators back), then one TMA + TMEM warp and one MMA warp.
+// Eight decoders for 256-row tiles: a lone warp per scheduler issues about one instruction every
+// four cycles, and at four warps the decode of a K step (about 550 instructions per warp) took
+// twice as long as its eight MMAs; two warps per scheduler hide each other's latencies.
 // Weight rows per CTA (MMA N) is a template argument: 256 for large grids; 64 when 256-row tiles
 // would leave most SMs without a CTA (few tokens and a narrow output, e.g. 64 tokens x 8192 rows).
 template <int ROWS, int TOK = 256>
@@ -45,7 +50,9 @@ struct T5Cfg {
     static constexpr int PREFETCH = ROWS >= 256 ? 2 : 6;           // K steps of weight tiles requested ahead
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024;       // + slack to align the ring to 1024 bytes
     static constexpr int TMEM_COLS = (TOK / 128) * ROWS < 32 ? 32 : (TOK / 128) * ROWS;  // one accumulator of ROWS columns per token half
-    static constexpr int TILES_PER_WARP = ROWS / TILE_ROWS / 4;    // row tiles each decoder warp handles
+    static constexpr int DECODERS = ROWS >= 256 ? 8 : 4;           // decoder warps
+    static constexpr int THREADS = (DECODERS + 2) * 32;
+    static constexpr int TILES_PER_WARP = ROWS / TILE_ROWS / DECODERS;  // row tiles each decoder warp handles
 };
 constexpr long long T5_SPIN_CYCLES = 400000000LL;  // about 0.2 s
 
@@ -54,6 +61,14 @@ struct Tc5Params {
     int32_t* acc;       // [ncols][out]
     unsigned* status;
     int out, nrt, nkt, ncols;
+    // gated epilogue (GATED kernel): `tiles` holds the gate matrix followed by the up matrix (ff rows
+    // each); a CTA takes 128 gate rows and the matching 128 up rows, and writes
+    // gated[token][channel] = act(gate * sx[token] * sg) * (up * sx[token] * su) as float32 instead
+    // of two int32 accumulators per channel
+    float* gated;       // [ncols][ff]
+    const float* sx;    // [ncols] activation scales (one term per token)
+    float sg, su;
+    int ff, ffn_act;
 };
 
 __device__ __forceinline__ bool t5_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned* status,
@@ -83,16 +98,28 @@ __device__ __forceinline__ uint64_t t5_desc(uint32_t smem_addr) {
            (2ull << 61);
 }
 
+__device__ __forceinline__ void t5_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+
 // codes {0,1,2} in four bytes -> signed bytes {-1,0,+1}
 __device__ __forceinline__ uint32_t t5_s8(uint32_t codes) { return (codes + 0x7f7f7f7fu) ^ 0x80808080u; }
 
-template <int ROWS, int T5_TOK = 256>
-__global__ void __launch_bounds__(T5_THREADS, T5_TOK == 128 ? 2 : 1)
+template <int ROWS, int T5_TOK = 256, bool GATED = false>
+__global__ void __launch_bounds__(T5Cfg<ROWS, T5_TOK>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Tc5Params p) {
     using Cfg = T5Cfg<ROWS, T5_TOK>;
     constexpr int T5_A_BYTES = Cfg::A_BYTES, A_HALF = 128 * TILE_K;
     constexpr int T5_ROWS = ROWS, T5_STAGE_BYTES = Cfg::STAGE_BYTES, TPW = Cfg::TILES_PER_WARP;
-    constexpr int T5_STAGES = Cfg::STAGES, PF = Cfg::PREFETCH;
+    constexpr int T5_STAGES = Cfg::STAGES, PF = Cfg::PREFETCH, NDW = Cfg::DECODERS;
     extern __shared__ unsigned char t5_raw[];
     __shared__ __align__(8) unsigned long long s_full[T5_STAGES], s_empty[T5_STAGES], s_accf;
     __shared__ uint32_t s_tmem;
@@ -106,13 +133,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < T5_STAGES; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_full[s])), "r"(128 + 1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_full[s])), "r"(NDW * 32 + 1));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_empty[s])), "r"(1));
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_accf)), "r"(1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {  // the whole warp allocates the accumulators' tensor-memory columns (one CTA per SM)
+    if (warp == NDW) {  // the whole warp allocates the accumulators' tensor-memory columns (one CTA per SM)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)),
                      "r"(Cfg::TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -122,7 +149,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
-    if (warp < 4) {
+    if (warp < NDW) {
         // ---------------- weight decoders: warp w owns row tiles TPW w .. TPW w + TPW - 1 of the CTA's
         const int g = lane >> 2, t = lane & 3;
         // weight tiles are requested PF K steps ahead of their decode, so that the L2 / HBM latency
@@ -131,7 +158,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
         auto fetch = [&](int kt, uint4 (&dst)[TPW]) {
 #pragma unroll
             for (int u = 0; u < TPW; ++u) {
-                const int rt = rt0 + warp * TPW + u;
+                int rt = rt0 + warp * TPW + u;
+                if constexpr (GATED) {
+                    // operand rows 0-127: gate row tiles 8 blockIdx.y ..; rows 128-255: the same channels of the up matrix
+                    const int i = warp * TPW + u, ch_rt = (int)blockIdx.y * 8 + (i & 7), ff_rt = p.ff / TILE_ROWS;
+                    rt = ch_rt < ff_rt ? (i < 8 ? ch_rt : ff_rt + ch_rt) : p.nrt;  // past the last channel: zero weights
+                }
                 dst[u] = (rt < p.nrt && kt < p.nkt)
                              ? ld_stream_v4(p.tiles + ((size_t)rt * p.nkt + kt) * 32 + lane)
                              : make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
@@ -139,6 +171,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
         };
 #pragma unroll
         for (int par = 0; par < PF; ++par) fetch(par, wv[par]);
+#ifdef RB_TRACE
+        TraceRec trd = {};
+        const bool tracedd = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
+        unsigned long long tld = gtime(), t0d = tld;
+#endif
         for (int kt2 = 0; kt2 < p.nkt; kt2 += PF) {
 #pragma unroll
           for (int par = 0; par < PF; ++par) {
@@ -149,6 +186,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                 kt2 = p.nkt;  // leave both loops
                 break;
             }
+#ifdef RB_TRACE
+            if (tracedd) { const unsigned long long n_ = gtime(); trd.t[0] += n_ - tld; tld = n_; }
+#endif
             const uint32_t bbase = ring + s * T5_STAGE_BYTES + T5_A_BYTES;
 #pragma unroll
             for (int u = 0; u < TPW; ++u) {
@@ -174,21 +214,76 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s_full[s])) : "memory");
             fetch(kt + PF, wv[par]);
+#ifdef RB_TRACE
+            if (tracedd) { const unsigned long long n_ = gtime(); trd.t[1] += n_ - tld; tld = n_; }
+#endif
           }
         }
+#ifdef RB_TRACE
+        if (tracedd) {
+            trd.t[2] = gtime() - t0d;
+            trd.t[7] = (unsigned long long)p.nkt;
+            trd.kind = 601;
+            unsigned idx_ = atomicAdd(&g_trace_n, 1u);
+            if (idx_ < 4096) g_trace[idx_] = trd;
+        }
+#endif
         // ---------------- epilogue: lane = token, 32 columns (weight rows) per load
         // (warp-uniform decision: the tensor-memory loads below are warp-wide instructions)
         const bool acc_ok = !*abort_flag && t5_wait(smem_u32(&s_accf), 0, abort_flag, p.status, 0x7c000002u);
         if (__all_sync(0xffffffffu, acc_ok)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row0 = rt0 * TILE_ROWS;
+            // a warp reaches the tensor-memory lanes of its quarter (warp % 4); with eight warps the two
+            // groups of four split the (token half, 32-row chunk) pairs between them
+            constexpr int NCH = T5_ROWS / 32, GROUPS = NDW / 4;
+            const int wq = warp & 3, grp = warp >> 2;
+            if constexpr (GATED) {
+                // lane = token; per item 32 channels: gate accumulators in columns [32 ch, +32), up in [128 + 32 ch, +32)
 #pragma unroll 1
-            for (int half = 0; half < nhalf; ++half) {
-                const int token = tok0 + half * 128 + warp * 32 + lane;
+                for (int item = grp; item < nhalf * (NCH / 2); item += GROUPS) {
+                    const int half = item / (NCH / 2), ch = item - half * (NCH / 2);
+                    const int token = tok0 + half * 128 + wq * 32 + lane;
+                    uint32_t gv[32], uv[32];
+                    const uint32_t taddr = tmem + ((uint32_t)(wq * 32) << 16) + (uint32_t)(half * ROWS + ch * 32);
+                    t5_ld32(taddr, gv);
+                    t5_ld32(taddr + 128u, uv);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int c0 = (int)blockIdx.y * 128 + ch * 32;
+                    if (token < p.ncols && c0 < p.ff) {
+                        const float sxv = __ldg(p.sx + token);
+                        float* dst = p.gated + (size_t)token * p.ff + c0;
+                        float r[32];
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) {
+                            const float g = ((float)(int32_t)gv[q] * sxv) * p.sg, u = ((float)(int32_t)uv[q] * sxv) * p.su;
+                            if (p.ffn_act == ROTOR_B200_FFN_RELU2) {
+                                const float a = fmaxf(g, 0.f);
+                                r[q] = a * a * u;
+                            } else {
+                                const float c = fminf(fmaxf(u, -20.f), 20.f);
+                                r[q] = g * (c / (1.f + expf(-c)));
+                            }
+                        }
+                        if (c0 + 32 <= p.ff && (p.ff & 3) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                *reinterpret_cast<float4*>(dst + 4 * q) = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 32; ++q)
+                                if (c0 + q < p.ff) dst[q] = r[q];
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
-                for (int ch = 0; ch < T5_ROWS / 32; ++ch) {
+            for (int item = grp; item < nhalf * NCH; item += GROUPS) {
+                const int half = item / NCH, ch = item - half * NCH;
+                const int token = tok0 + half * 128 + wq * 32 + lane;
+                {
                     uint32_t v[32];
-                    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(half * ROWS + ch * 32);
+                    const uint32_t taddr = tmem + ((uint32_t)(wq * 32) << 16) + (uint32_t)(half * ROWS + ch * 32);
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -217,7 +312,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                 }
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == NDW) {
         // ---------------- token operand by TMA
         if (lane == 0) {
             for (int kt = 0; kt < p.nkt; ++kt) {
@@ -243,10 +338,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
             // kind::i8, S32 accumulate, signed x signed, both operands K-major, N = 256, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(T5_ROWS >> 3) << 17) | ((128u >> 4) << 24);
             bool ok = true;
+#ifdef RB_TRACE
+            TraceRec trm = {};
+            const bool traced = blockIdx.x == 0 && blockIdx.y == 0;
+            unsigned long long tl = gtime(), t0m = tl;
+#endif
             for (int kt = 0; kt < p.nkt && ok; ++kt) {
                 const int s = kt % T5_STAGES;
                 ok = t5_wait(smem_u32(&s_full[s]), (kt / T5_STAGES) & 1, abort_flag, p.status, 0x7c000004u);
                 if (!ok) break;
+#ifdef RB_TRACE
+                if (traced) { const unsigned long long n_ = gtime(); trm.t[0] += n_ - tl; tl = n_; }
+#endif
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t abase = ring + s * T5_STAGE_BYTES, bbase = abase + T5_A_BYTES;
                 for (int half = 0; half < nhalf; ++half)
@@ -268,7 +371,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                  smem_u32(&s_empty[s]))
                              : "memory");
+#ifdef RB_TRACE
+                if (traced) { const unsigned long long n_ = gtime(); trm.t[1] += n_ - tl; tl = n_; }
+#endif
             }
+#ifdef RB_TRACE
+            if (traced) {
+                trm.t[2] = gtime() - t0m;
+                trm.t[7] = (unsigned long long)p.nkt;
+                trm.kind = 600;
+                unsigned idx_ = atomicAdd(&g_trace_n, 1u);
+                if (idx_ < 4096) g_trace[idx_] = trm;
+            }
+#endif
             if (ok)
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                  smem_u32(&s_accf))
@@ -284,7 +399,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 4) {
+    if (warp == NDW) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS));
     }
@@ -314,6 +429,8 @@ int configure_gemm_tcgen05() {
     g_encode = (EncodeTiledFn)fn;
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<256>::SMEM));
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<64>::SMEM));
+    RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256, 256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 T5Cfg<256>::SMEM));
     g_tc5_ready.here() = true;
     return ROTOR_B200_OK;
 }
@@ -322,7 +439,7 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
                         cudaStream_t st) {
     int rc = configure_gemm_tcgen05();
     if (rc) return rc;
-    Tc5Params p;
+    Tc5Params p = {};
     p.tiles = (const uint4*)tiles;
     p.acc = acc;
     p.status = library_status_word();
@@ -350,11 +467,52 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
     }
     if (tok_tiles * ((rows + 255) / 256) < sms) {  // 256-row tiles would leave SMs idle
         dim3 grid(tok_tiles, (rows + 63) / 64);
-        gemm_tcgen05_kernel<64><<<grid, T5_THREADS, T5Cfg<64>::SMEM, st>>>(tmap, p);
+        gemm_tcgen05_kernel<64><<<grid, T5Cfg<64>::THREADS, T5Cfg<64>::SMEM, st>>>(tmap, p);
     } else {
         dim3 grid(tok_tiles, (rows + 255) / 256);
-        gemm_tcgen05_kernel<256><<<grid, T5_THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);
+        gemm_tcgen05_kernel<256><<<grid, T5Cfg<256>::THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);
     }
+    return launch_status();
+}
+
+// Gate/up product with the gating in the epilogue: `tiles` holds the gate matrix followed by the up
+// matrix (ff rows each, ff a multiple of 16), one activation term per token.  Writes
+// gated[token][channel] as float32; no int32 accumulator leaves the kernel.
+bool gemm_tcgen05_gated_supported(size_t ff, size_t in, int ncols, const void* xq) {
+    return ff % TILE_ROWS == 0 && ncols >= 256 && gemm_tcgen05_supported(2 * ff, in, ncols, xq);
+}
+
+int launch_gemm_tcgen05_gated(const void* tiles, size_t ff, size_t in, const int8_t* xq, const float* sx, int ncols,
+                              float sg, float su, int ffn_act, float* gated, cudaStream_t st) {
+    int rc = configure_gemm_tcgen05();
+    if (rc) return rc;
+    if (!gemm_tcgen05_gated_supported(ff, in, ncols, xq)) return ROTOR_B200_ERR_SHAPE;
+    Tc5Params p = {};
+    p.tiles = (const uint4*)tiles;
+    p.status = library_status_word();
+    p.out = (int)(2 * ff);
+    p.nrt = (int)(2 * ff / TILE_ROWS);
+    p.nkt = (int)(kpad_of(in) / TILE_K);
+    p.ncols = ncols;
+    p.gated = gated;
+    p.sx = sx;
+    p.sg = sg;
+    p.su = su;
+    p.ff = (int)ff;
+    p.ffn_act = ffn_act;
+    if (!p.status) return ROTOR_B200_ERR_CUDA;
+    const size_t kpad = kpad_of(in);
+    CUtensorMap tmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t)kpad, (cuuint64_t)ncols};
+    const cuuint64_t gstride[1] = {(cuuint64_t)kpad};
+    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, 128u};
+    const cuuint32_t estride[2] = {1u, 1u};
+    if (g_encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)xq, gdim, gstride, box, estride,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return ROTOR_B200_ERR_CUDA;
+    dim3 grid((ncols + 255) / 256, (unsigned)((ff + 127) / 128));
+    gemm_tcgen05_kernel<256, 256, true><<<grid, T5Cfg<256>::THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);
     return launch_status();
 }
 

@@ -363,6 +363,24 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
 // Out: accumulators of the down projection (view *vd), activation scales in sx[1].
 static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView* vd, cudaStream_t st) {
     const int cols = rows * c.terms;
+    if (c.terms == 1 && c.tp_size <= 1 && c.variant == ROTOR_B200_VARIANT_AUTO &&
+        gemm_tcgen05_gated_supported((size_t)c.ff, c.d, cols, c.xq)) {
+        // prompt-sized row counts, one activation term: the gate/up product applies the gating in its epilogue and
+        // writes float32 gated rows (into the accumulator area: a quarter of the bytes of the two int32 halves);
+        // the stage that follows only has to sub-norm and quantise them
+        float* gated = reinterpret_cast<float*>(c.accA);
+        RB_TRY(launch_gemm_tcgen05_gated(L.gate_up_tiles, (size_t)c.ff, c.d, c.xq, c.sx[0], cols, L.gate_scale, L.up_scale,
+                                         c.ffn_act, gated, st));
+        VecStageParams gp = {};
+        gp.mode = VS_PLAIN;
+        gp.n = c.ff;
+        gp.src = gated;
+        gp.norm1 = L.ffn_sub_norm;
+        gp.eps = c.eps;
+        quant_sink(c, gp, 1, c.ff);
+        RB_TRY(launch_vec_stage(gp, rows, st));
+        return gemv(c, L.down_tiles, c.d, c.ff, cols, 1, c.accB, vd, st);
+    }
     AccView va;
     RB_TRY(gemv(c, L.gate_up_tiles, 2 * (size_t)c.ff, c.d, cols, 0, c.accA, &va, st));
     VecStageParams fp = {};
