@@ -42,10 +42,12 @@ struct SampleParams {
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const __grid_constant__ SampleParams p) {
     __shared__ float s_red[64];
     __shared__ unsigned s_cnt[256];
-    __shared__ float s_mass[256];
+    // bin masses in 2^-40 fixed point: integer atomics add in any order to the same bits, so the cut (and with it
+    // the drawn token) does not depend on which thread's atomic lands first
+    __shared__ unsigned long long s_mass[256];
     __shared__ unsigned s_prefix;      // bit prefix of the cut found so far
     __shared__ unsigned s_cnt_above;   // tokens strictly above the current prefix range
-    __shared__ float s_mass_above;
+    __shared__ unsigned long long s_mass_above;
     __shared__ unsigned s_scan_u[SMP_THREADS / 32];
     __shared__ float s_scan_f[SMP_THREADS / 32];
     __shared__ int s_token;
@@ -64,18 +66,19 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const __grid_consta
     z = block_sum(z, s_red);
 
     // ---- radix select of the cut over the bits of e (positive floats order like their bits)
-    const float want_mass = p.top_p * z;                 // top-p: descending mass to reach
+    const double fix = 1099511627776.0;                  // 2^40; e <= 1, so a bin sum stays far below 2^63
+    const unsigned long long want_mass = (unsigned long long)((double)p.top_p * (double)z * fix);  // top-p: descending mass to reach
     const unsigned want_cnt = (unsigned)(p.top_k < V ? p.top_k : V);  // top-k
     if (tid == 0) {
         s_prefix = 0;
         s_cnt_above = 0;
-        s_mass_above = 0.f;
+        s_mass_above = 0ull;
     }
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
         if (tid < 256) {
             s_cnt[tid] = 0;
-            s_mass[tid] = 0.f;
+            s_mass[tid] = 0ull;
         }
         __syncthreads();
         const unsigned prefix = s_prefix;
@@ -86,13 +89,13 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const __grid_consta
             if ((b & himask) == prefix) {
                 const unsigned bin = (b >> shift) & 255u;
                 atomicAdd(&s_cnt[bin], 1u);
-                atomicAdd(&s_mass[bin], e);
+                atomicAdd(&s_mass[bin], (unsigned long long)((double)e * fix));
             }
         }
         __syncthreads();
         if (tid == 0) {  // walk the bins from the largest values down
             unsigned cnt = s_cnt_above;
-            float mass = s_mass_above;
+            unsigned long long mass = s_mass_above;
             int bin = 255;
             for (; bin > 0; --bin) {
                 const bool reached = p.mode == 0 ? (cnt + s_cnt[bin] >= want_cnt) : (mass + s_mass[bin] >= want_mass);
@@ -113,8 +116,8 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const __grid_consta
     if (p.mode == 0) {
         ties_wanted = want_cnt - s_cnt_above;
     } else {
-        const float missing = want_mass - s_mass_above;
-        ties_wanted = cut_e > 0.f ? (unsigned)ceilf(missing / cut_e) : 1u;
+        const double missing = want_mass > s_mass_above ? (double)(want_mass - s_mass_above) / fix : 0.0;
+        ties_wanted = cut_e > 0.f ? (unsigned)ceil(missing / (double)cut_e) : 1u;
         if (ties_wanted < 1u) ties_wanted = 1u;
     }
 

@@ -59,6 +59,15 @@ def test_edge_cases(ops):
     assert set(got.tolist()) == set(range(7))          # ties admitted in vocabulary order
     got = _draws(ops, flat, 1, 0, 0.25, 1.0, 9, 2000)
     assert set(got.tolist()) == set(range(75))         # 75 of 300 equal tokens carry a quarter of the mass
+    # the mass of the kept set sits exactly on the threshold here: the bin masses are summed in fixed point, so
+    # repeated runs keep the same set and draw the same tokens whatever order the atomics land in
+    for _ in range(3):
+        assert np.array_equal(_draws(ops, flat, 1, 0, 0.25, 1.0, 9, 2000), got)
+    near = logits.copy()
+    near[:64] = near.max() + 1.0                         # 64 equal leaders: p = 0.5 of their mass cuts through the ties
+    first = _draws(ops, near, 1, 0, 0.5, 1.0, 21, 1000)
+    for _ in range(3):
+        assert np.array_equal(_draws(ops, near, 1, 0, 0.5, 1.0, 21, 1000), first)
     full = _draws(ops, logits, 1, 0, 1.0, 1.0, 11, 3000)                                    # p = 1 keeps everything
     assert len(set(full.tolist())) > 200
     a = ops.sample(torch.from_numpy(logits[None, :]).cuda(), 1, top_p=0.9, seed=5, counter=17).cpu().numpy()
