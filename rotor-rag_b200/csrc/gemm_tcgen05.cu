@@ -416,8 +416,7 @@ bool gemm_tcgen05_supported(size_t out, size_t in, int ncols, const void* xq) {
     static const bool off = getenv("ROTOR_B200_NO_TCGEN05") != nullptr;  // measurement aid: legacy mma.sync path
     // from 32 tokens on: with fewer than 256 the tile is partly empty, but the product is then bound by
     // the weight stream, which this kernel moves faster than the mma.sync kernel does
-    static const int min_cols = getenv("ROTOR_B200_TCGEN05_MIN") ? atoi(getenv("ROTOR_B200_TCGEN05_MIN")) : 32;
-    return !off && ncols >= min_cols && out >= 16 && in >= 4 && ((uintptr_t)xq & 15) == 0;
+    return !off && ncols >= 32 && out >= 16 && in >= 4 && ((uintptr_t)xq & 15) == 0;
 }
 
 int configure_gemm_tcgen05() {

@@ -458,19 +458,13 @@ static bool fused_step_ok(const Model& m, int batch, int seq) {
     const Ctx& c = m.c;
     static const bool off = getenv("ROTOR_B200_NO_FUSED_STEP") != nullptr;  // measurement aid
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
-    static const bool tp_unfused = getenv("ROTOR_B200_TP_UNFUSED") != nullptr;  // measurement aid
-    const bool tp_ok = c.tp_size <= 1 || (!tp_unfused && c.terms == 1 && tp_fused_ready(c.tp) &&
-                                          (size_t)batch * c.d <= (size_t)XCH_CAP);
+    const bool tp_ok = c.tp_size <= 1 || (c.terms == 1 && tp_fused_ready(c.tp) && (size_t)batch * c.d <= (size_t)XCH_CAP);
     const bool shape_ok = !off && tp_ok && seq == 1 && batch <= FUSED_MAX_ROWS && batch <= c.max_batch &&
                           c.terms <= 3 && batch * c.terms <= 8 && c.ff % 16 == 0;
     const bool q = fused_gemv_supported(qkv_out, c.d, batch, c.terms, 1, 0);
     const bool o = fused_gemv_supported(c.d, c.dq, batch, c.terms, 1, c.n_heads * c.nsplit);
     const bool g = fused_gemv_supported(c.ff, c.d, batch, c.terms, 2, 0);
     const bool dn = fused_gemv_supported(c.d, c.ff, batch, c.terms, 1, 0);
-    static const bool verbose = getenv("ROTOR_B200_VERBOSE") != nullptr;
-    if (verbose && seq == 1)
-        fprintf(stderr, "rotor_b200: fused step shape %d qkv %d o %d gate/up %d down %d (batch %d terms %d tp %d)\n",
-                (int)shape_ok, (int)q, (int)o, (int)g, (int)dn, batch, c.terms, c.tp_size);
     return shape_ok && q && o && g && dn;
 }
 

@@ -256,11 +256,10 @@ bool row_stage_supported(const VecStageParams& p, int rows) {
 // variant on a grid of resident CTAs; everything else runs one CTA per row.
 template <int V, bool RESID, int TH>
 static int launch_one(const VecStageParams& p, int rows, cudaStream_t st) {
-    static const bool no_pf = getenv("ROTOR_B200_ROWSTAGE_NO_PREFETCH") != nullptr;  // comparison aid
     const bool from_acc = p.mode == VS_OPROJ || p.mode == VS_FFN || p.mode == VS_DOWN || p.mode == VS_DEQ;
     const size_t pieces = (size_t)p.terms * (p.mode == VS_FFN ? 2 : 1) + (RESID ? 1 : 0);
     const size_t smem = pieces * (size_t)p.n * sizeof(int);
-    if (from_acc && !no_pf && smem <= 200 * 1024) {
+    if (from_acc && smem <= 200 * 1024) {
         auto* k = row_stage_kernel<V, RESID, TH, true>;
         static PerDevice<size_t> once;  // per instantiation and device
         static PerDevice<int> sm_counts;
@@ -300,8 +299,7 @@ int launch_row_stage(const VecStageParams& p, int rows, cudaStream_t st) {
     if (width > 4 * 16 * RS_THREADS)  // wide rows without a residual: 512 threads, up to 14 groups each
         return launch_one<14, false, RS_WIDE_THREADS>(p, rows, st);
     const int v = (width / 4 + RS_THREADS - 1) / RS_THREADS;
-    static const bool ffn512 = getenv("ROTOR_B200_FFN_STAGE_128") == nullptr;  // comparison aid
-    if (ffn512 && v > 8 && p.mode != VS_OPROJ && p.mode != VS_DOWN)
+    if (v > 8 && p.mode != VS_OPROJ && p.mode != VS_DOWN)
         // 4097..8192 elements without a residual (the 2B FFN row): four groups per thread at 512 threads
         // keep more warps per SM busy than fourteen groups at 128
         return launch_one<4, false, RS_WIDE_THREADS>(p, rows, st);
