@@ -18,7 +18,7 @@ namespace rb {
 constexpr int FG_THREADS = 512;
 constexpr int FG_WARPS = FG_THREADS / 32;
 constexpr int FG_U = 4;        // weight tiles in flight per warp
-constexpr int FG_L2_AHEAD = 12;  // deep variant: further tiles per warp pulled into L2 before the wait
+constexpr int FG_L2_AHEAD = 32;  // deep variant: further tiles per warp pulled into L2 before the wait
 constexpr size_t FG_STAGE_MAX = 96 * 1024;  // shallow variant: most tile bytes a CTA stages
 constexpr int FG_V = 4;        // float4 groups per thread in the register prologue: input width <= 8192
 constexpr int FG_V_NARROW = 2; // shallow variant, stages that hold four arrays per group: width <= 4096
@@ -141,14 +141,6 @@ __device__ __forceinline__ ProductCtx product_ctx(const FusedGemvParams& p, unsi
     return c;
 }
 
-__device__ __forceinline__ const uint4* product_tile_ptr(const FusedGemvParams& p, const ProductCtx& c, int lt) {
-    const int lane = threadIdx.x & 31;
-    const int slot = lt / p.nkt, kt = lt - slot * p.nkt;
-    const int u = c.u0 + slot / p.halves, half = slot - (slot / p.halves) * p.halves;
-    const size_t rt = (size_t)half * p.units + u;
-    return p.tiles + (rt * p.nkt + kt) * 32 + lane;
-}
-
 // Shallow variant: copies the CTA's tiles into shared memory, one contiguous span per half
 // (constants: may run before the activations this product consumes exist).  Completion:
 // cp.async.wait_group 0 by every thread, then a CTA barrier.
@@ -166,12 +158,31 @@ __device__ __forceinline__ void product_stage(const FusedGemvParams& p, const Pr
 // Deep variant: requests the warp's first FG_U weight tiles and pulls up to FG_L2_AHEAD more into L2
 // (constants: may run before the activations this product consumes exist).
 __device__ __forceinline__ void product_prefetch(const FusedGemvParams& p, const ProductCtx& c, uint4 (&wv)[FG_U]) {
+    // one division for the first tile, the rest advance by counting
+    const int lane = threadIdx.x & 31;
+    int slot = c.w0 / p.nkt, kt = c.w0 - slot * p.nkt;
+    auto slot_ptr = [&](int sl) {
+        const int u = c.u0 + (p.halves == 2 ? sl >> 1 : sl), half = p.halves == 2 ? (sl & 1) : 0;
+        return p.tiles + ((size_t)half * p.units + u) * p.nkt * 32 + lane;
+    };
+    const uint4* ptr = slot_ptr(slot) + (size_t)kt * 32;
+    auto advance = [&]() {
+        ptr += 32;
+        if (++kt == p.nkt) {
+            kt = 0;
+            ptr = slot_ptr(++slot);
+        }
+    };
 #pragma unroll
     for (int u = 0; u < FG_U; ++u)
-        if (c.w0 + u < c.w1) wv[u] = ld_stream_v4(product_tile_ptr(p, c, c.w0 + u));
-    if ((threadIdx.x & 7) == 0) {  // four 128-byte lines per tile
-        const int end = min(c.w1, c.w0 + FG_U + FG_L2_AHEAD);
-        for (int lt = c.w0 + FG_U; lt < end; ++lt) prefetch_l2(product_tile_ptr(p, c, lt));
+        if (c.w0 + u < c.w1) {
+            wv[u] = ld_stream_v4(ptr);
+            advance();
+        }
+    const int end = min(c.w1, c.w0 + FG_U + FG_L2_AHEAD);
+    for (int lt = c.w0 + FG_U; lt < end; ++lt) {  // four 128-byte lines per tile
+        if ((threadIdx.x & 7) == 0) prefetch_l2(ptr);
+        advance();
     }
 }
 
@@ -204,40 +215,92 @@ __device__ __forceinline__ void product_run(const FusedGemvParams& p, const Prod
         }
         if ((int)threadIdx.x < p.cols) s_xsum[threadIdx.x] = __ldcg(p.xsum_in + threadIdx.x);
     } else if constexpr (WIDE) {
+        // Every pass walks the row in the same pattern (float4 number threadIdx.x + k * blockDim.x), so a
+        // thread only ever touches its own elements and the passes need no barrier beyond the reductions'.
+        // Loads are issued WB at a time: one L2 round trip per batch instead of one per element group.
+        constexpr int WB = 7;
         float* row = aux;  // [n] float32
-        const int n = p.st.n;
+        const int n = p.st.n, step = blockDim.x * 4;
+        const XchScalarDev* x = (TP && p.xs.size) ? &p.xs : nullptr;
         for (int m = 0; m < p.rows; ++m) {
-            __syncthreads();  // the previous row's quantiser is done with the buffer
-            for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4)
-                *reinterpret_cast<float4*>(row + i) = ldcg4(p.st.y + (size_t)m * n + i);
-            __syncthreads();
-            __shared__ float s_ext[2];
-            const XchScalarDev* x = (TP && p.xs.size) ? &p.xs : nullptr;
+            const float* src = p.st.y + (size_t)m * n;
+            float ss = 0.f, mx = 0.f;
+            for (int i0 = threadIdx.x * 4; i0 < n; i0 += step * WB) {
+                float4 r[WB];
+#pragma unroll
+                for (int u = 0; u < WB; ++u)
+                    if (i0 + u * step < n) r[u] = ldcg4(src + i0 + u * step);
+#pragma unroll
+                for (int u = 0; u < WB; ++u)
+                    if (i0 + u * step < n) {
+                        *reinterpret_cast<float4*>(row + i0 + u * step) = r[u];
+                        ss += r[u].x * r[u].x + r[u].y * r[u].y + r[u].z * r[u].z + r[u].w * r[u].w;
+                        mx = fmaxf(mx, amax4(r[u]));
+                    }
+            }
             if (p.st.norm1) {
-                if (x && p.st.xi_sum) {  // sum of squares of the whole (sharded) row
-                    float ss = 0.f;
-                    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += row[i] * row[i];
-                    ss = block_sum(ss, scratch);
-                    ss = xch_scalar(*x, p.st.xi_sum - 1, m, ss, false, writer, scratch);
-                    if (threadIdx.x == 0) s_ext[0] = ss;
-                    __syncthreads();
-                    rmsnorm_inplace(row, n, p.st.norm1, p.st.eps, scratch, &s_ext[0], p.st.norm_n);
-                } else {
-                    rmsnorm_inplace(row, n, p.st.norm1, p.st.eps, scratch);
+                float4 wn[WB];  // first batch of norm weights in flight across the reduction
+#pragma unroll
+                for (int u = 0; u < WB; ++u) {
+                    const int i = threadIdx.x * 4 + u * step;
+                    if (i < n) wn[u] = __ldg(reinterpret_cast<const float4*>(p.st.norm1 + i));
+                }
+                ss = block_sum(ss, scratch);
+                if (x && p.st.xi_sum) ss = xch_scalar(*x, p.st.xi_sum - 1, m, ss, false, writer, scratch);
+                const float inv = 1.0f / sqrtf(ss / (float)(p.st.norm_n ? p.st.norm_n : n) + p.st.eps);
+                mx = 0.f;
+                for (int i0 = threadIdx.x * 4; i0 < n; i0 += step * WB) {
+                    if (i0 != (int)threadIdx.x * 4) {
+#pragma unroll
+                        for (int u = 0; u < WB; ++u)
+                            if (i0 + u * step < n) wn[u] = __ldg(reinterpret_cast<const float4*>(p.st.norm1 + i0 + u * step));
+                    }
+#pragma unroll
+                    for (int u = 0; u < WB; ++u)
+                        if (i0 + u * step < n) {
+                            float4* rp = reinterpret_cast<float4*>(row + i0 + u * step);
+                            float4 v = *rp;
+                            v.x = v.x * inv * wn[u].x;
+                            v.y = v.y * inv * wn[u].y;
+                            v.z = v.z * inv * wn[u].z;
+                            v.w = v.w * inv * wn[u].w;
+                            *rp = v;
+                            mx = fmaxf(mx, amax4(v));
+                        }
                 }
             }
-            const float* given = nullptr;
-            if (x && p.st.xi_max) {  // absolute maximum of the whole row
-                float mx = 0.f;
-                for (int i = threadIdx.x; i < n; i += blockDim.x) mx = fmaxf(mx, fabsf(row[i]));
+            int8_t* xq = xs + (size_t)m * p.st.terms * xs_stride;
+            for (int t = 0; t < p.st.terms; ++t) {
+                if (t > 0) {
+                    mx = 0.f;
+                    for (int i = threadIdx.x * 4; i < n; i += step) mx = fmaxf(mx, amax4(*reinterpret_cast<float4*>(row + i)));
+                }
+                if (threadIdx.x == 0) s_xsum[m * p.st.terms + t] = 0;  // ordered before the atomics by the reduction's barrier
                 mx = block_max(mx, scratch);
-                mx = xch_scalar(*x, p.st.xi_max - 1, m, mx, true, writer, scratch);
-                if (threadIdx.x == 0) s_ext[1] = mx;
-                __syncthreads();
-                given = &s_ext[1];
+                if (t == 0 && x && p.st.xi_max) mx = xch_scalar(*x, p.st.xi_max - 1, m, mx, true, writer, scratch);
+                const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
+                const float rs = __fdiv_rn(1.0f, s);
+                const bool resid = t + 1 < p.st.terms;
+                int lsum = 0;
+                for (int i = threadIdx.x * 4; i < p.st.kpad; i += step) {
+                    int packed = 0;
+                    if (i < n) {
+                        float4* rp = reinterpret_cast<float4*>(row + i);
+                        float4 v = *rp;
+                        if (resid) {
+                            packed = quant4_pack<true>(v, s, rs, lsum);
+                            *rp = v;
+                        } else {
+                            packed = quant4_pack<false>(v, s, rs, lsum);
+                        }
+                    }
+                    *reinterpret_cast<int*>(xq + (size_t)t * xs_stride + i) = packed;
+                }
+                // read after the prologue's closing barrier: warps add their shares with a shared-memory atomic
+                lsum = warp_sum_i(lsum);
+                if ((threadIdx.x & 31) == 0 && lsum) atomicAdd(&s_xsum[m * p.st.terms + t], lsum);
+                if (threadIdx.x == 0) s_sx[m * p.st.terms + t] = s;
             }
-            quantize_row_from_smem(row, n, p.st.kpad, p.st.terms, xs + (size_t)m * p.st.terms * xs_stride,
-                                   s_sx + m * p.st.terms, s_xsum + m * p.st.terms, scratch, (size_t)xs_stride, given);
         }
     } else {
         const XchScalarDev* x = (TP && p.xs.size) ? &p.xs : nullptr;

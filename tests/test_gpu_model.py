@@ -372,6 +372,24 @@ def test_wide_ffn_generation_step(rb):
     assert model.generate_greedy(prompt, G.N_NEW, use_graph=True) == ids
 
 
+@pytest.mark.parametrize("name", list(G.TINY_MODELS))
+def test_long_cache_generation_step(rb, name):
+    """A cache of 1024 and more positions: one-token attention runs with sixteen slices per KV head
+    (a 16-CTA cluster where the device places one).  Last-position logits after a 1040-token prompt and
+    the next 8 greedy tokens against the oracle, float semantics."""
+    om, _, model = _tiny(rb, name, rb.sem.REFERENCE, max_seq=1100)
+    rng = np.random.default_rng(5150)
+    prompt = rng.integers(0, om["cfg"]["vocab_size"], size=1040).astype(np.int64)
+    ids, steps = O.generate_greedy(om, prompt, 8, O.REFERENCE, return_logits=True)
+    want = ids[len(prompt):]
+    logits, cache = model.forward(prompt[None, :], use_cache=True, logits_positions="last")
+    assert rel_err(logits[0, -1], steps[0]) < TOL
+    nxt, _ = model.forward(np.array([[want[0]]]), past_kv_cache=cache, use_cache=True)
+    assert rel_err(nxt[0, -1], steps[1]) < TOL
+    assert model.generate_greedy(prompt, 8, use_graph=False) == want
+    assert model.generate_greedy(prompt, 8, use_graph=True) == want
+
+
 def test_empty_and_single_element_inputs(rb):
     """Zero token rows give empty outputs (the reference's NumPy path does the same); one row of one
     sequence is the smallest real call."""
