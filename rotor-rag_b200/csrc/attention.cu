@@ -421,6 +421,67 @@ __device__ __forceinline__ void attn_warp_chunk(const float4 (&q4)[D / 32], cons
     m_run = m_new;
 }
 
+// The same step of the online softmax for the streaming kernel, where many warps per SM make issue
+// slots, not latency, the limit: fewer instructions per key.  K and V rows lie in shared memory with a
+// row stride of D + AC_PAD floats (consecutive rows start four banks apart, so 32 lanes reading the
+// same piece of 32 different rows do not collide).  Scores: lane j multiplies key j's whole row with q
+// (shared memory, pre-scaled; every lane reads the same piece: a broadcast) in four independent
+// chains, no shuffles.  Weighted V: the probabilities go through `ps` (32 floats of this warp) and
+// come back four at a time as broadcasts; lane l accumulates output dimensions (D / 32) l .. in two
+// alternating sets.
+constexpr int AC_PAD = 4;
+
+template <int D>
+__device__ __forceinline__ void attn_warp_chunk_rows(const float* qs, const float* Kc, const float* Vc, float* ps, int nk,
+                                                     int lane, float& m_run, float& l_run, float4& o) {
+    constexpr int KS = D + AC_PAD, OPL = D / 32, C4 = D / 4;
+    float my_s = -INFINITY;
+    if (lane < nk) {
+        const float4* kr = reinterpret_cast<const float4*>(Kc + (size_t)lane * KS);
+        const float4* qr = reinterpret_cast<const float4*>(qs);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < C4; ++c) {
+            const float4 k4 = kr[c], q4 = qr[c];
+            acc[c & 3] += q4.x * k4.x + q4.y * k4.y + q4.z * k4.z + q4.w * k4.w;
+        }
+        my_s = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    }
+    const float m_new = fmaxf(m_run, warp_max(my_s));
+    const float keep = m_run == -INFINITY ? 0.f : __expf(m_run - m_new);
+    const float pr = lane < nk ? __expf(my_s - m_new) : 0.f;
+    l_run = l_run * keep + warp_sum(pr);
+    __syncwarp();  // the previous chunk's readers of ps are done
+    ps[lane] = pr;
+    __syncwarp();
+    float4 oa = make_float4(o.x * keep, o.y * keep, o.z * keep, o.w * keep), ob = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* vr = Vc + OPL * lane;
+    auto fma_row = [&](float4& acc4, float pj, int j) {
+        if constexpr (OPL == 4) {
+            const float4 v4 = *reinterpret_cast<const float4*>(vr + (size_t)j * KS);
+            acc4.x += pj * v4.x;
+            acc4.y += pj * v4.y;
+            acc4.z += pj * v4.z;
+            acc4.w += pj * v4.w;
+        } else {
+            const float2 v2 = *reinterpret_cast<const float2*>(vr + (size_t)j * KS);
+            acc4.x += pj * v2.x;
+            acc4.y += pj * v2.y;
+        }
+    };
+    int j = 0;
+    for (; j + 4 <= nk; j += 4) {  // rows at and beyond nk are never read: they may hold anything
+        const float4 p4 = *reinterpret_cast<const float4*>(ps + j);
+        fma_row(oa, p4.x, j);
+        fma_row(ob, p4.y, j + 1);
+        fma_row(oa, p4.z, j + 2);
+        fma_row(ob, p4.w, j + 3);
+    }
+    for (; j < nk; ++j) fma_row(oa, ps[j], j);
+    o = make_float4(oa.x + ob.x, oa.y + ob.y, oa.z + ob.z, oa.w + ob.w);
+    m_run = m_new;
+}
+
 template <int D>
 __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(const __grid_constant__ AttnDecodeParams p) {
     extern __shared__ __align__(16) float sm[];
@@ -583,14 +644,14 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(
 // (n_kv_heads, batch), one warp per query head of the group.  q is finished (rotated), the new
 // k / v row is in the cache already.  The CTA streams its sequence's K and V rows through shared
 // memory 32 keys at a time, double buffered with cp.async, and every warp runs the same
-// per-head chunk routine as the cluster kernel; no partials, no merge: one pass over the cache
+// per-head chunk routine (attn_warp_chunk_rows); no partials, no merge: one pass over the cache
 // per group of heads, written as finished attention rows.
 constexpr int AS_KEYS = 32;
 
 template <int D>
 __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int C4 = D / 4, NCH = D / 32, OPL = D / 32;
+    constexpr int C4 = D / 4, OPL = D / 32, KS = D + AC_PAD;
     const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
     const int G = p.n_heads / p.n_kv_heads;  // blockDim.x == 32 * G
     const int hk = blockIdx.x, b = blockIdx.y;
@@ -598,29 +659,26 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(c
     const int T = min(p.past_len[b] + 1, p.max_seq);
     const float* kc = p.k_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
     const float* vc = p.v_cache + ((size_t)b * p.n_kv_heads + hk) * p.max_seq * D;
-    float* Ks = sm;                         // [2][AS_KEYS][D]
-    float* Vs = sm + 2 * AS_KEYS * D;       // [2][AS_KEYS][D]
+    float* qs = sm;                         // [G][D]
+    float* ps = qs + G * D;                 // [G][32]
+    float* Ks = ps + G * 32;                // [2][AS_KEYS][KS]
+    float* Vs = Ks + 2 * AS_KEYS * KS;      // [2][AS_KEYS][KS]
     auto fetch = [&](int chunk, int stage) {
         const int t0 = chunk * AS_KEYS, n = min(AS_KEYS, T - t0);
         for (int idx = tid; idx < n * C4; idx += nthr) {
             const int r = idx / C4, c4 = idx - r * C4;
-            cp_async16(Ks + ((size_t)stage * AS_KEYS + r) * D + 4 * c4, kc + (size_t)(t0 + r) * D + 4 * c4);
-            cp_async16(Vs + ((size_t)stage * AS_KEYS + r) * D + 4 * c4, vc + (size_t)(t0 + r) * D + 4 * c4);
+            cp_async16(Ks + ((size_t)stage * AS_KEYS + r) * KS + 4 * c4, kc + (size_t)(t0 + r) * D + 4 * c4);
+            cp_async16(Vs + ((size_t)stage * AS_KEYS + r) * KS + 4 * c4, vc + (size_t)(t0 + r) * D + 4 * c4);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const int nchunk = (T + AS_KEYS - 1) / AS_KEYS;
     fetch(0, 0);
-    const int l8 = lane & 7;
-    float4 q4[NCH];
-    {
+    if (lane < C4) {  // this warp's q, pre-scaled (read back by the same warp only, after the first CTA barrier)
         const float* qh = p.q + (size_t)b * dq + (size_t)(hk * G + warp) * D;
         const float scale = 1.0f / sqrtf((float)D);
-#pragma unroll
-        for (int e = 0; e < NCH; ++e) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(qh) + (8 * e + l8));
-            q4[e] = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
-        }
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(qh) + lane);
+        reinterpret_cast<float4*>(qs + warp * D)[lane] = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
     }
     float m_run = -INFINITY, l_run = 0.f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -633,8 +691,8 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(c
         }
         __syncthreads();  // chunk c has landed for every thread
         const int st = c & 1;
-        attn_warp_chunk<D>(q4, Ks + (size_t)st * AS_KEYS * D, Vs + (size_t)st * AS_KEYS * D, min(AS_KEYS, T - c * AS_KEYS),
-                           lane, m_run, l_run, o);
+        attn_warp_chunk_rows<D>(qs + warp * D, Ks + (size_t)st * AS_KEYS * KS, Vs + (size_t)st * AS_KEYS * KS,
+                                ps + warp * 32, min(AS_KEYS, T - c * AS_KEYS), lane, m_run, l_run, o);
         __syncthreads();  // every warp is done with this stage before chunk c + 2 overwrites it
     }
     const float inv = 1.0f / l_run;
@@ -654,7 +712,7 @@ static bool attn_decode_stream_ok(const AttnParams& p, int rows) {
 
 static int launch_attn_decode_stream(const AttnParams& p, int rows, cudaStream_t st) {
     const int G = p.n_heads / p.n_kv_heads, D = p.head_dim;
-    const size_t smem = (size_t)4 * AS_KEYS * D * sizeof(float);
+    const size_t smem = ((size_t)G * D + (size_t)G * 32 + (size_t)4 * AS_KEYS * (D + AC_PAD)) * sizeof(float);
     dim3 grid(p.n_kv_heads, rows);
     if (D == 64)
         attn_decode_stream_kernel<64><<<grid, 32 * G, smem, st>>>(p);
@@ -766,8 +824,8 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,

@@ -61,6 +61,7 @@ struct Tc5Params {
     int32_t* acc;       // [ncols][out]
     unsigned* status;
     int out, nrt, nkt, ncols;
+    int kt_per_split;   // > 0: CTA z takes K steps [z kt_per_split, +kt_per_split) and ADDS its sums into zeroed acc
     // gated epilogue (GATED kernel): `tiles` holds the gate matrix followed by the up matrix (ff rows
     // each); a CTA takes 128 gate rows and the matching 128 up rows, and writes
     // gated[token][channel] = act(gate * sx[token] * sg) * (up * sx[token] * su) as float32 instead
@@ -128,6 +129,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok0 = blockIdx.x * T5_TOK, rt0 = blockIdx.y * (T5_ROWS / TILE_ROWS);
     const int nhalf = (T5_TOK > 128 && p.ncols - tok0 > 128) ? 2 : 1;  // token halves of this CTA that hold any token
+    // K steps of this CTA: all of them, or its share when the K range is split over blockIdx.z.  Loops
+    // below count local steps 0 .. nk-1; ktb + step is the position in the matrix.
+    const int ktb = p.kt_per_split ? (int)blockIdx.z * p.kt_per_split : 0;
+    const int nk = p.kt_per_split ? min(p.kt_per_split, p.nkt - ktb) : p.nkt;
     volatile int* abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
@@ -164,8 +169,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                     const int i = warp * TPW + u, ch_rt = (int)blockIdx.y * 8 + (i & 7), ff_rt = p.ff / TILE_ROWS;
                     rt = ch_rt < ff_rt ? (i < 8 ? ch_rt : ff_rt + ch_rt) : p.nrt;  // past the last channel: zero weights
                 }
-                dst[u] = (rt < p.nrt && kt < p.nkt)
-                             ? ld_stream_v4(p.tiles + ((size_t)rt * p.nkt + kt) * 32 + lane)
+                dst[u] = (rt < p.nrt && kt < nk)
+                             ? ld_stream_v4(p.tiles + ((size_t)rt * p.nkt + ktb + kt) * 32 + lane)
                              : make_uint4(0x55555555u, 0x55555555u, 0x55555555u, 0x55555555u);
             }
         };
@@ -176,14 +181,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
         const bool tracedd = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0;
         unsigned long long tld = gtime(), t0d = tld;
 #endif
-        for (int kt2 = 0; kt2 < p.nkt; kt2 += PF) {
+        for (int kt2 = 0; kt2 < nk; kt2 += PF) {
 #pragma unroll
           for (int par = 0; par < PF; ++par) {
             const int kt = kt2 + par;
-            if (kt >= p.nkt) break;
+            if (kt >= nk) break;
             const int s = kt % T5_STAGES;
             if (!t5_wait(smem_u32(&s_empty[s]), ((kt / T5_STAGES) & 1) ^ 1, abort_flag, p.status, 0x7c000001u)) {
-                kt2 = p.nkt;  // leave both loops
+                kt2 = nk;  // leave both loops
                 break;
             }
 #ifdef RB_TRACE
@@ -298,7 +303,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                     const int rbase = row0 + ch * 32;
                     if (token < p.ncols && rbase < p.out) {
                         int32_t* dst = p.acc + (size_t)token * p.out + rbase;
-                        if (rbase + 32 <= p.out && (p.out & 3) == 0) {
+                        if (p.kt_per_split) {  // one of several partial sums: exact, in any order
+#pragma unroll
+                            for (int q = 0; q < 32; ++q)
+                                if (rbase + q < p.out) atomicAdd(dst + q, (int32_t)v[q]);
+                        } else if (rbase + 32 <= p.out && (p.out & 3) == 0) {
 #pragma unroll
                             for (int q = 0; q < 8; ++q)
                                 *reinterpret_cast<uint4*>(dst + 4 * q) =
@@ -315,7 +324,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     } else if (warp == NDW) {
         // ---------------- token operand by TMA
         if (lane == 0) {
-            for (int kt = 0; kt < p.nkt; ++kt) {
+            for (int kt = 0; kt < nk; ++kt) {
                 const int s = kt % T5_STAGES;
                 if (!t5_wait(smem_u32(&s_empty[s]), ((kt / T5_STAGES) & 1) ^ 1, abort_flag, p.status, 0x7c000003u)) break;
                 const uint32_t bar = smem_u32(&s_full[s]);
@@ -327,7 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
                         "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                        "l"(&tmap), "r"(kt * TILE_K), "r"(tok0 + half * 128), "r"(bar)
+                        "l"(&tmap), "r"((ktb + kt) * TILE_K), "r"(tok0 + half * 128), "r"(bar)
                         : "memory");
                 }
             }
@@ -343,7 +352,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
             const bool traced = blockIdx.x == 0 && blockIdx.y == 0;
             unsigned long long tl = gtime(), t0m = tl;
 #endif
-            for (int kt = 0; kt < p.nkt && ok; ++kt) {
+            for (int kt = 0; kt < nk && ok; ++kt) {
                 const int s = kt % T5_STAGES;
                 ok = t5_wait(smem_u32(&s_full[s]), (kt / T5_STAGES) & 1, abort_flag, p.status, 0x7c000004u);
                 if (!ok) break;
@@ -464,7 +473,19 @@ int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* 
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, current_device()) != cudaSuccess || sms <= 0)
             sms = 148;
     }
-    if (tok_tiles * ((rows + 255) / 256) < sms) {  // 256-row tiles would leave SMs idle
+    const int tiles256 = tok_tiles * ((rows + 255) / 256);
+    // fewer 256-row tiles than SMs: split the K range so that the grid covers the GPU (a K step of a
+    // 256-row tile costs a decoder less per weight than four steps of 64-row tiles); at least four K
+    // steps per CTA, partial sums added into the zeroed accumulators
+    int splits = tiles256 < sms ? sms / tiles256 : 1;
+    if (splits > p.nkt / 4) splits = p.nkt / 4;
+    if (splits >= 2) {
+        p.kt_per_split = (p.nkt + splits - 1) / splits;
+        splits = (p.nkt + p.kt_per_split - 1) / p.kt_per_split;
+        RB_CUDA(cudaMemsetAsync(acc, 0, (size_t)ncols * out * sizeof(int32_t), st));
+        dim3 grid(tok_tiles, (rows + 255) / 256, splits);
+        gemm_tcgen05_kernel<256><<<grid, T5Cfg<256>::THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);
+    } else if (tiles256 < sms) {  // 256-row tiles would leave SMs idle
         dim3 grid(tok_tiles, (rows + 63) / 64);
         gemm_tcgen05_kernel<64><<<grid, T5Cfg<64>::THREADS, T5Cfg<64>::SMEM, st>>>(tmap, p);
     } else {

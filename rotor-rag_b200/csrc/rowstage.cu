@@ -19,6 +19,9 @@ namespace rb {
 constexpr int RS_THREADS = 128;
 constexpr int RS_MIN_ROWS = 64;
 constexpr int RS_WIDE_THREADS = 512;
+// With fewer rows than SMs every CTA runs its code once, from a cold instruction cache: the duration is
+// the length of the unrolled code, so the widest rows take 1024 threads with half the groups each.
+constexpr int RS_FEW_ROWS = 296;
 
 __device__ __forceinline__ float4 rs_deq(const VecStageParams& p, size_t col0, int off, int g, const float (&sxv)[3],
                                          float wscale) {
@@ -290,20 +293,30 @@ template <bool RESID>
 static int launch_row_stage_v(const VecStageParams& p, int rows, int v, cudaStream_t st) {
     if (v <= 5) return launch_one<5, RESID, RS_THREADS>(p, rows, st);
     if (v <= 8) return launch_one<8, RESID, RS_THREADS>(p, rows, st);
-    if (v <= 14) return launch_one<14, RESID, RS_THREADS>(p, rows, st);
-    return launch_one<16, RESID, RS_THREADS>(p, rows, st);
+    if constexpr (!RESID) {
+        if (v <= 14) return launch_one<14, RESID, RS_THREADS>(p, rows, st);
+        return launch_one<16, RESID, RS_THREADS>(p, rows, st);
+    }
+    return ROTOR_B200_ERR_SHAPE;  // wider rows with a residual take the 512-thread kernel (launch_row_stage)
 }
 
 int launch_row_stage(const VecStageParams& p, int rows, cudaStream_t st) {
     const int width = p.xq && p.kpad > p.n ? p.kpad : p.n;   // the quantiser also writes the zero padding
-    if (width > 4 * 16 * RS_THREADS)  // wide rows without a residual: 512 threads, up to 14 groups each
+    if (width > 4 * 16 * RS_THREADS) {  // wide rows without a residual: 512 threads, up to 14 groups each
+        if (rows <= RS_FEW_ROWS) return launch_one<7, false, 1024>(p, rows, st);  // see RS_FEW_ROWS
         return launch_one<14, false, RS_WIDE_THREADS>(p, rows, st);
+    }
     const int v = (width / 4 + RS_THREADS - 1) / RS_THREADS;
     if (v > 8 && p.mode != VS_OPROJ && p.mode != VS_DOWN)
         // 4097..8192 elements without a residual (the 2B FFN row): four groups per thread at 512 threads
         // keep more warps per SM busy than fourteen groups at 128
         return launch_one<4, false, RS_WIDE_THREADS>(p, rows, st);
-    if (p.mode == VS_OPROJ || p.mode == VS_DOWN) return launch_row_stage_v<true>(p, rows, v, st);
+    if (p.mode == VS_OPROJ || p.mode == VS_DOWN) {
+        // 4097..8192 elements with a residual row: sixteen groups per thread do not fit the registers of a
+        // 128-thread CTA, four groups at 512 threads do
+        if (v > 8) return launch_one<4, true, RS_WIDE_THREADS>(p, rows, st);
+        return launch_row_stage_v<true>(p, rows, v, st);
+    }
     return launch_row_stage_v<false>(p, rows, v, st);
 }
 
