@@ -431,55 +431,100 @@ __device__ __forceinline__ void attn_warp_chunk(const float4 (&q4)[D / 32], cons
 // alternating sets.
 constexpr int AC_PAD = 4;
 
-template <int D>
+// H query heads of the group per warp (H = 1 or 2): a K or V piece is read from shared memory once and
+// multiplied for every head of the warp, which halves the shared-memory traffic that bounds this kernel.
+// qs: H rows of D floats, ps: H rows of 32.
+template <int D, int H>
 __device__ __forceinline__ void attn_warp_chunk_rows(const float* qs, const float* Kc, const float* Vc, float* ps, int nk,
-                                                     int lane, float& m_run, float& l_run, float4& o) {
+                                                     int lane, float (&m_run)[H], float (&l_run)[H], float4 (&o)[H]) {
     constexpr int KS = D + AC_PAD, OPL = D / 32, C4 = D / 4;
-    float my_s = -INFINITY;
+    float my_s[H];
+#pragma unroll
+    for (int h = 0; h < H; ++h) my_s[h] = -INFINITY;
     if (lane < nk) {
         const float4* kr = reinterpret_cast<const float4*>(Kc + (size_t)lane * KS);
         const float4* qr = reinterpret_cast<const float4*>(qs);
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc[H][2];
+#pragma unroll
+        for (int h = 0; h < H; ++h) acc[h][0] = acc[h][1] = 0.f;
 #pragma unroll
         for (int c = 0; c < C4; ++c) {
-            const float4 k4 = kr[c], q4 = qr[c];
-            acc[c & 3] += q4.x * k4.x + q4.y * k4.y + q4.z * k4.z + q4.w * k4.w;
+            const float4 k4 = kr[c];
+#pragma unroll
+            for (int h = 0; h < H; ++h) {
+                const float4 q4 = qr[h * C4 + c];
+                acc[h][c & 1] += q4.x * k4.x + q4.y * k4.y + q4.z * k4.z + q4.w * k4.w;
+            }
         }
-        my_s = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+        for (int h = 0; h < H; ++h) my_s[h] = acc[h][0] + acc[h][1];
     }
-    const float m_new = fmaxf(m_run, warp_max(my_s));
-    const float keep = m_run == -INFINITY ? 0.f : __expf(m_run - m_new);
-    const float pr = lane < nk ? __expf(my_s - m_new) : 0.f;
-    l_run = l_run * keep + warp_sum(pr);
+    float keep[H];
     __syncwarp();  // the previous chunk's readers of ps are done
-    ps[lane] = pr;
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+        const float m_new = fmaxf(m_run[h], warp_max(my_s[h]));
+        keep[h] = m_run[h] == -INFINITY ? 0.f : __expf(m_run[h] - m_new);
+        const float pr = lane < nk ? __expf(my_s[h] - m_new) : 0.f;
+        l_run[h] = l_run[h] * keep[h] + warp_sum(pr);
+        ps[h * 32 + lane] = pr;
+        m_run[h] = m_new;
+    }
     __syncwarp();
-    float4 oa = make_float4(o.x * keep, o.y * keep, o.z * keep, o.w * keep), ob = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 oa[H], ob[H];
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+        oa[h] = make_float4(o[h].x * keep[h], o[h].y * keep[h], o[h].z * keep[h], o[h].w * keep[h]);
+        ob[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     const float* vr = Vc + OPL * lane;
-    auto fma_row = [&](float4& acc4, float pj, int j) {
+    auto fma_row = [&](float4 (&acc4)[H], const float (&pj)[H], int j) {
         if constexpr (OPL == 4) {
             const float4 v4 = *reinterpret_cast<const float4*>(vr + (size_t)j * KS);
-            acc4.x += pj * v4.x;
-            acc4.y += pj * v4.y;
-            acc4.z += pj * v4.z;
-            acc4.w += pj * v4.w;
+#pragma unroll
+            for (int h = 0; h < H; ++h) {
+                acc4[h].x += pj[h] * v4.x;
+                acc4[h].y += pj[h] * v4.y;
+                acc4[h].z += pj[h] * v4.z;
+                acc4[h].w += pj[h] * v4.w;
+            }
         } else {
             const float2 v2 = *reinterpret_cast<const float2*>(vr + (size_t)j * KS);
-            acc4.x += pj * v2.x;
-            acc4.y += pj * v2.y;
+#pragma unroll
+            for (int h = 0; h < H; ++h) {
+                acc4[h].x += pj[h] * v2.x;
+                acc4[h].y += pj[h] * v2.y;
+            }
         }
     };
     int j = 0;
     for (; j + 4 <= nk; j += 4) {  // rows at and beyond nk are never read: they may hold anything
-        const float4 p4 = *reinterpret_cast<const float4*>(ps + j);
-        fma_row(oa, p4.x, j);
-        fma_row(ob, p4.y, j + 1);
-        fma_row(oa, p4.z, j + 2);
-        fma_row(ob, p4.w, j + 3);
+        float4 p4[H];
+#pragma unroll
+        for (int h = 0; h < H; ++h) p4[h] = *reinterpret_cast<const float4*>(ps + h * 32 + j);
+        float pj[H];
+#pragma unroll
+        for (int h = 0; h < H; ++h) pj[h] = p4[h].x;
+        fma_row(oa, pj, j);
+#pragma unroll
+        for (int h = 0; h < H; ++h) pj[h] = p4[h].y;
+        fma_row(ob, pj, j + 1);
+#pragma unroll
+        for (int h = 0; h < H; ++h) pj[h] = p4[h].z;
+        fma_row(oa, pj, j + 2);
+#pragma unroll
+        for (int h = 0; h < H; ++h) pj[h] = p4[h].w;
+        fma_row(ob, pj, j + 3);
     }
-    for (; j < nk; ++j) fma_row(oa, ps[j], j);
-    o = make_float4(oa.x + ob.x, oa.y + ob.y, oa.z + ob.z, oa.w + ob.w);
-    m_run = m_new;
+    for (; j < nk; ++j) {
+        float pj[H];
+#pragma unroll
+        for (int h = 0; h < H; ++h) pj[h] = ps[h * 32 + j];
+        fma_row(oa, pj, j);
+    }
+#pragma unroll
+    for (int h = 0; h < H; ++h)
+        o[h] = make_float4(oa[h].x + ob[h].x, oa[h].y + ob[h].y, oa[h].z + ob[h].z, oa[h].w + ob[h].w);
 }
 
 template <int D>
@@ -646,14 +691,14 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(
 // memory 32 keys at a time, double buffered with cp.async, and every warp runs the same
 // per-head chunk routine (attn_warp_chunk_rows); no partials, no merge: one pass over the cache
 // per group of heads, written as finished attention rows.
-constexpr int AS_KEYS = 32;
+constexpr int AS_KEYS = 24;  // two stages of 24 keys: four CTAs per SM at head_dim 128, so that 64 sequences x 8 KV heads run as one wave
 
-template <int D>
+template <int D, int H>
 __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ __align__(16) float sm[];
     constexpr int C4 = D / 4, OPL = D / 32, KS = D + AC_PAD;
     const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
-    const int G = p.n_heads / p.n_kv_heads;  // blockDim.x == 32 * G
+    const int G = p.n_heads / p.n_kv_heads;  // blockDim.x == 32 * G / H: warp w takes heads H w .. H w + H - 1 of the group
     const int hk = blockIdx.x, b = blockIdx.y;
     const int dq = p.n_heads * D;
     const int T = min(p.past_len[b] + 1, p.max_seq);
@@ -674,14 +719,22 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(c
     };
     const int nchunk = (T + AS_KEYS - 1) / AS_KEYS;
     fetch(0, 0);
-    if (lane < C4) {  // this warp's q, pre-scaled (read back by the same warp only, after the first CTA barrier)
-        const float* qh = p.q + (size_t)b * dq + (size_t)(hk * G + warp) * D;
+    {  // this warp's q rows, pre-scaled (read back by the same warp only, after the first CTA barrier)
+        const float* qh = p.q + (size_t)b * dq + (size_t)(hk * G + warp * H) * D;
         const float scale = 1.0f / sqrtf((float)D);
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(qh) + lane);
-        reinterpret_cast<float4*>(qs + warp * D)[lane] = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+        for (int i = lane; i < H * C4; i += 32) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(qh) + i);
+            reinterpret_cast<float4*>(qs + warp * H * D)[i] = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+        }
     }
-    float m_run = -INFINITY, l_run = 0.f;
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    float m_run[H], l_run[H];
+    float4 o[H];
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+        m_run[h] = -INFINITY;
+        l_run[h] = 0.f;
+        o[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     for (int c = 0; c < nchunk; ++c) {
         if (c + 1 < nchunk) {
             fetch(c + 1, (c + 1) & 1);
@@ -691,16 +744,19 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(c
         }
         __syncthreads();  // chunk c has landed for every thread
         const int st = c & 1;
-        attn_warp_chunk_rows<D>(qs + warp * D, Ks + (size_t)st * AS_KEYS * KS, Vs + (size_t)st * AS_KEYS * KS,
-                                ps + warp * 32, min(AS_KEYS, T - c * AS_KEYS), lane, m_run, l_run, o);
+        attn_warp_chunk_rows<D, H>(qs + warp * H * D, Ks + (size_t)st * AS_KEYS * KS, Vs + (size_t)st * AS_KEYS * KS,
+                                   ps + warp * H * 32, min(AS_KEYS, T - c * AS_KEYS), lane, m_run, l_run, o);
         __syncthreads();  // every warp is done with this stage before chunk c + 2 overwrites it
     }
-    const float inv = 1.0f / l_run;
-    float* dst = p.out + (size_t)b * dq + (size_t)(hk * G + warp) * D + OPL * lane;
-    if constexpr (OPL == 4) {
-        *reinterpret_cast<float4*>(dst) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
-    } else {
-        *reinterpret_cast<float2*>(dst) = make_float2(o.x * inv, o.y * inv);
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+        const float inv = 1.0f / l_run[h];
+        float* dst = p.out + (size_t)b * dq + (size_t)(hk * G + warp * H + h) * D + OPL * lane;
+        if constexpr (OPL == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(o[h].x * inv, o[h].y * inv, o[h].z * inv, o[h].w * inv);
+        } else {
+            *reinterpret_cast<float2*>(dst) = make_float2(o[h].x * inv, o[h].y * inv);
+        }
     }
 }
 
@@ -714,10 +770,18 @@ static int launch_attn_decode_stream(const AttnParams& p, int rows, cudaStream_t
     const int G = p.n_heads / p.n_kv_heads, D = p.head_dim;
     const size_t smem = ((size_t)G * D + (size_t)G * 32 + (size_t)4 * AS_KEYS * (D + AC_PAD)) * sizeof(float);
     dim3 grid(p.n_kv_heads, rows);
-    if (D == 64)
-        attn_decode_stream_kernel<64><<<grid, 32 * G, smem, st>>>(p);
-    else
-        attn_decode_stream_kernel<128><<<grid, 32 * G, smem, st>>>(p);
+    // two heads per warp when the group is even and leaves at least two warps
+    if (G % 2 == 0 && G >= 4) {
+        if (D == 64)
+            attn_decode_stream_kernel<64, 2><<<grid, 16 * G, smem, st>>>(p);
+        else
+            attn_decode_stream_kernel<128, 2><<<grid, 16 * G, smem, st>>>(p);
+    } else {
+        if (D == 64)
+            attn_decode_stream_kernel<64, 1><<<grid, 32 * G, smem, st>>>(p);
+        else
+            attn_decode_stream_kernel<128, 1><<<grid, 32 * G, smem, st>>>(p);
+    }
     return launch_status();
 }
 
@@ -824,8 +888,14 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128, 1>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128, 2>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
