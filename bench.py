@@ -605,11 +605,11 @@ def run_b200(args, rank, world):
                     "whole_call_tokens_per_s": world * (1 + W + K) / e2e_total},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "bitlinear_acc_kernel (ternary GEMV 2560->6912, batch 1)",
+            "roofline": {"bound": "hbm", "kernel": "fused_gemv_kernel as the stand-alone product (ternary GEMV 2560->6912, batch 1, tiles staged in shared memory)",
                          "achieved": alg / gsec / 1e9, "peak": peak, "unit": "GB/s", "frac": alg / gsec / 1e9 / peak,
                          "peak_kind": f"{peak_kind} HBM copy bandwidth",
                          # dram read + write per launch from the committed ncu capture (None if not recorded)
-                         "traffic": profile_figure("bitlinear_acc_kernel_2560x6912_gemv.md", "traffic_bytes_per_launch"),
+                         "traffic": profile_figure("fused_gemv_kernel_2560x6912_gemv.md", "traffic_bytes_per_launch"),
                          "bytes_per_launch": alg, "us_per_launch": gsec * 1e6,
                          "launch_floor_us": floor * 1e6,
                          "hbm_time_us": alg / (peak * 1e9) * 1e6,
