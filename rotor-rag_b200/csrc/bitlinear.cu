@@ -303,7 +303,7 @@ int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* x
     if (rc) return rc;
     if (ncols >= GEMM_MIN_COLS && variant == ROTOR_B200_VARIANT_AUTO) {
         // compute-bound regime: the tiled GEMM writes complete sums into plane 0 (callers use one plane)
-        if (gemm_tcgen05_supported(out, in, ncols, xq)) return launch_gemm_tcgen05(tiles, out, in, xq, ncols, acc, st);
+        if (gemm_tcgen05_supported(out, in, ncols, xq)) return launch_gemm_tcgen05(tiles, out, in, xq, xsum, ncols, acc, st);
         return launch_gemm_mma(tiles, out, in, xq, xsum, ncols, acc, st);
     }
     const int nkt = (int)(kpad_of(in) / TILE_K), nrt = (int)(opad_of(out) / TILE_ROWS);
@@ -348,7 +348,7 @@ int rotor_b200_bitlinear_acc(const void* tiles, size_t out, size_t in, const int
     const size_t kpad = kpad_of(in);
     if (ncols >= GEMM_MIN_COLS && variant == ROTOR_B200_VARIANT_AUTO) {
         if (gemm_tcgen05_supported(out, in, (int)ncols, xq))
-            return launch_gemm_tcgen05(tiles, out, in, xq, (int)ncols, acc, st);
+            return launch_gemm_tcgen05(tiles, out, in, xq, xsum, (int)ncols, acc, st);
         return launch_gemm_mma(tiles, out, in, xq, xsum, (int)ncols, acc, st);
     }
     // small matrices, up to eight columns: the staged kernel (every CTA's share of the tiles sits in shared

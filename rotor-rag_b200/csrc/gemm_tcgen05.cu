@@ -58,6 +58,7 @@ constexpr long long T5_SPIN_CYCLES = 400000000LL;  // about 0.2 s
 
 struct Tc5Params {
     const uint4* tiles;
+    const int32_t* xsum;  // [ncols] sum of each token's int8 activations (removes the +1 of the weight codes)
     int32_t* acc;       // [ncols][out]
     unsigned* status;
     int out, nrt, nkt, ncols;
@@ -111,8 +112,31 @@ __device__ __forceinline__ void t5_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr));
 }
 
-// codes {0,1,2} in four bytes -> signed bytes {-1,0,+1}
-__device__ __forceinline__ uint32_t t5_s8(uint32_t codes) { return (codes + 0x7f7f7f7fu) ^ 0x80808080u; }
+// Read-back store of a warp's 32 tokens x 32 values (lane = token after tcgen05.ld) as whole 128-byte
+// rows: through a per-warp shared-memory block (32 rows of 144 bytes: conflict-free both ways) so that
+// one store instruction covers four tokens' rows (four lines) instead of one 16-byte piece of 32
+// different lines.  dst0: address of token tok_base's first value; tokens at and beyond ntok are skipped.
+constexpr uint32_t T5_XPOSE_BYTES = 32 * 144;
+__device__ __forceinline__ void t5_store_rows(uint32_t stage, const uint32_t (&v)[32], void* dst0, size_t row_bytes,
+                                              int tok_base, int ntok, int lane) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + (uint32_t)lane * 144u + 16u * q),
+                     "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                     : "memory");
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int tl = 4 * i + (lane >> 3);
+        uint4 w;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                     : "r"(stage + (uint32_t)tl * 144u + 16u * (lane & 7)));
+        if (tok_base + tl < ntok)
+            *reinterpret_cast<uint4*>(static_cast<unsigned char*>(dst0) + (size_t)tl * row_bytes + 16 * (lane & 7)) = w;
+    }
+    __syncwarp();  // the block is rewritten by the warp's next item
+}
 
 template <int ROWS, int T5_TOK = 256, bool GATED = false>
 __global__ void __launch_bounds__(T5Cfg<ROWS, T5_TOK>::THREADS, 1)
@@ -121,6 +145,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     constexpr int T5_A_BYTES = Cfg::A_BYTES, A_HALF = 128 * TILE_K;
     constexpr int T5_ROWS = ROWS, T5_STAGE_BYTES = Cfg::STAGE_BYTES, TPW = Cfg::TILES_PER_WARP;
     constexpr int T5_STAGES = Cfg::STAGES, PF = Cfg::PREFETCH, NDW = Cfg::DECODERS;
+#ifdef RB_TRACE
+    const unsigned long long t_entry = gtime();
+#endif
     extern __shared__ unsigned char t5_raw[];
     __shared__ __align__(8) unsigned long long s_full[T5_STAGES], s_empty[T5_STAGES], s_accf;
     __shared__ uint32_t s_tmem;
@@ -205,10 +232,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                     const uint32_t lo = pw[rh], hi = pw[rh + 2];
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {  // 16-byte chunk 2 t + c holds bit pairs 2 c and 2 c + 1
-                        const uint32_t a0 = t5_s8((lo >> (4 * c)) & 0x03030303u);
-                        const uint32_t a1 = t5_s8((hi >> (4 * c)) & 0x03030303u);
-                        const uint32_t a2 = t5_s8((lo >> (4 * c + 2)) & 0x03030303u);
-                        const uint32_t a3 = t5_s8((hi >> (4 * c + 2)) & 0x03030303u);
+                        // the operand bytes are the codes w + 1 themselves (unsigned operand); the read-back
+                        // subtracts the token's activation sum
+                        const uint32_t a0 = (lo >> (4 * c)) & 0x03030303u;
+                        const uint32_t a1 = (hi >> (4 * c)) & 0x03030303u;
+                        const uint32_t a2 = (lo >> (4 * c + 2)) & 0x03030303u;
+                        const uint32_t a3 = (hi >> (4 * c + 2)) & 0x03030303u;
                         const uint32_t dst = row + (uint32_t)(((2 * t + c) ^ g) << 4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(a0), "r"(a1), "r"(a2),
                                      "r"(a3)
@@ -227,15 +256,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
 #ifdef RB_TRACE
         if (tracedd) {
             trd.t[2] = gtime() - t0d;
+            trd.t[3] = t0d - t_entry;  // kernel entry -> first K step
             trd.t[7] = (unsigned long long)p.nkt;
-            trd.kind = 601;
-            unsigned idx_ = atomicAdd(&g_trace_n, 1u);
-            if (idx_ < 4096) g_trace[idx_] = trd;
+            tld = gtime();
         }
 #endif
         // ---------------- epilogue: lane = token, 32 columns (weight rows) per load
         // (warp-uniform decision: the tensor-memory loads below are warp-wide instructions)
         const bool acc_ok = !*abort_flag && t5_wait(smem_u32(&s_accf), 0, abort_flag, p.status, 0x7c000002u);
+#ifdef RB_TRACE
+        if (tracedd) { const unsigned long long n_ = gtime(); trd.t[4] = n_ - tld; tld = n_; }
+#endif
         if (__all_sync(0xffffffffu, acc_ok)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row0 = rt0 * TILE_ROWS;
@@ -255,29 +286,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                     t5_ld32(taddr + 128u, uv);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     const int c0 = (int)blockIdx.y * 128 + ch * 32;
-                    if (token < p.ncols && c0 < p.ff) {
-                        const float sxv = __ldg(p.sx + token);
-                        float* dst = p.gated + (size_t)token * p.ff + c0;
-                        float r[32];
+                    if (c0 < p.ff) {  // warp-uniform
+                        const int tok_base = tok0 + half * 128 + wq * 32;
+                        const bool live = token < p.ncols;
+                        const float sxv = live ? __ldg(p.sx + token) : 0.f;
+                        const int32_t xs = live ? __ldg(p.xsum + token) : 0;
+                        // the gated values replace the gate accumulators in place (bit patterns of float32)
 #pragma unroll
                         for (int q = 0; q < 32; ++q) {
-                            const float g = ((float)(int32_t)gv[q] * sxv) * p.sg, u = ((float)(int32_t)uv[q] * sxv) * p.su;
+                            const float g = ((float)((int32_t)gv[q] - xs) * sxv) * p.sg, u = ((float)((int32_t)uv[q] - xs) * sxv) * p.su;
+                            float r;
                             if (p.ffn_act == ROTOR_B200_FFN_RELU2) {
                                 const float a = fmaxf(g, 0.f);
-                                r[q] = a * a * u;
+                                r = a * a * u;
                             } else {
                                 const float c = fminf(fmaxf(u, -20.f), 20.f);
-                                r[q] = g * (c / (1.f + expf(-c)));
+                                r = g * (c / (1.f + expf(-c)));
                             }
+                            gv[q] = __float_as_uint(r);
                         }
                         if (c0 + 32 <= p.ff && (p.ff & 3) == 0) {
-#pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                *reinterpret_cast<float4*>(dst + 4 * q) = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
-                        } else {
+                            t5_store_rows(ring + (uint32_t)warp * T5_XPOSE_BYTES, gv, p.gated + (size_t)tok_base * p.ff + c0,
+                                          (size_t)p.ff * sizeof(float), tok_base, p.ncols, lane);
+                        } else if (live) {
+                            float* dst = p.gated + (size_t)token * p.ff + c0;
 #pragma unroll
                             for (int q = 0; q < 32; ++q)
-                                if (c0 + q < p.ff) dst[q] = r[q];
+                                if (c0 + q < p.ff) dst[q] = __uint_as_float(gv[q]);
                         }
                     }
                 }
@@ -301,18 +336,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                         : "r"(taddr));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     const int rbase = row0 + ch * 32;
-                    if (token < p.ncols && rbase < p.out) {
-                        int32_t* dst = p.acc + (size_t)token * p.out + rbase;
+                    if (rbase < p.out) {  // warp-uniform
+                        const int tok_base = tok0 + half * 128 + wq * 32;
+                        // remove the +1 of the codes: once per output, i.e. in the first K split only
+                        const uint32_t xs =
+                            ((p.kt_per_split && blockIdx.z) || token >= p.ncols) ? 0u : (uint32_t)__ldg(p.xsum + token);
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) v[q] -= xs;
                         if (p.kt_per_split) {  // one of several partial sums: exact, in any order
+                            if (token < p.ncols) {
+                                int32_t* dst = p.acc + (size_t)token * p.out + rbase;
 #pragma unroll
-                            for (int q = 0; q < 32; ++q)
-                                if (rbase + q < p.out) atomicAdd(dst + q, (int32_t)v[q]);
+                                for (int q = 0; q < 32; ++q)
+                                    if (rbase + q < p.out) atomicAdd(dst + q, (int32_t)v[q]);
+                            }
                         } else if (rbase + 32 <= p.out && (p.out & 3) == 0) {
-#pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                *reinterpret_cast<uint4*>(dst + 4 * q) =
-                                    make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                        } else {
+                            t5_store_rows(ring + (uint32_t)warp * T5_XPOSE_BYTES, v, p.acc + (size_t)tok_base * p.out + rbase,
+                                          (size_t)p.out * sizeof(int32_t), tok_base, p.ncols, lane);
+                        } else if (token < p.ncols) {
+                            int32_t* dst = p.acc + (size_t)token * p.out + rbase;
 #pragma unroll
                             for (int q = 0; q < 32; ++q)
                                 if (rbase + q < p.out) dst[q] = (int32_t)v[q];
@@ -321,6 +363,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
                 }
             }
         }
+#ifdef RB_TRACE
+        if (tracedd) {
+            trd.t[5] = gtime() - tld;  // read-back and stores
+            trd.kind = 601;
+            unsigned idx_ = atomicAdd(&g_trace_n, 1u);
+            if (idx_ < 4096) g_trace[idx_] = trd;
+        }
+#endif
     } else if (warp == NDW) {
         // ---------------- token operand by TMA
         if (lane == 0) {
@@ -344,8 +394,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     } else {
         // ---------------- MMA issue
         if (lane == 0) {
-            // kind::i8, S32 accumulate, signed x signed, both operands K-major, N = 256, M = 128
-            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(T5_ROWS >> 3) << 17) | ((128u >> 4) << 24);
+            // kind::i8, S32 accumulate, signed tokens (A) x unsigned weight codes (B), both K-major, N = ROWS, M = 128
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (0u << 10) | ((uint32_t)(T5_ROWS >> 3) << 17) | ((128u >> 4) << 24);
             bool ok = true;
 #ifdef RB_TRACE
             TraceRec trm = {};
@@ -443,12 +493,13 @@ int configure_gemm_tcgen05() {
     return ROTOR_B200_OK;
 }
 
-int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* xq, int ncols, int32_t* acc,
-                        cudaStream_t st) {
+int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
+                        int32_t* acc, cudaStream_t st) {
     int rc = configure_gemm_tcgen05();
     if (rc) return rc;
     Tc5Params p = {};
     p.tiles = (const uint4*)tiles;
+    p.xsum = xsum;
     p.acc = acc;
     p.status = library_status_word();
     p.out = (int)out;
@@ -502,8 +553,9 @@ bool gemm_tcgen05_gated_supported(size_t ff, size_t in, int ncols, const void* x
     return ff % TILE_ROWS == 0 && ncols >= 256 && gemm_tcgen05_supported(2 * ff, in, ncols, xq);
 }
 
-int launch_gemm_tcgen05_gated(const void* tiles, size_t ff, size_t in, const int8_t* xq, const float* sx, int ncols,
-                              float sg, float su, int ffn_act, float* gated, cudaStream_t st) {
+int launch_gemm_tcgen05_gated(const void* tiles, size_t ff, size_t in, const int8_t* xq, const float* sx,
+                              const int32_t* xsum, int ncols, float sg, float su, int ffn_act, float* gated,
+                              cudaStream_t st) {
     int rc = configure_gemm_tcgen05();
     if (rc) return rc;
     if (!gemm_tcgen05_gated_supported(ff, in, ncols, xq)) return ROTOR_B200_ERR_SHAPE;
@@ -516,6 +568,7 @@ int launch_gemm_tcgen05_gated(const void* tiles, size_t ff, size_t in, const int
     p.ncols = ncols;
     p.gated = gated;
     p.sx = sx;
+    p.xsum = xsum;
     p.sg = sg;
     p.su = su;
     p.ff = (int)ff;

@@ -369,7 +369,7 @@ static int ffn_part(Ctx& c, const rotor_b200_layer_weights& L, int rows, AccView
         // writes float32 gated rows (into the accumulator area: a quarter of the bytes of the two int32 halves);
         // the stage that follows only has to sub-norm and quantise them
         float* gated = reinterpret_cast<float*>(c.accA);
-        RB_TRY(launch_gemm_tcgen05_gated(L.gate_up_tiles, (size_t)c.ff, c.d, c.xq, c.sx[0], cols, L.gate_scale, L.up_scale,
+        RB_TRY(launch_gemm_tcgen05_gated(L.gate_up_tiles, (size_t)c.ff, c.d, c.xq, c.sx[0], c.xsum[0], cols, L.gate_scale, L.up_scale,
                                          c.ffn_act, gated, st));
         VecStageParams gp = {};
         gp.mode = VS_PLAIN;

@@ -75,13 +75,14 @@ int gemv_cols_per_launch(int variant, int ncols);
 // Many-column product (gemm_mma.cu): complete int32 sums into acc[ncols][out].
 constexpr int GEMM_MIN_COLS = 32;
 bool gemm_tcgen05_supported(size_t out, size_t in, int ncols, const void* xq);
-int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* xq, int ncols, int32_t* acc,
-                        cudaStream_t st);
+int launch_gemm_tcgen05(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
+                        int32_t* acc, cudaStream_t st);
 int configure_gemm_tcgen05();
 // gate/up product with the gating in its epilogue (float32 gated rows out, one activation term per token)
 bool gemm_tcgen05_gated_supported(size_t ff, size_t in, int ncols, const void* xq);
-int launch_gemm_tcgen05_gated(const void* tiles, size_t ff, size_t in, const int8_t* xq, const float* sx, int ncols,
-                              float sg, float su, int ffn_act, float* gated, cudaStream_t st);
+int launch_gemm_tcgen05_gated(const void* tiles, size_t ff, size_t in, const int8_t* xq, const float* sx,
+                              const int32_t* xsum, int ncols, float sg, float su, int ffn_act, float* gated,
+                              cudaStream_t st);
 int launch_gemm_mma(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
                     int32_t* acc, cudaStream_t st);
 
