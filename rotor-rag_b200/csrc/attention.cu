@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(256) qkv_finish_vec_kernel(const __grid_consta
 }
 
 int launch_qkv_finish(const QkvFinishParams& p, int rows, cudaStream_t st) {
-    if (rows >= 64 && p.acc.planes == 1 && p.acc.out % 4 == 0 && p.head_dim % 8 == 0 && p.terms >= 1 && p.terms <= 3)
+    if (rows >= 32 && p.acc.planes == 1 && p.acc.out % 4 == 0 && p.head_dim % 8 == 0 && p.terms >= 1 && p.terms <= 3)
         qkv_finish_vec_kernel<<<rows, 256, 0, st>>>(p);
     else
         qkv_finish_kernel<<<rows, 256, 0, st>>>(p);
@@ -708,8 +708,12 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(c
     float* ps = qs + G * D;                 // [G][32]
     float* Ks = ps + G * 32;                // [2][AS_KEYS][KS]
     float* Vs = Ks + 2 * AS_KEYS * KS;      // [2][AS_KEYS][KS]
+    // this CTA's run of the sequence: all of it, or one of gridDim.z equal parts
+    const int nrun = (int)gridDim.z, run = (int)blockIdx.z;
+    const int rlen = (T + nrun - 1) / nrun, k0 = run * rlen, k1 = min(T, k0 + rlen);
+    const int nchunk = k1 > k0 ? (k1 - k0 + AS_KEYS - 1) / AS_KEYS : 0;
     auto fetch = [&](int chunk, int stage) {
-        const int t0 = chunk * AS_KEYS, n = min(AS_KEYS, T - t0);
+        const int t0 = k0 + chunk * AS_KEYS, n = min(AS_KEYS, k1 - t0);
         for (int idx = tid; idx < n * C4; idx += nthr) {
             const int r = idx / C4, c4 = idx - r * C4;
             cp_async16(Ks + ((size_t)stage * AS_KEYS + r) * KS + 4 * c4, kc + (size_t)(t0 + r) * D + 4 * c4);
@@ -717,8 +721,7 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(c
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    const int nchunk = (T + AS_KEYS - 1) / AS_KEYS;
-    fetch(0, 0);
+    if (nchunk > 0) fetch(0, 0);
     {  // this warp's q rows, pre-scaled (read back by the same warp only, after the first CTA barrier)
         const float* qh = p.q + (size_t)b * dq + (size_t)(hk * G + warp * H) * D;
         const float scale = 1.0f / sqrtf((float)D);
@@ -745,8 +748,25 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(c
         __syncthreads();  // chunk c has landed for every thread
         const int st = c & 1;
         attn_warp_chunk_rows<D, H>(qs + warp * H * D, Ks + (size_t)st * AS_KEYS * KS, Vs + (size_t)st * AS_KEYS * KS,
-                                   ps + warp * H * 32, min(AS_KEYS, T - c * AS_KEYS), lane, m_run, l_run, o);
+                                   ps + warp * H * 32, min(AS_KEYS, k1 - k0 - c * AS_KEYS), lane, m_run, l_run, o);
         __syncthreads();  // every warp is done with this stage before chunk c + 2 overwrites it
+    }
+    if (nrun > 1) {  // partial results of this run: merged by the stage that follows
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+            const size_t slot = ((size_t)b * p.n_heads + (hk * G + warp * H + h)) * nrun + run;
+            float* dst = p.part_o + slot * D + OPL * lane;
+            if constexpr (OPL == 4) {
+                *reinterpret_cast<float4*>(dst) = o[h];
+            } else {
+                *reinterpret_cast<float2*>(dst) = make_float2(o[h].x, o[h].y);
+            }
+            if (lane == 0) {
+                p.part_m[slot] = m_run[h];
+                p.part_l[slot] = l_run[h];
+            }
+        }
+        return;
     }
 #pragma unroll
     for (int h = 0; h < H; ++h) {
@@ -761,15 +781,27 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_stream_kernel(c
 }
 
 static bool attn_decode_stream_ok(const AttnParams& p, int rows) {
-    if (p.seq != 1 || rows < 16 || (p.head_dim != 64 && p.head_dim != 128)) return false;
+    if (p.seq != 1 || (p.head_dim != 64 && p.head_dim != 128)) return false;
+    if (rows < 16 && !(p.nsplit > 1 && p.part_o && p.part_m && p.part_l)) return false;
     const int G = p.n_heads / p.n_kv_heads;
     return G >= 1 && G <= AC_MAX_GROUP;
+}
+
+// Fewer sequences than fill the GPU: cut each into runs so that about 512 CTAs exist (a power of two,
+// at most max_nsplit).
+int attn_stream_splits(int rows, int n_heads, int n_kv_heads, int head_dim, int max_nsplit) {
+    if (n_kv_heads < 1 || n_heads % n_kv_heads || (head_dim != 64 && head_dim != 128)) return 0;
+    const int G = n_heads / n_kv_heads;
+    if (G < 1 || G > AC_MAX_GROUP) return 0;
+    int s = 1;
+    while (2 * s <= max_nsplit && (long)rows * n_kv_heads * 2 * s <= 512) s *= 2;
+    return s;
 }
 
 static int launch_attn_decode_stream(const AttnParams& p, int rows, cudaStream_t st) {
     const int G = p.n_heads / p.n_kv_heads, D = p.head_dim;
     const size_t smem = ((size_t)G * D + (size_t)G * 32 + (size_t)4 * AS_KEYS * (D + AC_PAD)) * sizeof(float);
-    dim3 grid(p.n_kv_heads, rows);
+    dim3 grid(p.n_kv_heads, rows, p.nsplit > 1 ? p.nsplit : 1);
     // two heads per warp when the group is even and leaves at least two warps
     if (G % 2 == 0 && G >= 4) {
         if (D == 64)

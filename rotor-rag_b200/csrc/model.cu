@@ -286,7 +286,11 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     RB_TRY(gemv(c, L.qkv_tiles, qkv_out, c.d, cols, 0, c.accA, &va, st));
     // (sixteen and more sequences: the tiled attention kernel streams each sequence's cache once per
     // group of heads, which beats thousands of small split CTAs; measured on the XL shape, batch 64)
-    if (seq == 1 && batch <= c.max_batch && batch < 16) {
+    // 5 to 63 sequences: the streaming kernel over runs of every sequence (about 512 CTAs), partial results
+    // merged by the stage that quantises the attention rows
+    const int runs = (seq == 1 && batch >= 5 && batch <= c.max_batch)
+                         ? attn_stream_splits(batch, c.n_heads, c.n_kv_heads, c.head_dim, c.nsplit) : 0;
+    if (seq == 1 && batch <= c.max_batch && batch < 16 && runs <= 1) {
         // generation step: dequantise, rotate, append to the cache, attend, merge and quantise in one launch
         AttnDecodeParams dp = {};
         dp.acc = va;
@@ -348,11 +352,23 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     ap.causal = c.causal;
     ap.kv_split = seq >= 16 ? c.kvsplit : nullptr;  // a key tile shared by several query tiles is split once
     ap.split_plane = c.kvsplit_plane;
+    if (runs > 1) {
+        ap.nsplit = runs;
+        ap.part_o = c.part_o;
+        ap.part_m = c.part_m;
+        ap.part_l = c.part_l;
+    }
     RB_TRY(launch_attention(ap, rows, st));
     VecStageParams qa = {};
-    qa.mode = VS_PLAIN;
+    qa.mode = runs > 1 ? VS_ATTN : VS_PLAIN;
     qa.n = c.dq;
     qa.src = c.attn;
+    qa.part_o = c.part_o;
+    qa.part_m = c.part_m;
+    qa.part_l = c.part_l;
+    qa.nsplit = runs;
+    qa.n_heads = c.n_heads;
+    qa.head_dim = c.head_dim;
     qa.eps = c.eps;
     quant_sink(c, qa, 1, c.dq);
     RB_TRY(launch_vec_stage(qa, rows, st));

@@ -167,8 +167,17 @@ struct AttnParams {
     int causal;
     __nv_bfloat16* kv_split;  // optional scratch: K hi, K lo, V hi, V lo planes of the cache rows in use
     size_t split_plane;       // elements per plane (batch capacity * n_kv_heads * max_seq * head_dim)
+    // one-token steps of a few sequences: nsplit > 1 cuts every sequence's cache into nsplit runs, one CTA
+    // each, which write un-normalised partial outputs with their (max, sum) instead of `out`
+    int nsplit;
+    float* part_o;        // [rows][n_heads][nsplit][head_dim]
+    float* part_m;        // [rows][n_heads][nsplit]
+    float* part_l;
 };
 int launch_attention(const AttnParams& p, int rows, cudaStream_t st);
+// Runs for a one-token step of `rows` sequences handled by the streaming kernel (1 = whole sequences,
+// finished rows in `out`); 0 if that kernel does not take the shape.
+int attn_stream_splits(int rows, int n_heads, int n_kv_heads, int head_dim, int max_nsplit);
 bool attn_prefill_supported(const AttnParams& p, int rows);
 int launch_attn_prefill_tc(const AttnParams& p, int rows, cudaStream_t st);
 // head_dim 128 on tcgen05 / tensor memory (attn_prefill_t5.cu); needs the split planes sized for

@@ -17,7 +17,7 @@
 namespace rb {
 
 constexpr int RS_THREADS = 128;
-constexpr int RS_MIN_ROWS = 64;
+constexpr int RS_MIN_ROWS = 32;
 constexpr int RS_WIDE_THREADS = 512;
 // With fewer rows than SMs every CTA runs its code once, from a cold instruction cache: the duration is
 // the length of the unrolled code, so the widest rows take 1024 threads with half the groups each.
