@@ -97,6 +97,15 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
     // PF: start the fetch of `row` (pieces into the staging area, scales into registers)
     auto fetch = [&](int row) {
         const size_t c0 = (size_t)row * p.terms;
+        if (p.mode == VS_PLAIN) {  // one piece: the float row itself
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                const int g = tid + j * TH;
+                if (g < n4) rs_cp16(rs_stage + g, reinterpret_cast<const int4*>(p.src + (size_t)row * n) + g);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            return;
+        }
 #pragma unroll
         for (int j = 0; j < V; ++j) {
             const int g = tid + j * TH;
@@ -137,7 +146,10 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (RESID) aux[RESID ? j : 0] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (g >= n4) continue;
-        if (PF) {
+        if (PF && p.mode == VS_PLAIN) {
+            const int4 r = rs_stage[g];
+            v[j] = make_float4(__int_as_float(r.x), __int_as_float(r.y), __int_as_float(r.z), __int_as_float(r.w));
+        } else if (PF) {
             float4 a = rs_deq_staged(rs_stage, n4, halves, 0, p.terms, g, sxv, p.wscale0);
             if (p.mode == VS_FFN) {
                 const float4 b = rs_deq_staged(rs_stage, n4, halves, 1, p.terms, g, sxv, p.wscale1);
@@ -260,9 +272,10 @@ bool row_stage_supported(const VecStageParams& p, int rows) {
 template <int V, bool RESID, int TH>
 static int launch_one(const VecStageParams& p, int rows, cudaStream_t st) {
     const bool from_acc = p.mode == VS_OPROJ || p.mode == VS_FFN || p.mode == VS_DOWN || p.mode == VS_DEQ;
-    const size_t pieces = (size_t)p.terms * (p.mode == VS_FFN ? 2 : 1) + (RESID ? 1 : 0);
+    const bool plain = p.mode == VS_PLAIN && !RESID;  // float rows in: one staged piece
+    const size_t pieces = plain ? 1 : (size_t)p.terms * (p.mode == VS_FFN ? 2 : 1) + (RESID ? 1 : 0);
     const size_t smem = pieces * (size_t)p.n * sizeof(int);
-    if (from_acc && smem <= 200 * 1024) {
+    if ((from_acc || plain) && smem <= 200 * 1024) {
         auto* k = row_stage_kernel<V, RESID, TH, true>;
         static PerDevice<size_t> once;  // per instantiation and device
         static PerDevice<int> sm_counts;
