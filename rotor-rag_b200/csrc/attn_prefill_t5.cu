@@ -437,7 +437,31 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap tm_kh, const __grid_c
         s_xch[half][r] = l_run;
         asm volatile("bar.sync 1, %0;" ::"n"(A5_SOFT) : "memory");
         l_run += s_xch[half ^ 1][r];
-        if (ok && srow < p.seq) {
+        if (__all_sync(0xffffffffu, ok)) {
+            // A lane holds 64 consecutive outputs of ONE row, so a 16-byte store instruction of the warp would
+            // touch 32 different lines.  The rows cross a per-warp block of the K ring (idle: every MMA has
+            // completed) and leave as 256-byte pieces, two rows per instruction.
+            const float inv = 1.0f / l_run;
+            const uint32_t blk = kring + (uint32_t)warp * (32u * 272u);
+#pragma unroll
+            for (int i = 0; i < A5_D / 2; i += 4)
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(blk + (uint32_t)lane * 272u + 4u * i),
+                             "f"(o[i] * inv), "f"(o[i + 1] * inv), "f"(o[i + 2] * inv), "f"(o[i + 3] * inv)
+                             : "memory");
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const int rr = 2 * k + (lane >> 4), chunk = lane & 15;
+                float4 w;
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(w.x), "=f"(w.y), "=f"(w.z), "=f"(w.w)
+                             : "r"(blk + (uint32_t)rr * 272u + 16u * chunk));
+                const int r2 = wq * 32 + rr, srow2 = s0 + r2 / G, gi2 = r2 - (r2 / G) * G;
+                if (srow2 < p.seq)
+                    *reinterpret_cast<float4*>(p.out + ((size_t)b * p.seq + srow2) * p.n_heads * A5_D +
+                                               (size_t)(hk * G + gi2) * A5_D + half * 64 + 4 * chunk) = w;
+            }
+        } else if (ok && srow < p.seq) {
             const float inv = 1.0f / l_run;
             float* op = p.out + ((size_t)b * p.seq + srow) * p.n_heads * A5_D + (size_t)(hk * G + gi) * A5_D + half * 64;
 #pragma unroll
