@@ -71,6 +71,16 @@ struct Tc5Params {
     const float* sx;    // [ncols] activation scales (one term per token)
     float sg, su;
     int ff, ffn_act;
+    // q/k/v epilogue (QKV kernel, head_dim 128): `tiles` is the stacked [q; k; v] matrix; the read-back
+    // dequantises (sx[token] * sq / sk / sv), rotates q and k (half-split pairs i, i + 64) and writes q rows
+    // and the K / V cache rows of the token's position; no int32 accumulator leaves the kernel
+    int dq, dkv, seq, max_seq;
+    const int* past_len;   // [batch] cached length per sequence
+    const float2* rope;    // [max_seq][64] (cos, sin), or null
+    float* qout;           // [ncols][dq]
+    float* k_cache;        // [batch][dkv / 128][max_seq][128]
+    float* v_cache;
+    float sq, sk, sv;
 };
 
 __device__ __forceinline__ bool t5_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned* status,
@@ -138,7 +148,30 @@ __device__ __forceinline__ void t5_store_rows(uint32_t stage, const uint32_t (&v
     __syncwarp();  // the block is rewritten by the warp's next item
 }
 
-template <int ROWS, int T5_TOK = 256, bool GATED = false>
+// The same with a destination per token: dst_of(tl) is the address of token tok_base + tl's 128 bytes
+// (null = skip).
+template <typename F>
+__device__ __forceinline__ void t5_store_rows_to(uint32_t stage, const uint32_t (&v)[32], int lane, F dst_of) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage + (uint32_t)lane * 144u + 16u * q),
+                     "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                     : "memory");
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int tl = 4 * i + (lane >> 3);
+        uint4 w;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                     : "r"(stage + (uint32_t)tl * 144u + 16u * (lane & 7)));
+        unsigned char* d = static_cast<unsigned char*>(dst_of(tl));
+        if (d) *reinterpret_cast<uint4*>(d + 16 * (lane & 7)) = w;
+    }
+    __syncwarp();
+}
+
+template <int ROWS, int T5_TOK = 256, bool GATED = false, bool QKV = false>
 __global__ void __launch_bounds__(T5Cfg<ROWS, T5_TOK>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Tc5Params p) {
     using Cfg = T5Cfg<ROWS, T5_TOK>;
@@ -274,7 +307,63 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
             // groups of four split the (token half, 32-row chunk) pairs between them
             constexpr int NCH = T5_ROWS / 32, GROUPS = NDW / 4;
             const int wq = warp & 3, grp = warp >> 2;
-            if constexpr (GATED) {
+            if constexpr (QKV) {
+                // lane = token; per item one head of the tile (0 / 1) and one pair of 32-row chunks (pp, pp + 2):
+                // rows 32 pp + [0, 32) of the head rotate with rows 64 + 32 pp + [0, 32)
+#pragma unroll 1
+                for (int item = grp; item < nhalf * 4; item += GROUPS) {
+                    const int half = item >> 2, hh = (item >> 1) & 1, pp = item & 1;
+                    const int R0 = row0 + hh * 128;  // first row of the head in the stacked matrix
+                    if (R0 >= p.out) continue;       // warp-uniform
+                    const int tok_base = tok0 + half * 128 + wq * 32;
+                    const int token = tok_base + lane;
+                    uint32_t gv[32], uv[32];
+                    const uint32_t taddr = tmem + ((uint32_t)(wq * 32) << 16) + (uint32_t)(half * ROWS + hh * 128 + pp * 32);
+                    t5_ld32(taddr, gv);
+                    t5_ld32(taddr + 64u, uv);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int kind = R0 < p.dq ? 0 : (R0 < p.dq + p.dkv ? 1 : 2);  // q, k, v
+                    const int head = (kind == 0 ? R0 : (kind == 1 ? R0 - p.dq : R0 - p.dq - p.dkv)) >> 7;
+                    const float sc = kind == 0 ? p.sq : (kind == 1 ? p.sk : p.sv);
+                    const bool live = token < p.ncols;
+                    const int bb = live ? token / p.seq : 0;
+                    const int pos = live ? __ldg(p.past_len + bb) + (token - bb * p.seq) : 0;
+                    const float sxv = live ? __ldg(p.sx + token) : 0.f;
+                    const int32_t xs = live ? __ldg(p.xsum + token) : 0;
+                    const bool rot = kind != 2 && p.rope != nullptr && live && pos < p.max_seq;
+                    const float4* cs4 = reinterpret_cast<const float4*>(p.rope + (size_t)(rot ? pos : 0) * 64 + 32 * pp);
+#pragma unroll
+                    for (int q = 0; q < 32; q += 2) {
+                        float a0 = ((float)((int32_t)gv[q] - xs) * sxv) * sc, a1 = ((float)((int32_t)gv[q + 1] - xs) * sxv) * sc;
+                        float c0 = ((float)((int32_t)uv[q] - xs) * sxv) * sc, c1 = ((float)((int32_t)uv[q + 1] - xs) * sxv) * sc;
+                        if (rot) {
+                            const float4 cs = __ldg(cs4 + (q >> 1));  // (cos, sin) of pairs q and q + 1
+                            const float r0 = a0 * cs.x - c0 * cs.y, r1 = a1 * cs.z - c1 * cs.w;
+                            c0 = c0 * cs.x + a0 * cs.y;
+                            c1 = c1 * cs.z + a1 * cs.w;
+                            a0 = r0;
+                            a1 = r1;
+                        }
+                        gv[q] = __float_as_uint(a0);
+                        gv[q + 1] = __float_as_uint(a1);
+                        uv[q] = __float_as_uint(c0);
+                        uv[q + 1] = __float_as_uint(c1);
+                    }
+                    // destination of token tok_base + tl: its q row, or its position's row of the head's cache
+                    auto dst_of = [&](int tl, int col) -> void* {
+                        const int t2 = tok_base + tl;
+                        if (t2 >= p.ncols) return nullptr;
+                        if (kind == 0) return p.qout + (size_t)t2 * p.dq + (size_t)head * 128 + col;
+                        const int b2 = t2 / p.seq, pos2 = __ldg(p.past_len + b2) + (t2 - b2 * p.seq);
+                        if (pos2 >= p.max_seq) return nullptr;
+                        float* cache = kind == 1 ? p.k_cache : p.v_cache;
+                        return cache + (((size_t)b2 * (p.dkv >> 7) + head) * p.max_seq + pos2) * 128 + col;
+                    };
+                    const uint32_t stage = ring + (uint32_t)warp * T5_XPOSE_BYTES;
+                    t5_store_rows_to(stage, gv, lane, [&](int tl) { return dst_of(tl, 32 * pp); });
+                    t5_store_rows_to(stage, uv, lane, [&](int tl) { return dst_of(tl, 64 + 32 * pp); });
+                }
+            } else if constexpr (GATED) {
                 // lane = token; per item 32 channels: gate accumulators in columns [32 ch, +32), up in [128 + 32 ch, +32)
 #pragma unroll 1
                 for (int item = grp; item < nhalf * (NCH / 2); item += GROUPS) {
@@ -489,6 +578,8 @@ int configure_gemm_tcgen05() {
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, T5Cfg<64>::SMEM));
     RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256, 256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  T5Cfg<256>::SMEM));
+    RB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<256, 256, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 T5Cfg<256>::SMEM));
     g_tc5_ready.here() = true;
     return ROTOR_B200_OK;
 }
@@ -586,6 +677,56 @@ int launch_gemm_tcgen05_gated(const void* tiles, size_t ff, size_t in, const int
         return ROTOR_B200_ERR_CUDA;
     dim3 grid((ncols + 255) / 256, (unsigned)((ff + 127) / 128));
     gemm_tcgen05_kernel<256, 256, true><<<grid, T5Cfg<256>::THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);
+    return launch_status();
+}
+
+// q/k/v product with dequantisation, rotary and the cache append in its read-back: head_dim 128, one
+// activation term per token, enough tokens for 256-row tiles to cover the GPU.
+bool gemm_tcgen05_qkv_supported(size_t dq, size_t dkv, size_t in, int head_dim, int ncols, const void* xq) {
+    return head_dim == 128 && dq % 128 == 0 && dkv % 128 == 0 && ncols >= 256 &&
+           gemm_tcgen05_supported(dq + 2 * dkv, in, ncols, xq);
+}
+
+int launch_gemm_tcgen05_qkv(const void* tiles, size_t in, const int8_t* xq, const float* sx, const int32_t* xsum,
+                            int ncols, const QkvFinishParams& f, cudaStream_t st) {
+    int rc = configure_gemm_tcgen05();
+    if (rc) return rc;
+    const size_t dq = (size_t)f.n_heads * f.head_dim, dkv = (size_t)f.n_kv_heads * f.head_dim;
+    if (!gemm_tcgen05_qkv_supported(dq, dkv, in, f.head_dim, ncols, xq) || f.terms != 1) return ROTOR_B200_ERR_SHAPE;
+    Tc5Params p = {};
+    p.tiles = (const uint4*)tiles;
+    p.status = library_status_word();
+    p.out = (int)(dq + 2 * dkv);
+    p.nrt = (int)(opad_of(dq + 2 * dkv) / TILE_ROWS);
+    p.nkt = (int)(kpad_of(in) / TILE_K);
+    p.ncols = ncols;
+    p.sx = sx;
+    p.xsum = xsum;
+    p.dq = (int)dq;
+    p.dkv = (int)dkv;
+    p.seq = f.seq;
+    p.max_seq = f.max_seq;
+    p.past_len = f.past_len;
+    p.rope = f.rope;
+    p.qout = f.q;
+    p.k_cache = f.k_cache;
+    p.v_cache = f.v_cache;
+    p.sq = f.sq;
+    p.sk = f.sk;
+    p.sv = f.sv;
+    if (!p.status) return ROTOR_B200_ERR_CUDA;
+    const size_t kpad = kpad_of(in);
+    CUtensorMap tmap;
+    const cuuint64_t gdim[2] = {(cuuint64_t)kpad, (cuuint64_t)ncols};
+    const cuuint64_t gstride[1] = {(cuuint64_t)kpad};
+    const cuuint32_t box[2] = {(cuuint32_t)TILE_K, 128u};
+    const cuuint32_t estride[2] = {1u, 1u};
+    if (g_encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)xq, gdim, gstride, box, estride,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return ROTOR_B200_ERR_CUDA;
+    dim3 grid((ncols + 255) / 256, (unsigned)((p.nrt * TILE_ROWS + 255) / 256));
+    gemm_tcgen05_kernel<256, 256, false, true><<<grid, T5Cfg<256>::THREADS, T5Cfg<256>::SMEM, st>>>(tmap, p);
     return launch_status();
 }
 

@@ -282,8 +282,12 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
                           cudaStream_t st) {
     const int rows = batch * seq, cols = rows * c.terms;
     const size_t qkv_out = (size_t)c.dq + 2 * c.dkv;
-    AccView va;
-    RB_TRY(gemv(c, L.qkv_tiles, qkv_out, c.d, cols, 0, c.accA, &va, st));
+    // prompt-sized row counts, one activation term, head_dim 128: the q/k/v product dequantises, rotates and
+    // appends to the cache in its read-back (no int32 accumulators, no separate finish kernel)
+    const bool fuse_qkv = c.terms == 1 && c.variant == ROTOR_B200_VARIANT_AUTO && seq >= 16 &&
+                          gemm_tcgen05_qkv_supported((size_t)c.dq, (size_t)c.dkv, c.d, c.head_dim, cols, c.xq);
+    AccView va = {};
+    if (!fuse_qkv) RB_TRY(gemv(c, L.qkv_tiles, qkv_out, c.d, cols, 0, c.accA, &va, st));
     // (sixteen and more sequences: the tiled attention kernel streams each sequence's cache once per
     // group of heads, which beats thousands of small split CTAs; measured on the XL shape, batch 64)
     // 5 to 63 sequences: the streaming kernel over runs of every sequence (about 512 CTAs), partial results
@@ -337,7 +341,10 @@ static int attention_part(Ctx& c, const rotor_b200_layer_weights& L, int batch, 
     qf.q = c.qbuf;
     qf.k_cache = L.k_cache;
     qf.v_cache = L.v_cache;
-    RB_TRY(launch_qkv_finish(qf, rows, st));
+    if (fuse_qkv)
+        RB_TRY(launch_gemm_tcgen05_qkv(L.qkv_tiles, c.d, c.xq, c.sx[0], c.xsum[0], cols, qf, st));
+    else
+        RB_TRY(launch_qkv_finish(qf, rows, st));
     AttnParams ap = {};
     ap.q = c.qbuf;
     ap.k_cache = L.k_cache;

@@ -83,6 +83,11 @@ bool gemm_tcgen05_gated_supported(size_t ff, size_t in, int ncols, const void* x
 int launch_gemm_tcgen05_gated(const void* tiles, size_t ff, size_t in, const int8_t* xq, const float* sx,
                               const int32_t* xsum, int ncols, float sg, float su, int ffn_act, float* gated,
                               cudaStream_t st);
+struct QkvFinishParams;
+// q/k/v product whose read-back dequantises, rotates and appends to the cache (acc of `f` unused)
+bool gemm_tcgen05_qkv_supported(size_t dq, size_t dkv, size_t in, int head_dim, int ncols, const void* xq);
+int launch_gemm_tcgen05_qkv(const void* tiles, size_t in, const int8_t* xq, const float* sx, const int32_t* xsum,
+                            int ncols, const QkvFinishParams& f, cudaStream_t st);
 int launch_gemm_mma(const void* tiles, size_t out, size_t in, const int8_t* xq, const int32_t* xsum, int ncols,
                     int32_t* acc, cudaStream_t st);
 

@@ -356,6 +356,28 @@ def test_tiled_prefill_attention(rb, name, causal):
     assert rel_err(got2, want2) < TOL and cache2.length == 187
 
 
+def test_prefill_qkv_epilogue_cache_rows(rb):
+    """Prompt-sized calls in published semantics (one activation term, head_dim 128, 256 rows and more): the
+    q/k/v product dequantises, rotates and appends to the cache in its read-back.  The cache rows (a direct
+    function of the quantised input: rotary angles, positions, per-sequence offsets) and the attention
+    output against the oracle, for a first chunk of 2 x 150 positions and a second of 2 x 140 behind it."""
+    om, prompt, model = _tiny(rb, "hd128", rb.sem.BASELINE, max_seq=320, max_batch=2)
+    cfg, lw = om["cfg"], om["layers"][0]
+    rng = np.random.default_rng(77)
+    att = model.layers[0].attention
+    x = rng.standard_normal((2, 150, cfg["d_model"])).astype(np.float32)
+    want, wc = O.attention(x, lw, cfg, O.BASELINE, None, True)
+    got, cache = att.forward(x, mask=O.causal_mask(150, 150), use_cache=True)
+    assert rel_err(cache["k"], wc["k"]) < TOL and rel_err(cache["v"], wc["v"]) < TOL
+    assert rel_err(got, want) < 5e-3   # one-term int8 output projection: a flipped rounding tie moves a row
+    x2 = rng.standard_normal((2, 140, cfg["d_model"])).astype(np.float32)
+    want2, wc2 = O.attention(x2, lw, cfg, O.BASELINE, wc, True)
+    got2, cache2 = att.forward(x2, mask=O.causal_mask(140, 290), kv_cache=cache, use_cache=True)
+    assert cache2.length == 290
+    assert rel_err(cache2["k"], wc2["k"]) < TOL and rel_err(cache2["v"], wc2["v"]) < TOL
+    assert rel_err(got2, want2) < 5e-3
+
+
 def test_wide_ffn_generation_step(rb):
     """d_ff above 8192: the down projection's prologue stages its input row in shared memory.
     Logits within tolerance and the same 32 greedy tokens as the oracle, published semantics."""
