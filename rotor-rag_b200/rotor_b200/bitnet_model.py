@@ -236,16 +236,37 @@ class BitNetModel:
             first_host = []
         if remaining > 0:
             check(lib.rotor_b200_model_decode_begin(h.h, ptr(first), 1, n_prompt, s), "decode_begin")
-            done = 0
             step = chunk if chunk > 0 else remaining
             buf = np.empty(step, dtype=np.int64)
-            while done < remaining:
-                n = min(step, remaining - done)
-                check(lib.rotor_b200_model_decode_steps(h.h, n, int(use_graph), s), "decode_steps")
-                check(lib.rotor_b200_model_read_tokens(h.h, done, n, buf.ctypes.data, s), "read_tokens")
-                done += n
-                yield first_host + [int(t) for t in buf[:n]]
-                first_host = []
+            # The steps feed one another on the device, so the next chunk is launched BEFORE the current
+            # one's tokens are read: the read goes through a second stream that waits for the chunk's own
+            # event, and the device never idles for the host round trip.  A consumer that stops iterating
+            # (EOS) leaves at most one chunk of surplus steps, which the close below waits out.
+            copier = self._copy_stream()
+
+            def launch(first_step):
+                n = min(step, remaining - first_step)
+                with torch.cuda.stream(stream):
+                    check(lib.rotor_b200_model_decode_steps(h.h, n, int(use_graph), s), "decode_steps")
+                    done_ev = torch.cuda.Event()
+                    done_ev.record(stream)
+                return first_step, n, done_ev
+
+            try:
+                queue = [launch(0)]
+                launched = queue[0][1]
+                while queue:
+                    start, n, done_ev = queue.pop(0)
+                    if launched < remaining:
+                        queue.append(launch(launched))
+                        launched += queue[-1][1]
+                    copier.wait_event(done_ev)
+                    check(lib.rotor_b200_model_read_tokens(h.h, start, n, buf.ctypes.data, copier.cuda_stream),
+                          "read_tokens")
+                    yield first_host + [int(t) for t in buf[:n]]
+                    first_host = []
+            finally:
+                stream.synchronize()   # nothing of this generation is in flight when the handle is used again
         abi.device_status()
 
     def generate_greedy(self, prompt_ids, max_new_tokens: int, use_graph: bool = True, chunk: int = 0):
@@ -308,6 +329,12 @@ class BitNetModel:
                 out[:, 1:] = buf.T
         abi.device_status()
         return out
+
+    def _copy_stream(self):
+        torch = abi.require_cuda()
+        if getattr(self, "_copier", None) is None:
+            self._copier = torch.cuda.Stream()
+        return self._copier
 
     def _side_stream(self):
         torch = abi.require_cuda()
