@@ -364,7 +364,7 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, float4 v) {
                  : "memory");
 }
 
-constexpr int AC_MAX_SPLIT = 8;  // portable cluster size
+constexpr int AC_MAX_SPLIT = 16;  // largest cluster (above the portable 8 the device is asked first)
 constexpr int AC_MAX_GROUP = 8;  // query heads per KV head = warps per CTA
 
 __host__ __device__ inline int round4(int v) { return (v + 3) & ~3; }
@@ -527,7 +527,8 @@ __device__ __forceinline__ void attn_warp_chunk_rows(const float* qs, const floa
         o[h] = make_float4(oa[h].x + ob[h].x, oa[h].y + ob[h].y, oa[h].z + ob[h].z, oa[h].w + ob[h].w);
 }
 
-template <int D>
+// MAXS: the most slices (cluster size) this instantiation merges: 8 for portable clusters, 16 beyond.
+template <int D, int MAXS>
 __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(const __grid_constant__ AttnDecodeParams p) {
     extern __shared__ __align__(16) float sm[];
     constexpr int half = D / 2, C4 = D / 4, NCH = D / 32;  // 16-byte pieces per row; pieces per lane of a key's 8 lanes
@@ -659,16 +660,16 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(
     // ---- merge: outputs [sp * share, (sp + 1) * share) of the group, from this CTA's own shared memory
     for (int idx = tid; idx < share; idx += nthr) {
         const int oi = sp * share + idx, g = oi / D, d = oi - g * D;
-        float f[AC_MAX_SPLIT];
+        float f[MAXS];
         float M = -INFINITY;
 #pragma unroll
-        for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2) {
+        for (int s2 = 0; s2 < MAXS; ++s2) {
             f[s2] = s2 < ns ? recv_ml[s2 * 2 * G + g] : -INFINITY;
             M = fmaxf(M, f[s2]);
         }
         float L = 0.f;
 #pragma unroll
-        for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2) {
+        for (int s2 = 0; s2 < MAXS; ++s2) {
             const float e = f[s2] == -INFINITY ? 0.f : __expf(f[s2] - M);
             if (s2 < ns) L += recv_ml[s2 * 2 * G + G + g] * e;
             f[s2] = e;
@@ -676,7 +677,7 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(
         const float inv = 1.0f / L;
         float acc = 0.f;
 #pragma unroll
-        for (int s2 = 0; s2 < AC_MAX_SPLIT; ++s2)
+        for (int s2 = 0; s2 < MAXS; ++s2)
             if (s2 < ns) acc += recv_o[s2 * share + idx] * (f[s2] * inv);
         p.attn_out[(size_t)b * dq + (size_t)(hk * G + g) * D + d] = acc;
     }
@@ -849,7 +850,19 @@ static int launch_attn_decode_cluster_d(const AttnDecodeParams& p, int batch, cu
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_use_pdl ? 2 : 1;
-    if (cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel<D>, p) != cudaSuccess) {
+    cudaError_t e;
+    if (p.nsplit > 8) {  // beyond the portable cluster size: opt in once per device
+        static PerDevice<bool> once;
+        bool& allowed = once.here();
+        if (!allowed) {
+            RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<D, 16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+            allowed = true;
+        }
+        e = cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel<D, 16>, p);
+    } else {
+        e = cudaLaunchKernelEx(&cfg, attn_decode_cluster_kernel<D, 8>, p);
+    }
+    if (e != cudaSuccess) {
         ++g_launch_count;
         return ROTOR_B200_ERR_CUDA;
     }
@@ -873,6 +886,48 @@ int attn_decode_nsplit(int max_seq) {
 
 size_t attn_decode_part_floats(int batch, int n_heads, int head_dim, int max_seq) {
     return (size_t)batch * n_heads * attn_decode_nsplit(max_seq) * (head_dim + 2);
+}
+
+// Whether the current device can place one 16-CTA cluster of the cluster kernel with this much shared
+// memory per CTA (asked of the occupancy calculator; nothing is launched).
+template <int D>
+static bool cluster16_placeable(int G, size_t smem) {
+    if (cudaFuncSetAttribute(attn_decode_cluster_kernel<D, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_decode_cluster_kernel<D, 16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(16, 1);
+    cfg.blockDim = dim3(32 * G);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 16;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, attn_decode_cluster_kernel<D, 16>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return n >= 1;
+}
+
+// Slices per KV head for a model of this shape.  The cluster kernel keeps a slice of the cache in shared
+// memory, so it wants as few slices as still fit: eight (a portable cluster) while a slice of max_seq / 8
+// rows fits, sixteen (a 16-CTA cluster, when the device can place one) up to twice that; longer caches
+// take the split kernel with one slice per 128 positions.
+int attn_decode_nsplit_for(int n_heads, int n_kv_heads, int head_dim, int max_seq) {
+    if (attn_decode_cluster_ok(n_heads, n_kv_heads, head_dim, max_seq, 8)) return 8;
+    if (attn_decode_cluster_ok(n_heads, n_kv_heads, head_dim, max_seq, 16)) {
+        const int G = n_heads / n_kv_heads;
+        const size_t smem = attn_cluster_smem(G, head_dim, (max_seq + 15) / 16, 16);
+        if (head_dim == 128 ? cluster16_placeable<128>(G, smem) : cluster16_placeable<64>(G, smem)) return 16;
+    }
+    return attn_decode_nsplit(max_seq);
 }
 
 template <int D>
@@ -918,8 +973,10 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128, 1>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128, 2>, cudaFuncAttributePreferredSharedMemoryCarveout,
@@ -928,9 +985,13 @@ int configure_attention() {
     RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
     RB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64, 8>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
-    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128, 8>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<64, 16>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+    RB_CUDA(cudaFuncSetAttribute(attn_decode_cluster_kernel<128, 16>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
     if (int rc = configure_attn_prefill_t5()) return rc;
     return configure_attn_prefill_tc();

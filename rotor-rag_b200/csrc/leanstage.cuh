@@ -219,10 +219,12 @@ __device__ __forceinline__ int quant4_pack(float4& v, float s, float rs, int& ls
 // (shared memory, zero padded to kpad), its scale and sum to sx[t] / xsum[t] (shared).
 // Same results as quantize_row_from_smem.  Requires kpad <= 4 * LEAN_V * blockDim.x; sx / xsum are
 // complete after the next CTA barrier.  ONE_TERM: p.terms is 1 (the loop and the residual drop out).
+// given_absmax: optional max|row| of term 0 supplied by the caller (sharded rows).
 template <int LEAN_V, bool ONE_TERM = false>
 __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LEAN_V], float* scratch, int8_t* xq,
                                               size_t tstride, float* sx, int* xsum, int& rk, int m = 0,
-                                              bool writer = false, const XchScalarDev* x = nullptr) {
+                                              bool writer = false, const XchScalarDev* x = nullptr,
+                                              const float* given_absmax = nullptr) {
     const int n4 = p.n >> 2, k4 = p.kpad >> 2, bd = blockDim.x;
     const int terms = ONE_TERM ? 1 : p.terms;
     for (int t = 0; t < terms; ++t) {
@@ -232,6 +234,7 @@ __device__ __forceinline__ void lean_quantize(const LeanStage& p, float4 (&v)[LE
         if (threadIdx.x == 0) xsum[t] = 0;  // ordered before the atomics below by the reduction's barrier
         mx = block_max_alt(mx, scratch, rk);
         if (x && p.xi_max && t == 0) mx = xch_scalar(*x, p.xi_max - 1, m, mx, true, writer, scratch);
+        if (given_absmax && t == 0) mx = *given_absmax;  // the row is a slice: the whole row's maximum comes from outside
         const float s = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f;
         const float rs = __fdiv_rn(1.0f, s);
         int lsum = 0;

@@ -154,7 +154,7 @@ static void carve_ctx(Ctx& c, Carve& cv, size_t rows) {
     c.accB = cv.take<int32_t>(pb1 > pb2 ? pb1 : pb2);
     c.d_pos = cv.take<int>(c.max_batch > 1 ? c.max_batch : 1);  // cached length of every sequence
     c.rope_buf = cv.take<float2>((size_t)c.max_seq * (c.head_dim / 2));
-    c.nsplit = attn_decode_nsplit(c.max_seq);
+    c.nsplit = attn_decode_nsplit_for(c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq);
     const size_t heads = (size_t)c.max_batch * c.n_heads * c.nsplit;
     c.part_o = cv.take<float>(heads * c.head_dim);
     c.part_m = cv.take<float>(heads);

@@ -157,6 +157,7 @@ int launch_attn_decode(const AttnDecodeParams& p, int batch, cudaStream_t st);
 bool attn_decode_cluster_ok(int n_heads, int n_kv_heads, int head_dim, int max_seq, int nsplit);
 int launch_attn_decode_cluster(const AttnDecodeParams& p, int batch, cudaStream_t st);
 int attn_decode_nsplit(int max_seq);
+int attn_decode_nsplit_for(int n_heads, int n_kv_heads, int head_dim, int max_seq);
 size_t attn_decode_part_floats(int batch, int n_heads, int head_dim, int max_seq);
 int configure_attention();
 

@@ -17,7 +17,8 @@
 namespace rb {
 
 constexpr int RS_THREADS = 128;
-constexpr int RS_MIN_ROWS = 32;
+constexpr int RS_MIN_ROWS = 32;        // stages that read accumulators (complete sums in one plane from 32 columns on)
+constexpr int RS_MIN_ROWS_FLOAT = 5;   // stages that read float rows or the embedding table
 constexpr int RS_WIDE_THREADS = 512;
 // With fewer rows than SMs every CTA runs its code once, from a cold instruction cache: the duration is
 // the length of the unrolled code, so the widest rows take 1024 threads with half the groups each.
@@ -213,12 +214,25 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
 
     // ---- pre-norm of the consumer (its weights are fetched as they are applied: they come from L2
     // and holding them all would cost the registers that keep four rows per SM in flight)
-    if (p.norm1) {
+    // (sharded rows: out_sumsq / out_absmax hand this slice's statistics to the caller, ext_sumsq / ext_absmax
+    // bring the whole row's back; norm_n is then the whole row's width)
+    if (p.out_sumsq) {
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < V; ++j) ss += sq4(v[j]);
         ss = block_sum(ss, scratch);
-        const float inv = 1.0f / sqrtf(ss / (float)n + p.eps);
+        if (tid == 0) p.out_sumsq[m] = ss;
+    }
+    if (p.norm1) {
+        float ss = 0.f;
+        if (p.ext_sumsq) {
+            ss = __ldcg(p.ext_sumsq + m);
+        } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) ss += sq4(v[j]);
+            ss = block_sum(ss, scratch);
+        }
+        const float inv = 1.0f / sqrtf(ss / (float)(p.norm_n ? p.norm_n : n) + p.eps);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
             const int g = tid + j * TH;
@@ -228,6 +242,13 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
             v[j].z = v[j].z * inv * w.z;
             v[j].w = v[j].w * inv * w.w;
         }
+    }
+    if (p.out_absmax) {
+        float mx = 0.f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) mx = fmaxf(mx, amax4(v[j]));
+        mx = block_max(mx, scratch);
+        if (tid == 0) p.out_absmax[m] = mx;
     }
     if (p.y_out) {
 #pragma unroll
@@ -244,7 +265,8 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
         int rk = 0;
         __syncthreads();  // readers of `scratch` in the reductions above are done
         lean_quantize<V>(q, v, scratch, p.xq + (size_t)m * p.terms_out * p.kpad, (size_t)p.kpad,
-                         p.sx_out + (size_t)m * p.terms_out, p.xsum_out + (size_t)m * p.terms_out, rk);
+                         p.sx_out + (size_t)m * p.terms_out, p.xsum_out + (size_t)m * p.terms_out, rk, 0, false, nullptr,
+                         p.ext_absmax ? p.ext_absmax + m : nullptr);
     }
     }  // rows of this CTA
 }
@@ -253,7 +275,8 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
 // one plane, 16-byte aligned rows, no sharded-row statistics.
 bool row_stage_supported(const VecStageParams& p, int rows) {
     static const bool off = getenv("ROTOR_B200_NO_ROWSTAGE") != nullptr;  // comparison aid
-    if (off || rows < RS_MIN_ROWS) return false;
+    const bool from_floats = p.mode == VS_EMBED || p.mode == VS_PLAIN;
+    if (off || rows < (from_floats ? RS_MIN_ROWS_FLOAT : RS_MIN_ROWS)) return false;
     if (p.mode != VS_EMBED && p.mode != VS_PLAIN && p.mode != VS_OPROJ && p.mode != VS_FFN && p.mode != VS_DOWN &&
         p.mode != VS_DEQ)
         return false;
@@ -263,7 +286,6 @@ bool row_stage_supported(const VecStageParams& p, int rows) {
     const int widest = resid ? 4 * 16 * RS_THREADS : 4 * 14 * RS_WIDE_THREADS;  // 8192, or 28672 without a residual row
     if (p.n % 4 || p.n > widest) return false;
     if (p.xq && (p.kpad > widest || p.terms_out < 1 || p.terms_out > 4)) return false;
-    if (p.ext_sumsq || p.ext_absmax || p.out_sumsq || p.out_absmax) return false;
     return true;
 }
 

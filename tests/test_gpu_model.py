@@ -395,13 +395,15 @@ def test_wide_ffn_generation_step(rb):
 
 
 @pytest.mark.parametrize("name", list(G.TINY_MODELS))
-def test_long_cache_generation_step(rb, name):
-    """A cache of 1024 and more positions: one-token attention runs with sixteen slices per KV head
-    (a 16-CTA cluster where the device places one).  Last-position logits after a 1040-token prompt and
-    the next 8 greedy tokens against the oracle, float semantics."""
-    om, _, model = _tiny(rb, name, rb.sem.REFERENCE, max_seq=1100)
+@pytest.mark.parametrize("max_seq,n_prompt", [(1100, 1040), (2100, 2040)])
+def test_long_cache_generation_step(rb, name, max_seq, n_prompt):
+    """Caches of 1024 and of 2048 and more positions: one-token attention keeps a slice of the cache in
+    shared memory per CTA, eight slices per KV head while they fit, sixteen (a 16-CTA cluster where the
+    device places one) beyond.  Last-position logits after the prompt and the next 8 greedy tokens against
+    the oracle, float semantics."""
+    om, _, model = _tiny(rb, name, rb.sem.REFERENCE, max_seq=max_seq)
     rng = np.random.default_rng(5150)
-    prompt = rng.integers(0, om["cfg"]["vocab_size"], size=1040).astype(np.int64)
+    prompt = rng.integers(0, om["cfg"]["vocab_size"], size=n_prompt).astype(np.int64)
     ids, steps = O.generate_greedy(om, prompt, 8, O.REFERENCE, return_logits=True)
     want = ids[len(prompt):]
     logits, cache = model.forward(prompt[None, :], use_cache=True, logits_positions="last")
