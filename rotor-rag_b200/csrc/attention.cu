@@ -365,7 +365,10 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, float4 v) {
 }
 
 constexpr int AC_MAX_SPLIT = 16;  // largest cluster (above the portable 8 the device is asked first)
-constexpr int AC_MAX_GROUP = 8;  // query heads per KV head = warps per CTA
+constexpr int AC_MAX_GROUP = 8;  // query heads per KV head
+constexpr int AC_MAX_THREADS = 512;
+// Warps per query head in the cluster kernel: as many as fit 512 threads, at most four.
+__host__ __device__ inline int ac_warps_per_head(int G) { return G <= 4 ? 4 : (G <= 8 ? 2 : 1); }
 
 __host__ __device__ inline int round4(int v) { return (v + 3) & ~3; }
 
@@ -529,11 +532,13 @@ __device__ __forceinline__ void attn_warp_chunk_rows(const float* qs, const floa
 
 // MAXS: the most slices (cluster size) this instantiation merges: 8 for portable clusters, 16 beyond.
 template <int D, int MAXS>
-__global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(const __grid_constant__ AttnDecodeParams p) {
+__global__ void __launch_bounds__(AC_MAX_THREADS) attn_decode_cluster_kernel(const __grid_constant__ AttnDecodeParams p) {
     extern __shared__ __align__(16) float sm[];
     constexpr int half = D / 2, C4 = D / 4, NCH = D / 32;  // 16-byte pieces per row; pieces per lane of a key's 8 lanes
-    const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
-    const int G = p.n_heads / p.n_kv_heads, ns = p.nsplit;  // blockDim.x == 32 * G
+    const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31;
+    const int G = p.n_heads / p.n_kv_heads, ns = p.nsplit;  // blockDim.x == 32 * G * W
+    const int W = (nthr >> 5) / G;                          // warps per query head: each takes a run of the slice's keys
+    const int warp = (tid >> 5) % G, sub = (tid >> 5) / G;  // head within the group, run within the slice
     const int hk = blockIdx.x / ns, sp = blockIdx.x % ns;   // sp is also the rank inside the cluster
     const int b = blockIdx.y;
     const int dq = p.n_heads * D, dkv = p.n_kv_heads * D;
@@ -543,6 +548,7 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(
     float* recv_ml = recv_o + ns * share;     // [ns][2 G]   (max, sum) of every slice and head
     float* Ks = recv_ml + round4(ns * 2 * G); // [lcmax][D]
     float* Vs = Ks + (size_t)lcmax * D;       // [lcmax][D]
+    float* runs = Vs + (size_t)lcmax * D;     // [(W - 1) G][D + 4] results of the runs 1 .. W-1: o, then (max, sum)
     TraceRec tr;
     RB_STAMP(tr, 0);
     // every CTA of the cluster has started (its shared memory may be written) once this phase completes
@@ -628,18 +634,56 @@ __global__ void __launch_bounds__(32 * AC_MAX_GROUP) attn_decode_cluster_kernel(
     __syncthreads();  // staged rows and the new row are visible to every warp
     RB_STAMP(tr, 3);
 
-    // ---- this warp's head over the slice, 32 keys at a time
+    // ---- this warp's head over its run of the slice, 32 keys at a time
     float m_run = -INFINITY, l_run = 0.f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);  // output dimensions OPL * lane .. + OPL - 1
     constexpr int OPL = D / 32;                  // output floats per lane
-    for (int c0 = t0; c0 < t1; c0 += 32)
-        attn_warp_chunk<D>(q4, Ks + (size_t)(c0 - t0) * D, Vs + (size_t)(c0 - t0) * D, min(32, t1 - c0), lane, m_run,
-                           l_run, o);
+    {
+        const int per = ((t1 - t0 + W - 1) / W + 3) & ~3;  // whole passes of four keys
+        const int a0 = t0 + sub * per, a1 = min(t1, a0 + per);
+        for (int c0 = a0; c0 < a1; c0 += 32)
+            attn_warp_chunk<D>(q4, Ks + (size_t)(c0 - t0) * D, Vs + (size_t)(c0 - t0) * D, min(32, a1 - c0), lane, m_run,
+                               l_run, o);
+    }
+    if (W > 1) {  // fold the runs of a head into its first warp
+        if (sub > 0) {
+            float* r = runs + (size_t)((sub - 1) * G + warp) * (D + 4);
+            if constexpr (OPL == 4) {
+                *reinterpret_cast<float4*>(r + OPL * lane) = o;
+            } else {
+                r[OPL * lane] = o.x;
+                r[OPL * lane + 1] = o.y;
+            }
+            if (lane == 0) {
+                r[D] = m_run;
+                r[D + 1] = l_run;
+            }
+        }
+        __syncthreads();
+        if (sub == 0) {
+            for (int s2 = 1; s2 < W; ++s2) {
+                const float* r = runs + (size_t)((s2 - 1) * G + warp) * (D + 4);
+                const float m2 = r[D], l2 = r[D + 1];
+                const float M = fmaxf(m_run, m2);
+                const float a = m_run == -INFINITY ? 0.f : __expf(m_run - M);
+                const float b2 = m2 == -INFINITY ? 0.f : __expf(m2 - M);
+                if constexpr (OPL == 4) {
+                    const float4 o2 = *reinterpret_cast<const float4*>(r + OPL * lane);
+                    o = make_float4(o.x * a + o2.x * b2, o.y * a + o2.y * b2, o.z * a + o2.z * b2, o.w * a + o2.w * b2);
+                } else {
+                    o.x = o.x * a + r[OPL * lane] * b2;
+                    o.y = o.y * a + r[OPL * lane + 1] * b2;
+                }
+                l_run = l_run * a + l2 * b2;
+                m_run = M;
+            }
+        }
+    }
     RB_STAMP(tr, 4);
 
     // ---- push this slice's results to the CTAs that merge them
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // (phase opened at the top of the kernel)
-    {
+    if (sub == 0) {
         const int oi = warp * D + OPL * lane;      // first output of this lane within the group
         const int dst = oi / share, off = oi - dst * share;
         const uint32_t ra = cluster_addr(recv_o + sp * share + off, (unsigned)dst);
@@ -819,7 +863,8 @@ static int launch_attn_decode_stream(const AttnParams& p, int rows, cudaStream_t
 }
 
 static size_t attn_cluster_smem(int G, int D, int lcmax, int ns) {
-    return ((size_t)G * D + round4(ns * 2 * G) + 2 * (size_t)lcmax * D) * sizeof(float);
+    return ((size_t)G * D + round4(ns * 2 * G) + 2 * (size_t)lcmax * D +
+            (size_t)(ac_warps_per_head(G) - 1) * G * (D + 4)) * sizeof(float);
 }
 
 // Whether a generation step of this shape takes the cluster kernel (the slices of one KV head fit a
@@ -838,7 +883,7 @@ static int launch_attn_decode_cluster_d(const AttnDecodeParams& p, int batch, cu
     const size_t smem = attn_cluster_smem(G, D, (p.max_seq + p.nsplit - 1) / p.nsplit, p.nsplit);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.n_kv_heads * p.nsplit, batch);
-    cfg.blockDim = dim3(32 * G);
+    cfg.blockDim = dim3(32 * G * ac_warps_per_head(G));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -899,7 +944,7 @@ static bool cluster16_placeable(int G, size_t smem) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(16, 1);
-    cfg.blockDim = dim3(32 * G);
+    cfg.blockDim = dim3(32 * G * ac_warps_per_head(G));
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
