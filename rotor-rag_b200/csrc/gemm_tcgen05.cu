@@ -2,23 +2,26 @@
 // acc[c][o] = sum_k xq[c][k] * w[o][k], exact int32, for hundreds to thousands of
 // activation columns c (tokens).
 //
-// CTA tile: 256 tokens x 256 weight rows (64 weight rows when the larger tile would leave SMs
-// without work), K walked 128 at a time through a 3-stage ring of shared-memory operand tiles.
-// tcgen05.mma.kind::i8 (M = 128 tokens, N = 256 or 64 weight rows, K = 32 per instruction)
-// accumulates into tensor memory: two 128-lane int32 accumulators of N columns (with N = 256,
-// all 512 TMEM columns of the SM).  A token half without tokens is skipped.  Per stage:
+// CTA tile: 256 tokens x 256 weight rows, K walked 128 at a time through a 3-stage ring of
+// shared-memory operand tiles.  tcgen05.mma.kind::i8 (M = 128 tokens, N = 256 weight rows, K = 32 per
+// instruction) accumulates into tensor memory: two 128-lane int32 accumulators of N columns (all 512
+// TMEM columns of the SM).  A token half without tokens is skipped.  Per stage:
 //   * the token operand (2 x 128 rows of 128 int8) arrives by TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past the last token zero filled),
-//   * four decoder warps turn the stage's packed weight tiles (2 bits per weight; 16 tiles = 8 KB
-//     for N = 256) into signed int8 (32 KB) in the same swizzled K-major layout: a lane's 128-bit tile word holds, per
+//   * eight decoder warps turn the stage's packed weight tiles (2 bits per weight; 16 tiles = 8 KB)
+//     into bytes (32 KB) in the same swizzled K-major layout: a lane's 128-bit tile word holds, per
 //     row, 32 consecutive K positions, i.e. two 16-byte chunks of the operand row,
 //   * one thread issues the eight MMAs and commits them to the stage's "empty" barrier.
-// The weights are signed int8 (-1, 0, +1) in shared memory, so no code-offset correction is
-// needed.  After the last stage the decoder warps read the accumulators back
-// (tcgen05.ld 32 lanes x 32 columns) and store acc[token][row], 128 contiguous bytes per
-// thread.  Every wait is bounded by a cycle count; a wait that runs out records a code in
-// the library status word, the CTA stops issuing work, lets its copies land, frees its
-// tensor memory and returns.
+// The weight operand holds the codes w + 1 (0, 1, 2) as unsigned bytes against signed activations;
+// the read-back subtracts the token's activation sum.  After the last stage the decoder warps read
+// the accumulators back (tcgen05.ld 32 lanes x 32 columns: a lane holds 32 consecutive outputs of
+// one token) and pass them through a per-warp shared-memory block so that they leave as whole
+// 128-byte rows.  Read-back variants: plain int32 sums; GATED (gate/up product: activation and
+// product in the read-back, float32 out); QKV (dequantise, rotary, cache append).  When 256-row tiles
+// do not cover the GPU the K range is split over blockIdx.z and the partial sums are added with
+// integer atomics (64-row tiles remain for products too short to split).
+// Every wait is bounded by a cycle count; a wait that runs out records a code in the library status
+// word, the CTA stops issuing work, lets its copies land, frees its tensor memory and returns.
 #include <cuda.h>
 
 #include <cstdlib>
