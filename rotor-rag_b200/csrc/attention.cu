@@ -731,11 +731,13 @@ __global__ void __launch_bounds__(AC_MAX_THREADS) attn_decode_cluster_kernel(con
 
 // ---------------------------------------------------------------------------------------
 // One-token attention for many sequences at once (batched generation steps): grid
-// (n_kv_heads, batch), one warp per query head of the group.  q is finished (rotated), the new
-// k / v row is in the cache already.  The CTA streams its sequence's K and V rows through shared
-// memory 32 keys at a time, double buffered with cp.async, and every warp runs the same
-// per-head chunk routine (attn_warp_chunk_rows); no partials, no merge: one pass over the cache
-// per group of heads, written as finished attention rows.
+// (n_kv_heads, batch, runs), H query heads of the group per warp.  q is finished (rotated), the new
+// k / v row is in the cache already.  The CTA streams its run of the sequence's K and V rows through
+// shared memory AS_KEYS keys at a time, double buffered with cp.async, and every warp runs the
+// per-head chunk routine (attn_warp_chunk_rows).  One run (64 sequences and more): whole sequences,
+// finished attention rows, no partials, no merge.  Several runs (fewer sequences, so that about 512
+// CTAs exist): every run writes its un-normalised output with its (max, sum), merged by the stage
+// that quantises the attention rows.
 constexpr int AS_KEYS = 24;  // two stages of 24 keys: four CTAs per SM at head_dim 128, so that 64 sequences x 8 KV heads run as one wave
 
 template <int D, int H>

@@ -1,14 +1,16 @@
-// Vector stages for many token rows (prompt prefill): the stages of vecstage.cuh with the row
-// held in registers.
+// Vector stages for many token rows (prompt prefill, batched generation steps): the stages of
+// vecstage.cuh with the row held in registers.
 //
-// With thousands of rows the stages are pure HBM traffic (int32 accumulators in, residual stream
-// in and out, int8 activations out); what matters is bytes in flight.  One CTA of 128 threads
-// per row; a thread owns up to V groups of four consecutive elements and issues ALL of its
-// 128-bit loads (accumulators of every term, residual stream, norm weights) before the first
-// use.  The row never visits shared memory: sums of squares and absolute maxima are
-// block reductions over register values, and the quantiser writes packed int8 words straight
-// to the activation buffer (leanstage.cuh).  Arithmetic and its association follow
-// vec_stage_row, which this kernel replaces when there are at least RS_MIN_ROWS rows.
+// With thousands of rows the stages are pure HBM traffic (int32 accumulators or float rows in,
+// residual stream in and out, int8 activations out); what matters is bytes in flight.  A CTA of 128,
+// 512 or 1024 threads per row; a thread owns up to V groups of four consecutive elements and issues
+// ALL of its 128-bit loads (accumulators of every term, residual stream, norm weights) before the
+// first use.  In the prefetching variant a grid of resident CTAs walks the rows, and a thread copies
+// its pieces of the next row into a private shared-memory area (cp.async) while the current row is
+// reduced.  Sums of squares and absolute maxima are block reductions over register values (sharded
+// rows hand this slice's statistics out and take the whole row's back in), and the quantiser writes
+// packed int8 words straight to the activation buffer (leanstage.cuh).  Arithmetic and its
+// association follow vec_stage_row, which this kernel replaces from RS_MIN_ROWS rows on.
 #include <cstdlib>
 
 #include "leanstage.cuh"
