@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(256) qkv_finish_vec_kernel(const __grid_consta
 }
 
 int launch_qkv_finish(const QkvFinishParams& p, int rows, cudaStream_t st) {
-    if (rows >= 32 && p.acc.planes == 1 && p.acc.out % 4 == 0 && p.head_dim % 8 == 0 && p.terms >= 1 && p.terms <= 3)
+    if (rows >= 5 && p.acc.planes == 1 && p.acc.out % 4 == 0 && p.head_dim % 8 == 0 && p.terms >= 1 && p.terms <= 3)
         qkv_finish_vec_kernel<<<rows, 256, 0, st>>>(p);
     else
         qkv_finish_kernel<<<rows, 256, 0, st>>>(p);

@@ -321,8 +321,10 @@ int launch_gemv_planes(const void* tiles, size_t out, size_t in, const int8_t* x
         p.nkt = nkt;
         p.kt_per_split = plan.kt_per_split;
         p.ncols = (ncols - c0) < chunk ? (ncols - c0) : chunk;
-        p.atomic = 0;
+        // plane_stride 0 with a split K range: the splits add into one zeroed plane (exact in any order)
+        p.atomic = plane_stride == 0 && plan.ksplit > 1;
         p.plane_stride = plane_stride;
+        if (p.atomic) RB_CUDA(cudaMemsetAsync(p.acc, 0, (size_t)p.ncols * out * sizeof(int32_t), st));
         rc = dispatch_acc(p, nrt, plan.ksplit, variant, st);
         if (rc) return rc;
     }

@@ -259,11 +259,16 @@ __global__ void advance_kernel(const long long* cur, long long* log, int batch, 
 static int gemv(Ctx& c, const void* tiles, size_t out, size_t in, int ncols, int xs, int32_t* acc, AccView* view,
                 cudaStream_t st) {
     GemvPlan plan = plan_gemv(out, in, ncols < 8 ? ncols : 8);
-    const size_t plane_stride = (size_t)ncols * out;
+    // five and more columns: the K splits add into one plane, so that the register-resident row stages
+    // (complete sums in one plane) can follow; fewer columns keep one plane per split, which the
+    // generation-step stages add while they dequantise
+    const bool gemm = ncols >= GEMM_MIN_COLS && c.variant == ROTOR_B200_VARIANT_AUTO;
+    const bool one_plane = gemm || ncols >= 5;
+    const size_t plane_stride = one_plane ? 0 : (size_t)ncols * out;
     view->acc = acc;
     view->plane_stride = plane_stride;
-    // many columns go to the tiled GEMM, which leaves complete sums in the first plane
-    view->planes = (ncols >= GEMM_MIN_COLS && c.variant == ROTOR_B200_VARIANT_AUTO) ? 1 : plan.ksplit;
+    // (many columns go to the tiled GEMM, which leaves complete sums in the first plane)
+    view->planes = one_plane ? 1 : plan.ksplit;
     view->out = (int)out;
     return launch_gemv_planes(tiles, out, in, c.xq, c.xsum[xs], ncols, acc, plane_stride, plan, c.variant, st);
 }

@@ -19,8 +19,7 @@
 namespace rb {
 
 constexpr int RS_THREADS = 128;
-constexpr int RS_MIN_ROWS = 32;        // stages that read accumulators (complete sums in one plane from 32 columns on)
-constexpr int RS_MIN_ROWS_FLOAT = 5;   // stages that read float rows or the embedding table
+constexpr int RS_MIN_ROWS = 5;         // (fewer rows: the generation-step kernels or the shared-memory stage)
 constexpr int RS_WIDE_THREADS = 512;
 // With fewer rows than SMs every CTA runs its code once, from a cold instruction cache: the duration is
 // the length of the unrolled code, so the widest rows take 1024 threads with half the groups each.
@@ -277,8 +276,7 @@ __global__ void __launch_bounds__(TH, TH > 128 ? (V <= 4 ? 2 : 1) : (V > 8 ? 4 :
 // one plane, 16-byte aligned rows, no sharded-row statistics.
 bool row_stage_supported(const VecStageParams& p, int rows) {
     static const bool off = getenv("ROTOR_B200_NO_ROWSTAGE") != nullptr;  // comparison aid
-    const bool from_floats = p.mode == VS_EMBED || p.mode == VS_PLAIN;
-    if (off || rows < (from_floats ? RS_MIN_ROWS_FLOAT : RS_MIN_ROWS)) return false;
+    if (off || rows < RS_MIN_ROWS) return false;
     if (p.mode != VS_EMBED && p.mode != VS_PLAIN && p.mode != VS_OPROJ && p.mode != VS_FFN && p.mode != VS_DOWN &&
         p.mode != VS_DEQ)
         return false;
