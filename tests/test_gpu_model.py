@@ -208,6 +208,30 @@ def test_greedy_generation_identical_to_reference(rb, golden_dir, name):
 
 
 @pytest.mark.parametrize("name", list(G.TINY_MODELS))
+def test_per_step_logits_against_fixture_margins(rb, golden_dir, name):
+    """Every one of the 32 teacher-forced generation steps against the reference fixture: the logit error
+    (max-abs over the vocabulary, in units of the step's logit RMS) stays below the tolerance AND below half
+    the reference's own top-1 / top-2 margin at that step (stored with the fixture), which is what makes the
+    greedy tokens identical rather than merely likely to be."""
+    z = np.load(os.path.join(golden_dir, f"model_{name}.npz"))
+    om, prompt, model = _tiny(rb, name, rb.sem.REFERENCE)
+    want = z["greedy_ids"].tolist()
+    logits, cache = model.forward(prompt[None, :], use_cache=True)
+    cur = logits[0, -1]
+    worst = 0.0
+    for i in range(G.N_NEW):
+        e = rel_err(cur, z["step_logits"][i])
+        worst = max(worst, e)
+        assert e < TOL, (i, e)
+        assert 2 * e < z["top2_margin"][i], (i, e, float(z["top2_margin"][i]))
+        assert int(np.argmax(cur)) == want[len(prompt) + i]
+        if i + 1 < G.N_NEW:
+            nxt, cache = model.forward(np.array([[want[len(prompt) + i]]]), past_kv_cache=cache, use_cache=True)
+            cur = nxt[0, -1]
+    print(f"{name}: worst per-step logit error {worst:.2e} of RMS, smallest margin {float(z['top2_margin'].min()):.2e}")
+
+
+@pytest.mark.parametrize("name", list(G.TINY_MODELS))
 def test_baseline_semantics_against_oracle(rb, name):
     """Published semantics (int8 activations, relu^2, rotary, causal, eps 1e-5) against the oracle that
     quantises identically.  A value on a rounding tie of the quantiser is decided by float summation
