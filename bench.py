@@ -31,7 +31,8 @@ One JSON line is printed by rank 0:
                (strong scaling), batch 1 / 8 / 64 after a 1024-token prompt
   cpu_baseline the NumPy oracle port of the reference's path on this box's host cores,
                bounded sample (N = 1 only)
---impl reference times that same CPU port as the reference arm.
+--impl reference times the reference itself on the host cores (its installed copy under baseline/_ref,
+through its own TextGenerator.generate; the port stands in where the copy is absent).
 --workload / --only select one section alone (profiling aids; they print their own line).
 """
 import argparse
